@@ -1,0 +1,153 @@
+/*
+ * mbema.h -- C ABI of libmbema.so: B200 (sm_100a) kernels for MathBrain's Per-Slot-EMA hot path.
+ *
+ * The reference (Mr-Skeleton-Max/MathBrain) has no FFI: its hot path is a set of Python operators
+ * backed by Triton kernels.  Each entry point below names the reference operator it stands in for
+ * (path within the reference tree : line).  The Python package mathbrain_b200 binds these symbols
+ * with ctypes and re-exports them under the reference's operator names.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless stated otherwise; all tensors are dense, row-major,
+ *     innermost dimension contiguous, in the shapes written beside each argument;
+ *   - the caller owns every buffer, including `workspace` (size from the matching *_workspace_bytes);
+ *     the library allocates nothing and keeps no mutable global state, so calls on different streams
+ *     may run concurrently as long as their buffers differ;
+ *   - `stream` is a cudaStream_t passed as void*; work is only enqueued, no entry point synchronises;
+ *   - the return value is 0 on success, otherwise an MBEMA_ERR_* code (see mbema_strerror); argument
+ *     errors are detected before anything is launched;
+ *   - dtype codes: MBEMA_F32 = 0, MBEMA_BF16 = 1.
+ *
+ * State convention (mathbrain/data.py:128-140, tests/test_gold_standard.py:196-221):
+ *   the memory state of slot k seen at chunk step t is
+ *       M_0[k] = c_base[k],   M_{t+1}[k] = rho * (M_t[k] + [x_t == key_k]).
+ */
+#ifndef MBEMA_H_
+#define MBEMA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MBEMA_VERSION 100
+
+#define MBEMA_F32 0
+#define MBEMA_BF16 1
+
+/* time-tile length of the slot-state snapshots (rows of one attention tile) */
+#define MBEMA_TILE_T 128
+
+/* flags */
+#define MBEMA_FLAG_SILU 1          /* gate = SiLU(pre); otherwise the gate is linear (use_silu=False)      */
+#define MBEMA_FLAG_LISTED_ONLY 2   /* softmax over listed slots only (what the reference's Triton kernel  */
+                                   /* computes, mathbrain/triton_flash_ema.py:214-230); default: all       */
+                                   /* V_total slots, unlisted ones with score 0 and value 0, as            */
+                                   /* mathbrain/flash_ema_attention.py:76-79                               */
+#define MBEMA_FLAG_CBASE_EXTRA_DECAY 4 /* M_0 = rho * c_base (mathbrain/triton_flash_ema.py:48-50,185)     */
+
+/* compute modes of the attention kernels */
+#define MBEMA_MODE_FP32 0          /* fp32 arithmetic on the CUDA cores                                    */
+#define MBEMA_MODE_TC_BF16 1       /* gate product on tcgen05 tensor cores, bf16 operands, fp32 accumulate */
+
+/* error codes */
+#define MBEMA_OK 0
+#define MBEMA_ERR_NULL 1
+#define MBEMA_ERR_SHAPE 2
+#define MBEMA_ERR_UNSUPPORTED 3
+#define MBEMA_ERR_WORKSPACE 4
+#define MBEMA_ERR_CUDA 5
+#define MBEMA_ERR_DTYPE 6
+#define MBEMA_ERR_ALIGN 7
+
+int mbema_version(void);
+const char* mbema_strerror(int code);
+/* last CUDA runtime error text seen by this thread inside the library (host pointer, never NULL) */
+const char* mbema_last_cuda_error(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Query-side per-slot EMA scan.
+ * Replaces compute_query_ema_history (mathbrain/triton_ema_query.py:120-169; kernel :11-64).
+ *   C_seq[b,t,:] = state of token x[b,t] just before step t; seeded, for every listed key, from
+ *   c_init (state seen at step 0); a listed key that occurs more than once in c_init_keys takes the
+ *   FIRST entry; key < 0 is ignored.  doc_ids (optional) reset a token's state when the document id
+ *   differs from the one at its previous occurrence (:50-57).
+ *   x [B,T] i64   rhos [N] f32   c_init [B,K,N] f32 or NULL   c_init_keys [B,K] i64 or NULL
+ *   doc_ids [B,T] i32 or NULL    C_seq [B,T,N] f32 (out)
+ *   limits: 1 <= T <= 8192, 1 <= N <= 128, tokens in [0, 2^31).
+ * ---------------------------------------------------------------------------------------------- */
+size_t mbema_query_scan_workspace_bytes(int64_t B, int64_t T);
+int mbema_query_scan(const int64_t* x, const float* rhos, const float* c_init, const int64_t* c_init_keys,
+                     const int32_t* doc_ids, float* C_seq, int64_t B, int64_t T, int64_t N, int64_t K,
+                     int flags, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Slot-state snapshots at the start of every MBEMA_TILE_T-step time tile, plus what the attention
+ * kernels need to rebuild the state inside a tile.
+ * Replaces precompute_boundaries (mathbrain/triton_flash_ema.py:81-113; kernel :29-78).
+ *   unique [B,K] i64 (-1 = not a slot)   c_base [B,K,N] f32 or NULL (zeros)
+ *   out: tile_state [B, nT, K, N] f32 with nT = ceil(T / MBEMA_TILE_T)
+ *        tok_state  [B, T, N]     f32  state of x[b,t]'s own slot just before step t (0 if unlisted)
+ *        kcount     [B]           i32  number of valid (>= 0) entries of unique[b,:]
+ *   flags: MBEMA_FLAG_CBASE_EXTRA_DECAY.
+ * ---------------------------------------------------------------------------------------------- */
+size_t mbema_tile_states_workspace_bytes(int64_t B, int64_t T);
+int mbema_tile_states(const int64_t* x, const int64_t* unique, const float* rhos, const float* c_base,
+                      float* tile_state, float* tok_state, int32_t* kcount, int64_t B, int64_t T, int64_t N,
+                      int64_t K, int flags, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Query gate + LayerNorm, forward and backward.
+ * Replaces FusedGatingFunction (mathbrain/triton_fused_gating.py:122-177; kernels :12-57, :61-119).
+ *   Y = LayerNorm_eps(x_q * gate(p_pre + bias)) * ln_w + ln_b,  gate = SiLU or identity.
+ *   x_q, p_pre [rows, D] (dtype codes)   bias, ln_w, ln_b [D] f32   Y [rows, D] (y_dtype)
+ *   mu, rstd [rows] f32 (saved for the backward).   D % 4 == 0, D <= 1024.
+ * backward: dY [rows,D] -> dx_q, dp_pre [rows,D] f32;  dbias, dln_w, dln_b [D] f32.
+ * ---------------------------------------------------------------------------------------------- */
+int mbema_qgate_fwd(const void* x_q, int x_dtype, const void* p_pre, int p_dtype, const float* bias,
+                    const float* ln_w, const float* ln_b, float eps, void* Y, int y_dtype, float* mu,
+                    float* rstd, int64_t rows, int64_t D, int flags, void* stream);
+size_t mbema_qgate_bwd_workspace_bytes(int64_t rows, int64_t D);
+int mbema_qgate_bwd(const void* dY, int dy_dtype, const void* x_q, int x_dtype, const void* p_pre, int p_dtype,
+                    const float* bias, const float* ln_w, const float* mu, const float* rstd, float* dx_q,
+                    float* dp_pre, float* dbias, float* dln_w, float* dln_b, int64_t rows, int64_t D, int flags,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Flash-EMA gated cross-attention over the listed slots, forward.
+ * Replaces FlashEMAFunction.forward / flash_ema_forward / _flash_ema_fwd
+ * (mathbrain/triton_flash_ema.py:571-582, :529-568, :121-241); semantics of
+ * mathbrain/flash_ema_attention.py:46-82.
+ *   Q [B,H,T,hd] (q_dtype)   x [B,T] i64   E_k, E_v [B,K,H*hd] (e_dtype)   W_pe [N,H*hd] f32
+ *   rhos [N] f32   unique [B,K] i64   tile_state, tok_state, kcount from mbema_tile_states
+ *   seq_lens [B] i32 or NULL: steps >= seq_lens[b] are skipped (their outputs are left untouched)
+ *   out: O [B,H,T,hd] f32, LSE [B,H,T] f32 (log of the softmax normaliser, saved for the backward)
+ *   limits: hd == 64, N in {16, 32, 64, 128} for MBEMA_MODE_TC_BF16; hd == 64, N <= 128 for FP32.
+ * ---------------------------------------------------------------------------------------------- */
+size_t mbema_flash_fwd_workspace_bytes(int64_t B, int64_t H, int64_t T, int64_t hd, int64_t N, int64_t K, int mode);
+int mbema_flash_fwd(const void* Q, int q_dtype, const int64_t* x, const void* E_k, const void* E_v, int e_dtype,
+                    const float* W_pe, const float* rhos, const int64_t* unique, const float* tile_state,
+                    const float* tok_state, const int32_t* kcount, const int32_t* seq_lens, float* O, float* LSE,
+                    int64_t B, int64_t H, int64_t T, int64_t hd, int64_t N, int64_t K, int64_t V_total, int flags,
+                    int mode, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Flash-EMA backward: recomputes state, gate and probabilities tile by tile.
+ * Replaces FlashEMAFunction.backward / _flash_ema_bwd_dq_de / _flash_ema_bwd_dw
+ * (mathbrain/triton_flash_ema.py:585-650, :250-355, :359-469).
+ *   dO [B,H,T,hd] (do_dtype), O and LSE from the forward.
+ *   out (all f32, fully overwritten): dQ [B,H,T,hd], dE_k, dE_v [B,K,H*hd], dW_pe [N,H*hd].
+ * ---------------------------------------------------------------------------------------------- */
+size_t mbema_flash_bwd_workspace_bytes(int64_t B, int64_t H, int64_t T, int64_t hd, int64_t N, int64_t K, int mode);
+int mbema_flash_bwd(const void* Q, int q_dtype, const int64_t* x, const void* E_k, const void* E_v, int e_dtype,
+                    const float* W_pe, const float* rhos, const int64_t* unique, const float* tile_state,
+                    const float* tok_state, const int32_t* kcount, const int32_t* seq_lens, const float* O,
+                    const float* LSE, const void* dO, int do_dtype, float* dQ, float* dE_k, float* dE_v,
+                    float* dW_pe, int64_t B, int64_t H, int64_t T, int64_t hd, int64_t N, int64_t K,
+                    int64_t V_total, int flags, int mode, void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MBEMA_H_ */

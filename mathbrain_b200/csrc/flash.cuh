@@ -1,0 +1,28 @@
+// Argument block and internal entry points shared by the attention kernels.
+#pragma once
+#include "common.cuh"
+
+namespace mbema {
+
+struct FlashArgs {
+    const void* Q; int q_dt;
+    const long long* x;
+    const void* Ek; const void* Ev; int e_dt;
+    const float* W; const float* rhos;
+    const long long* unique;
+    const float* tile_state; const float* tok_state;
+    const int* kcount; const int* seq_lens;
+    float* O; float* LSE;
+    // backward only
+    const void* dO; int do_dt;
+    float* dQ; float* dEk; float* dEv; float* dW_part;
+    int B, H, T, N, K, nT;
+    float v_total;
+    int silu, listed_only;
+};
+
+int flash_fwd_simt(const FlashArgs& a, cudaStream_t st);
+size_t flash_bwd_simt_ws(int64_t B, int64_t H, int64_t T, int64_t N);
+int flash_bwd_simt(FlashArgs a, float* dW, void* ws, cudaStream_t st);
+
+}  // namespace mbema

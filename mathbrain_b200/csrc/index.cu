@@ -1,0 +1,325 @@
+// Per-slot EMA state kernels: token sort/link, query-side chain scan, slot-state snapshots.
+//
+// The query-side state of token x_t depends only on the earlier occurrences of the same token, so the
+// time axis of every sample is first regrouped by token: one CTA per sample sorts (token, t) pairs in
+// shared memory (bitonic network), which turns every token's occurrences into one contiguous, time-ordered
+// "chain".  A warp then walks a chain with the N channels spread over its lanes (coalesced 4*N-byte rows),
+// carrying the fp32 state in registers:  c_t = (c_s + 1) * rho^(t - s).  No vocabulary-sized scratch is
+// touched (the reference fills [B, V+1, N] floats per call, mathbrain/triton_ema_query.py:141-143).
+#include <math.h>
+
+#include "common.cuh"
+
+namespace mbema {
+
+static constexpr int SORT_THREADS = 1024;
+static constexpr int NO_SEED = 0x7fffffff;
+
+struct IndexWs {
+    int32_t* s_tok;    // [B, T]  token of the j-th entry in (token, t) order
+    int32_t* s_pos;    // [B, T]  its time step
+    int32_t* ch_off;   // [B, T]  offset of the c-th chain head in the sorted order
+    int32_t* seed;     // [B, T]  at a chain head: index of the first listed key equal to the token, or NO_SEED
+    int32_t* n_chain;  // [B]
+    int32_t* n_valid;  // [B]     number of keys >= 0
+};
+
+static size_t index_ws_bytes(int64_t B, int64_t T) {
+    return align_up((size_t)(4 * B * T + 2 * B) * sizeof(int32_t), 256) + 256;
+}
+
+static IndexWs carve_index_ws(void* ws, int64_t B, int64_t T) {
+    IndexWs w;
+    uintptr_t p = (uintptr_t)ws;
+    p = (p + 255) / 256 * 256;
+    int32_t* base = (int32_t*)p;
+    w.s_tok = base;
+    w.s_pos = base + B * T;
+    w.ch_off = base + 2 * B * T;
+    w.seed = base + 3 * B * T;
+    w.n_chain = base + 4 * B * T;
+    w.n_valid = w.n_chain + B;
+    return w;
+}
+
+// ----------------------------------------------------------------------------------------------
+// one CTA per sample: sort (token, t), mark chain heads, compact them, attach listed keys
+// dynamic smem: uint64 key[Tp] | int32 seed[Tp] | int32 scan[SORT_THREADS]
+// ----------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(SORT_THREADS)
+k_sort_link(const int64_t* __restrict__ x, const int64_t* __restrict__ keys, IndexWs w, int T, int Tp, int K) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    unsigned long long* key = reinterpret_cast<unsigned long long*>(smem_raw);
+    int* seed = reinterpret_cast<int*>(key + Tp);
+    int* scan = seed + Tp;
+    const int b = blockIdx.x;
+    const int tid = threadIdx.x;
+
+    for (int i = tid; i < Tp; i += SORT_THREADS) {
+        unsigned long long kk = ~0ull;
+        if (i < T) {
+            unsigned long long tok = (unsigned long long)(x[(size_t)b * T + i]) & 0x7fffffffull;
+            kk = (tok << 32) | (unsigned)i;
+        }
+        key[i] = kk;
+        seed[i] = NO_SEED;
+    }
+    __syncthreads();
+    for (int k = 2; k <= Tp; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = tid; i < Tp; i += SORT_THREADS) {
+                int ixj = i ^ j;
+                if (ixj > i) {
+                    unsigned long long a = key[i], c = key[ixj];
+                    bool up = ((i & k) == 0);
+                    if ((a > c) == up) {
+                        key[i] = c;
+                        key[ixj] = a;
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    }
+    // chain heads: contiguous segment per thread, block-wide exclusive scan of the head counts
+    const int per = (Tp + SORT_THREADS - 1) / SORT_THREADS;
+    const int lo = tid * per;
+    int cnt = 0;
+    for (int i = lo; i < lo + per && i < T; ++i) {
+        bool head = (i == 0) || ((key[i] >> 32) != (key[i - 1] >> 32));
+        cnt += head ? 1 : 0;
+    }
+    scan[tid] = cnt;
+    __syncthreads();
+    for (int off = 1; off < SORT_THREADS; off <<= 1) {
+        int v = (tid >= off) ? scan[tid - off] : 0;
+        __syncthreads();
+        scan[tid] += v;
+        __syncthreads();
+    }
+    int c = scan[tid] - cnt;  // exclusive prefix
+    int32_t* ch_off = w.ch_off + (size_t)b * T;
+    for (int i = lo; i < lo + per && i < T; ++i) {
+        bool head = (i == 0) || ((key[i] >> 32) != (key[i - 1] >> 32));
+        if (head) ch_off[c++] = i;
+    }
+    if (tid == SORT_THREADS - 1) w.n_chain[b] = scan[tid];
+
+    // listed keys -> chain heads (first listed entry wins)
+    int nvalid = 0;
+    if (keys != nullptr) {
+        for (int i = tid; i < K; i += SORT_THREADS) {
+            long long kv = keys[(size_t)b * K + i];
+            if (kv < 0) continue;
+            nvalid++;
+            unsigned long long target = ((unsigned long long)kv & 0x7fffffffull) << 32;
+            int l = 0, r = T;  // lower bound of target in key[0..T)
+            while (l < r) {
+                int m = (l + r) >> 1;
+                if (key[m] < target) l = m + 1; else r = m;
+            }
+            if (l < T && (key[l] >> 32) == (target >> 32)) atomicMin(&seed[l], i);
+        }
+    }
+    __syncthreads();
+    scan[tid] = nvalid;
+    __syncthreads();
+    for (int off = SORT_THREADS / 2; off > 0; off >>= 1) {
+        if (tid < off) scan[tid] += scan[tid + off];
+        __syncthreads();
+    }
+    if (tid == 0) w.n_valid[b] = scan[0];
+    for (int i = tid; i < T; i += SORT_THREADS) {
+        w.s_tok[(size_t)b * T + i] = (int32_t)(key[i] >> 32);
+        w.s_pos[(size_t)b * T + i] = (int32_t)(key[i] & 0xffffffffull);
+        w.seed[(size_t)b * T + i] = seed[i];
+    }
+}
+
+// ----------------------------------------------------------------------------------------------
+// one warp per chain; lanes hold channels lane, lane+32, lane+64, lane+96
+// ----------------------------------------------------------------------------------------------
+static constexpr int CHAIN_WARPS = 8;
+
+__global__ void __launch_bounds__(CHAIN_WARPS * 32)
+k_chain_scan(IndexWs w, const float* __restrict__ rhos, const float* __restrict__ c_init,
+             const int32_t* __restrict__ doc_ids, float* __restrict__ out, int T, int N, int K, int extra_decay) {
+    const int b = blockIdx.y;
+    const int c = blockIdx.x * CHAIN_WARPS + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    const int nch = w.n_chain[b];
+    if (c >= nch) return;
+    const int32_t* ch_off = w.ch_off + (size_t)b * T;
+    const int32_t* s_pos = w.s_pos + (size_t)b * T;
+    const int j0 = ch_off[c];
+    const int j1 = (c + 1 < nch) ? ch_off[c + 1] : T;
+    const int sd = w.seed[(size_t)b * T + j0];
+
+    float l2r[4], u[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int n = lane + 32 * i;
+        float r = (n < N) ? rhos[n] : 1.0f;
+        l2r[i] = log2f(r);
+        u[i] = 0.0f;
+        if (sd != NO_SEED && n < N && c_init != nullptr) {
+            u[i] = c_init[((size_t)b * K + sd) * N + n];
+            if (extra_decay) u[i] *= r;
+        }
+    }
+    bool has = (sd != NO_SEED);
+    int s_ref = 0;
+    int last_doc = (doc_ids != nullptr) ? doc_ids[(size_t)b * T] : 0;
+    for (int j = j0; j < j1; ++j) {
+        const int t = s_pos[j];
+        bool keep = has;
+        if (doc_ids != nullptr) {
+            int d = doc_ids[(size_t)b * T + t];
+            if (has && d != last_doc) keep = false;
+            last_doc = d;
+        }
+        const float dt = (float)(t - s_ref);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            int n = lane + 32 * i;
+            float cval = keep ? u[i] * exp2f(dt * l2r[i]) : 0.0f;
+            if (n < N) out[((size_t)b * T + t) * N + n] = cval;
+            u[i] = cval + 1.0f;
+        }
+        s_ref = t;
+        has = true;
+    }
+}
+
+// ----------------------------------------------------------------------------------------------
+// one warp per listed slot: state at the start of every time tile
+// ----------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(CHAIN_WARPS * 32)
+k_tile_states(IndexWs w, const int64_t* __restrict__ unique, const float* __restrict__ rhos,
+              const float* __restrict__ c_base, float* __restrict__ tile_state, int T, int N, int K, int nT,
+              int extra_decay) {
+    const int b = blockIdx.y;
+    const int k = blockIdx.x * CHAIN_WARPS + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (k >= K) return;
+    const long long kv = unique[(size_t)b * K + k];
+    const int32_t* s_tok = w.s_tok + (size_t)b * T;
+    const int32_t* s_pos = w.s_pos + (size_t)b * T;
+    float* out = tile_state + ((size_t)b * nT * K + k) * N;  // + tile * K * N
+    if (kv < 0) {
+        for (int i = 0; i < nT; ++i)
+            for (int n = lane; n < N; n += 32) out[(size_t)i * K * N + n] = 0.0f;
+        return;
+    }
+    const int key = (int)(kv & 0x7fffffff);
+    int l = 0, r = T;
+    while (l < r) {
+        int m = (l + r) >> 1;
+        if (s_tok[m] < key) l = m + 1; else r = m;
+    }
+    int j = l;
+    float l2r[4], u[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int n = lane + 32 * i;
+        float rr = (n < N) ? rhos[n] : 1.0f;
+        l2r[i] = log2f(rr);
+        u[i] = 0.0f;
+        if (c_base != nullptr && n < N) {
+            u[i] = c_base[((size_t)b * K + k) * N + n];
+            if (extra_decay) u[i] *= rr;
+        }
+    }
+    int s_ref = 0;
+    for (int tile = 0; tile < nT; ++tile) {
+        const int t0 = tile * MBEMA_TILE_T;
+        while (j < T && s_tok[j] == key && s_pos[j] < t0) {
+            const int s = s_pos[j];
+            const float dt = (float)(s - s_ref);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) u[i] = u[i] * exp2f(dt * l2r[i]) + 1.0f;
+            s_ref = s;
+            ++j;
+        }
+        const float dt = (float)(t0 - s_ref);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            int n = lane + 32 * i;
+            if (n < N) out[(size_t)tile * K * N + n] = u[i] * exp2f(dt * l2r[i]);
+        }
+    }
+}
+
+static int launch_sort_link(const int64_t* x, const int64_t* keys, IndexWs w, int64_t B, int64_t T, int64_t K,
+                            cudaStream_t st) {
+    int Tp = 2;
+    while (Tp < T) Tp <<= 1;
+    size_t smem = (size_t)Tp * 12 + SORT_THREADS * 4;
+    // per-device attribute; setting it on every call keeps the library free of per-device bookkeeping
+    MBEMA_CUDA_TRY(cudaFuncSetAttribute(k_sort_link, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        8192 * 12 + SORT_THREADS * 4));
+    k_sort_link<<<(unsigned)B, SORT_THREADS, smem, st>>>(x, keys, w, (int)T, Tp, (int)K);
+    return check_launch();
+}
+
+}  // namespace mbema
+
+using namespace mbema;
+
+extern "C" size_t mbema_query_scan_workspace_bytes(int64_t B, int64_t T) { return index_ws_bytes(B, T); }
+extern "C" size_t mbema_tile_states_workspace_bytes(int64_t B, int64_t T) { return index_ws_bytes(B, T); }
+
+static int check_index_args(int64_t B, int64_t T, int64_t N, int64_t K) {
+    if (B < 0 || T < 1 || N < 1 || K < 0) return MBEMA_ERR_SHAPE;
+    if (T > 8192 || N > 128 || B > 65535) return MBEMA_ERR_UNSUPPORTED;
+    return MBEMA_OK;
+}
+
+extern "C" int mbema_query_scan(const int64_t* x, const float* rhos, const float* c_init, const int64_t* c_init_keys,
+                                const int32_t* doc_ids, float* C_seq, int64_t B, int64_t T, int64_t N, int64_t K,
+                                int flags, void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = check_index_args(B, T, N, K);
+    if (rc) return rc;
+    if (B == 0) return MBEMA_OK;
+    if (!x || !rhos || !C_seq || !workspace) return MBEMA_ERR_NULL;
+    if ((c_init == nullptr) != (c_init_keys == nullptr)) return MBEMA_ERR_NULL;
+    if (workspace_bytes < index_ws_bytes(B, T)) return MBEMA_ERR_WORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    IndexWs w = carve_index_ws(workspace, B, T);
+    rc = launch_sort_link(x, c_init_keys, w, B, T, c_init_keys ? K : 0, st);
+    if (rc) return rc;
+    dim3 grid((unsigned)((T + CHAIN_WARPS - 1) / CHAIN_WARPS), (unsigned)B);
+    k_chain_scan<<<grid, CHAIN_WARPS * 32, 0, st>>>(w, rhos, c_init, doc_ids, C_seq, (int)T, (int)N, (int)K,
+                                                    (flags & MBEMA_FLAG_CBASE_EXTRA_DECAY) ? 1 : 0);
+    return check_launch();
+}
+
+extern "C" int mbema_tile_states(const int64_t* x, const int64_t* unique, const float* rhos, const float* c_base,
+                                 float* tile_state, float* tok_state, int32_t* kcount, int64_t B, int64_t T,
+                                 int64_t N, int64_t K, int flags, void* workspace, size_t workspace_bytes,
+                                 void* stream) {
+    int rc = check_index_args(B, T, N, K);
+    if (rc) return rc;
+    if (B == 0) return MBEMA_OK;
+    if (K < 1) return MBEMA_ERR_SHAPE;
+    if (!x || !unique || !rhos || !tile_state || !tok_state || !kcount || !workspace) return MBEMA_ERR_NULL;
+    if (workspace_bytes < index_ws_bytes(B, T)) return MBEMA_ERR_WORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    IndexWs w = carve_index_ws(workspace, B, T);
+    const int extra = (flags & MBEMA_FLAG_CBASE_EXTRA_DECAY) ? 1 : 0;
+    rc = launch_sort_link(x, unique, w, B, T, K, st);
+    if (rc) return rc;
+    dim3 g1((unsigned)((T + CHAIN_WARPS - 1) / CHAIN_WARPS), (unsigned)B);
+    // a chain without a listed key keeps zero state in tok_state only if it is unlisted: such tokens own no slot,
+    // so their rows are never read by the attention kernels; they are still written (query-scan semantics).
+    k_chain_scan<<<g1, CHAIN_WARPS * 32, 0, st>>>(w, rhos, c_base, nullptr, tok_state, (int)T, (int)N, (int)K, extra);
+    rc = check_launch();
+    if (rc) return rc;
+    const int nT = (int)((T + MBEMA_TILE_T - 1) / MBEMA_TILE_T);
+    dim3 g2((unsigned)((K + CHAIN_WARPS - 1) / CHAIN_WARPS), (unsigned)B);
+    k_tile_states<<<g2, CHAIN_WARPS * 32, 0, st>>>(w, unique, rhos, c_base, tile_state, (int)T, (int)N, (int)K, nT, extra);
+    rc = check_launch();
+    if (rc) return rc;
+    MBEMA_CUDA_TRY(cudaMemcpyAsync(kcount, w.n_valid, (size_t)B * sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
+    return MBEMA_OK;
+}

@@ -1,0 +1,354 @@
+"""Python operators of the Per-Slot-EMA hot path, with the reference's names and signatures.
+
+Every operator here runs hand-written sm_100a CUDA kernels from libmbema.so through its C ABI
+(include/mbema.h).  There is no Triton, no dispatch between back ends and no CPU path: a tensor that is not
+on a CUDA device, or a missing shared library, raises.
+
+Reference operators mirrored (paths within the reference tree):
+  compute_query_ema_history            mathbrain/triton_ema_query.py:120
+  precompute_boundaries                mathbrain/triton_flash_ema.py:81
+  _build_unique_index                  mathbrain/triton_flash_ema.py:475
+  FlashEMAFunction                     mathbrain/triton_flash_ema.py:571
+  FusedGatingFunction                  mathbrain/triton_fused_gating.py:122
+  fused_apply_symmetric_query_gating   mathbrain/triton_fused_gating.py:179
+  HAS_TRITON                           the flag mathbrain/model.py:78,162 tests before taking the GPU path
+"""
+from __future__ import annotations
+
+import contextlib
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+# mathbrain/model.py takes its GPU operator path when this name is truthy.
+HAS_TRITON = True
+
+_OPTIONS = {"inactive_mass": "full_V", "cbase_extra_decay": False, "mode": "fp32"}
+_MODES = {"fp32": _lib.MODE_FP32, "tc_bf16": _lib.MODE_TC_BF16}
+
+
+def set_options(inactive_mass: Optional[str] = None, cbase_extra_decay: Optional[bool] = None,
+                mode: Optional[str] = None):
+    """Semantics and precision switches of the attention operator.
+
+    inactive_mass      "full_V" (default): softmax over all V_total vocabulary slots, as the PyTorch reference
+                       (mathbrain/flash_ema_attention.py:76-79); "listed_only": over the listed slots only, which
+                       is what the reference's Triton kernel computes (mathbrain/triton_flash_ema.py:214-230).
+    cbase_extra_decay  False (default): the slot state seen at chunk step 0 is exactly c_base
+                       (mathbrain/data.py:128-140); True: rho * c_base, the Triton kernels' convention
+                       (mathbrain/triton_flash_ema.py:48-50,185).
+    mode               "fp32": fp32 arithmetic on the CUDA cores; "tc_bf16": gate product on the tensor cores.
+    """
+    if inactive_mass is not None:
+        if inactive_mass not in ("full_V", "listed_only"):
+            raise ValueError(inactive_mass)
+        _OPTIONS["inactive_mass"] = inactive_mass
+    if cbase_extra_decay is not None:
+        _OPTIONS["cbase_extra_decay"] = bool(cbase_extra_decay)
+    if mode is not None:
+        if mode not in _MODES:
+            raise ValueError(mode)
+        _OPTIONS["mode"] = mode
+
+
+def get_options():
+    return dict(_OPTIONS)
+
+
+@contextlib.contextmanager
+def options(**kw):
+    old = dict(_OPTIONS)
+    set_options(**kw)
+    try:
+        yield
+    finally:
+        _OPTIONS.update(old)
+
+
+# ---------------------------------------------------------------------------------------------
+# helpers
+# ---------------------------------------------------------------------------------------------
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and t.device.type != "cuda":
+            raise _lib.MbemaError("mathbrain_b200 operators need CUDA tensors (got %s); there is no CPU path"
+                                  % t.device)
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _dt(t):
+    if t.dtype == torch.float32:
+        return _lib.F32
+    if t.dtype == torch.bfloat16:
+        return _lib.BF16
+    raise _lib.MbemaError("unsupported dtype %s (float32 or bfloat16 expected)" % t.dtype)
+
+
+def _f32_or_bf16(t):
+    return t if t.dtype in (torch.float32, torch.bfloat16) else t.float()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _workspace(nbytes, device):
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+# ---------------------------------------------------------------------------------------------
+# query-side scan
+# ---------------------------------------------------------------------------------------------
+def compute_query_ema_history(x, rhos, vocab_size, c_init=None, c_init_keys=None, doc_ids=None):
+    """C_seq[b, t, :] = EMA state of token x[b, t] just before step t, float32 [B, L, N].
+
+    Drop-in for mathbrain/triton_ema_query.py:120.  ``vocab_size`` is accepted for signature compatibility; no
+    vocabulary-sized buffer is used.  When a key occurs more than once in ``c_init_keys`` (the collate function
+    pads the list with token 0) the first entry wins.
+    """
+    _require_cuda(x, rhos, c_init, c_init_keys, doc_ids)
+    lib = _lib.load()
+    B, L = x.shape
+    N = rhos.shape[0]
+    x = x.long().contiguous()
+    rhos = rhos.float().contiguous()
+    K = 0
+    if c_init is not None and c_init_keys is not None:
+        c_init = c_init.float().contiguous()
+        c_init_keys = c_init_keys.long().contiguous()
+        K = c_init_keys.shape[1]
+        if c_init.shape != (B, K, N):
+            raise _lib.MbemaError("c_init must be [B, K, N] matching c_init_keys [B, K]")
+    else:
+        c_init = c_init_keys = None
+    if doc_ids is not None:
+        doc_ids = doc_ids.to(torch.int32).contiguous()
+    C_seq = torch.empty(B, L, N, dtype=torch.float32, device=x.device)
+    ws = _workspace(lib.mbema_query_scan_workspace_bytes(B, L), x.device)
+    flags = 0
+    rc = lib.mbema_query_scan(_ptr(x), _ptr(rhos), _ptr(c_init), _ptr(c_init_keys), _ptr(doc_ids), _ptr(C_seq),
+                              B, L, N, K, flags, _ptr(ws), ws.numel(), _stream())
+    _lib.check(rc, "mbema_query_scan")
+    return C_seq
+
+
+# ---------------------------------------------------------------------------------------------
+# slot-state snapshots (the handle the model passes around as "C_bounds")
+# ---------------------------------------------------------------------------------------------
+@dataclass
+class TileStates:
+    """Opaque result of precompute_boundaries, consumed by FlashEMAFunction."""
+    tile_state: torch.Tensor            # [B, nT, K, N] f32
+    tok_state: torch.Tensor             # [B, T, N] f32
+    kcount: torch.Tensor                # [B] i32
+    seq_lens: Optional[torch.Tensor]    # [B] i32 or None
+    unique: torch.Tensor                # [B, K] i64, the slot list the snapshots were built for
+    shape: tuple                        # (B, T, K, N)
+
+
+def precompute_boundaries(x, unique_tensor, rhos, Br, c_init=None, doc_ids=None, seq_lens=None):
+    """Slot-state snapshots per time tile; drop-in for mathbrain/triton_flash_ema.py:81.
+
+    ``Br`` (the reference's tile length) is accepted and ignored: the tile length is a property of the kernels
+    (128 steps).  ``doc_ids`` must be None, as in every call the reference makes (mathbrain/model.py:180; the
+    attention wrappers always run with has_doc_ids=False, mathbrain/triton_flash_ema.py:553-559).
+    ``seq_lens`` (extension, int tensor [B]) marks the valid length of every row; later steps are skipped by the
+    attention kernels.
+    """
+    if doc_ids is not None:
+        raise NotImplementedError("precompute_boundaries: doc_ids is not supported (chunks are single-document)")
+    _require_cuda(x, unique_tensor, rhos, c_init, seq_lens)
+    lib = _lib.load()
+    B, L = x.shape
+    K = unique_tensor.shape[1]
+    N = rhos.shape[0]
+    x = x.long().contiguous()
+    unique = unique_tensor.long().contiguous()
+    rhos = rhos.float().contiguous()
+    if c_init is not None:
+        c_init = c_init.float().contiguous()
+        if c_init.shape != (B, K, N):
+            raise _lib.MbemaError("c_init must be [B, K, N] matching unique_tensor [B, K]")
+    nT = (L + _lib.TILE_T - 1) // _lib.TILE_T
+    tile_state = torch.empty(B, nT, K, N, dtype=torch.float32, device=x.device)
+    tok_state = torch.empty(B, L, N, dtype=torch.float32, device=x.device)
+    kcount = torch.empty(B, dtype=torch.int32, device=x.device)
+    ws = _workspace(lib.mbema_tile_states_workspace_bytes(B, L), x.device)
+    flags = _lib.FLAG_CBASE_EXTRA_DECAY if _OPTIONS["cbase_extra_decay"] else 0
+    rc = lib.mbema_tile_states(_ptr(x), _ptr(unique), _ptr(rhos), _ptr(c_init), _ptr(tile_state), _ptr(tok_state),
+                               _ptr(kcount), B, L, N, K, flags, _ptr(ws), ws.numel(), _stream())
+    _lib.check(rc, "mbema_tile_states")
+    if seq_lens is not None:
+        seq_lens = seq_lens.to(torch.int32).contiguous()
+    return TileStates(tile_state, tok_state, kcount, seq_lens, unique, (B, L, K, N))
+
+
+def _build_unique_index(x, device=None):
+    """Per-row sorted unique tokens packed to the front, -1 padding; K_max = max(count, 16).
+    Drop-in for mathbrain/triton_flash_ema.py:475 (the fallback used when the data loader gives no slot list)."""
+    _require_cuda(x)
+    B, L = x.shape
+    xs, _ = torch.sort(x, dim=1)
+    first = torch.ones_like(xs, dtype=torch.bool)
+    first[:, 1:] = xs[:, 1:] != xs[:, :-1]
+    counts = first.sum(1)
+    k_max = max(int(counts.max().item()), 16)
+    rank = torch.cumsum(first.long(), 1) - 1
+    out = torch.full((B, max(k_max, L)), -1, dtype=x.dtype, device=x.device)
+    src = torch.where(first, xs, torch.full_like(xs, -1))
+    idx = torch.where(first, rank, torch.full_like(rank, max(k_max, L) - 1))
+    # non-first entries all write -1 into the last column, which is -1 unless the row has L distinct tokens,
+    # in which case no non-first entry exists
+    out.scatter_(1, idx, src)
+    return out[:, :k_max].contiguous(), k_max
+
+
+# ---------------------------------------------------------------------------------------------
+# flash-EMA attention
+# ---------------------------------------------------------------------------------------------
+def _flash_flags(use_silu):
+    f = _lib.FLAG_SILU if use_silu else 0
+    if _OPTIONS["inactive_mass"] == "listed_only":
+        f |= _lib.FLAG_LISTED_ONLY
+    return f
+
+
+class FlashEMAFunction(torch.autograd.Function):
+    """O = flash-EMA gated cross-attention; drop-in for mathbrain/triton_flash_ema.py:571.
+
+    forward(Q[B,H,L,hd], x[B,L], E_k_active[B,K_max,D], E_v_active[B,K_max,D], W_pe[N,D], rhos[N], V_total,
+            unique_tensor[B,K_max] (-1 = pad), K_max, C_bounds (from precompute_boundaries), use_silu, Br)
+    returns O[B,H,L,hd] float32; backward returns (dQ, None, dE_k, dE_v, dW_pe, None x 7).
+    """
+
+    @staticmethod
+    def forward(ctx, Q, x, E_k_active, E_v_active, W_pe, rhos, V_total, unique_tensor, K_max, C_bounds,
+                use_silu=True, Br=64):
+        _require_cuda(Q, x, E_k_active, E_v_active, W_pe, rhos, unique_tensor)
+        if not isinstance(C_bounds, TileStates):
+            raise _lib.MbemaError("C_bounds must come from mathbrain_b200.precompute_boundaries")
+        lib = _lib.load()
+        B, H, L, hd = Q.shape
+        D = H * hd
+        N = rhos.shape[0]
+        K = int(K_max)
+        if C_bounds.shape != (B, L, K, N):
+            raise _lib.MbemaError("C_bounds was built for (B,L,K,N)=%s, operator called with %s"
+                                  % (C_bounds.shape, (B, L, K, N)))
+        Qc = _f32_or_bf16(Q).contiguous()
+        Ek = _f32_or_bf16(E_k_active).contiguous()
+        Ev = _f32_or_bf16(E_v_active).contiguous()
+        if Ev.dtype != Ek.dtype:
+            Ev = Ev.to(Ek.dtype)
+        if Ek.shape != (B, K, D) or Ev.shape != (B, K, D):
+            raise _lib.MbemaError("E_k_active / E_v_active must be [B, K_max, D]")
+        W = W_pe.float().contiguous()
+        if W.shape != (N, D):
+            raise _lib.MbemaError("W_pe must be [N, D]")
+        rh = rhos.float().contiguous()
+        xx = x.long().contiguous()
+        O = torch.empty(B, H, L, hd, dtype=torch.float32, device=Q.device)
+        LSE = torch.empty(B, H, L, dtype=torch.float32, device=Q.device)
+        mode = _MODES[_OPTIONS["mode"]]
+        flags = _flash_flags(use_silu)
+        ws = _workspace(lib.mbema_flash_fwd_workspace_bytes(B, H, L, hd, N, K, mode), Q.device)
+        rc = lib.mbema_flash_fwd(_ptr(Qc), _dt(Qc), _ptr(xx), _ptr(Ek), _ptr(Ev), _dt(Ek), _ptr(W), _ptr(rh),
+                                 _ptr(C_bounds.unique), _ptr(C_bounds.tile_state), _ptr(C_bounds.tok_state),
+                                 _ptr(C_bounds.kcount), _ptr(C_bounds.seq_lens), _ptr(O), _ptr(LSE),
+                                 B, H, L, hd, N, K, int(V_total), flags, mode, _ptr(ws), ws.numel(), _stream())
+        _lib.check(rc, "mbema_flash_fwd")
+        ctx.save_for_backward(Qc, xx, Ek, Ev, W, rh, O, LSE)
+        ctx.handle = C_bounds
+        ctx.meta = (B, H, L, hd, N, K, int(V_total), flags, mode)
+        ctx.in_dtypes = (Q.dtype, E_k_active.dtype, E_v_active.dtype, W_pe.dtype)
+        return O
+
+    @staticmethod
+    def backward(ctx, dO):
+        lib = _lib.load()
+        Qc, xx, Ek, Ev, W, rh, O, LSE = ctx.saved_tensors
+        h = ctx.handle
+        B, H, L, hd, N, K, V_total, flags, mode = ctx.meta
+        D = H * hd
+        dOc = _f32_or_bf16(dO).contiguous()
+        dQ = torch.empty(B, H, L, hd, dtype=torch.float32, device=dO.device)
+        dEk = torch.empty(B, K, D, dtype=torch.float32, device=dO.device)
+        dEv = torch.empty(B, K, D, dtype=torch.float32, device=dO.device)
+        dW = torch.empty(N, D, dtype=torch.float32, device=dO.device)
+        ws = _workspace(lib.mbema_flash_bwd_workspace_bytes(B, H, L, hd, N, K, mode), dO.device)
+        rc = lib.mbema_flash_bwd(_ptr(Qc), _dt(Qc), _ptr(xx), _ptr(Ek), _ptr(Ev), _dt(Ek), _ptr(W), _ptr(rh),
+                                 _ptr(h.unique), _ptr(h.tile_state), _ptr(h.tok_state), _ptr(h.kcount),
+                                 _ptr(h.seq_lens), _ptr(O), _ptr(LSE), _ptr(dOc), _dt(dOc), _ptr(dQ), _ptr(dEk),
+                                 _ptr(dEv), _ptr(dW), B, H, L, hd, N, K, V_total, flags, mode, _ptr(ws), ws.numel(),
+                                 _stream())
+        _lib.check(rc, "mbema_flash_bwd")
+        qd, kd, vd, wd = ctx.in_dtypes
+        return (dQ.to(qd), None, dEk.to(kd), dEv.to(vd), dW.to(wd), None, None, None, None, None, None, None)
+
+
+# ---------------------------------------------------------------------------------------------
+# query gate + LayerNorm
+# ---------------------------------------------------------------------------------------------
+class FusedGatingFunction(torch.autograd.Function):
+    """x_ln = LayerNorm(x_q * gate(p_pre + bias)) * ln_w + ln_b, eps = 1e-5, float32 output.
+    Drop-in for mathbrain/triton_fused_gating.py:122; backward returns (dx_q, dp_pre, dbias, dln_w, dln_b, None)."""
+
+    @staticmethod
+    def forward(ctx, x_q, p_pre, bias, ln_w, ln_b, use_silu=True):
+        _require_cuda(x_q, p_pre, bias, ln_w, ln_b)
+        lib = _lib.load()
+        B, L, D = x_q.shape
+        xq = _f32_or_bf16(x_q).contiguous()
+        pp = _f32_or_bf16(p_pre).contiguous()
+        bb = bias.float().contiguous()
+        lw = ln_w.float().contiguous()
+        lb = ln_b.float().contiguous()
+        rows = B * L
+        y = torch.empty(B, L, D, dtype=torch.float32, device=x_q.device)
+        mu = torch.empty(rows, dtype=torch.float32, device=x_q.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x_q.device)
+        flags = _lib.FLAG_SILU if use_silu else 0
+        rc = lib.mbema_qgate_fwd(_ptr(xq), _dt(xq), _ptr(pp), _dt(pp), _ptr(bb), _ptr(lw), _ptr(lb), 1e-5, _ptr(y),
+                                 _lib.F32, _ptr(mu), _ptr(rstd), rows, D, flags, _stream())
+        _lib.check(rc, "mbema_qgate_fwd")
+        ctx.save_for_backward(xq, pp, bb, lw, mu, rstd)
+        ctx.flags = flags
+        ctx.in_dtypes = (x_q.dtype, p_pre.dtype, bias.dtype, ln_w.dtype, ln_b.dtype)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib.load()
+        xq, pp, bb, lw, mu, rstd = ctx.saved_tensors
+        B, L, D = xq.shape
+        rows = B * L
+        dyc = _f32_or_bf16(dy).contiguous()
+        dev = dy.device
+        dx = torch.empty(B, L, D, dtype=torch.float32, device=dev)
+        dp = torch.empty(B, L, D, dtype=torch.float32, device=dev)
+        dbias = torch.empty(D, dtype=torch.float32, device=dev)
+        dlw = torch.empty(D, dtype=torch.float32, device=dev)
+        dlb = torch.empty(D, dtype=torch.float32, device=dev)
+        ws = _workspace(lib.mbema_qgate_bwd_workspace_bytes(rows, D), dev)
+        rc = lib.mbema_qgate_bwd(_ptr(dyc), _dt(dyc), _ptr(xq), _dt(xq), _ptr(pp), _dt(pp), _ptr(bb), _ptr(lw),
+                                 _ptr(mu), _ptr(rstd), _ptr(dx), _ptr(dp), _ptr(dbias), _ptr(dlw), _ptr(dlb),
+                                 rows, D, ctx.flags, _ptr(ws), ws.numel(), _stream())
+        _lib.check(rc, "mbema_qgate_bwd")
+        d0, d1, d2, d3, d4 = ctx.in_dtypes
+        return dx.to(d0), dp.to(d1), dbias.to(d2), dlw.to(d3), dlb.to(d4), None
+
+
+def fused_apply_symmetric_query_gating(x_q, C_seq, pe_proj, ln_q, q_proj, use_silu=True):
+    """Q = q_proj(LN(x_q * gate(pe_proj(C_seq + 1)))); drop-in for mathbrain/triton_fused_gating.py:179.
+    The two projections are library GEMMs, as in the reference; the "+1" enters as the bias W.sum(1)."""
+    _require_cuda(x_q, C_seq)
+    bias_offset = pe_proj.weight.sum(dim=1)
+    p_pre = pe_proj(C_seq)
+    q_ln = FusedGatingFunction.apply(x_q, p_pre, bias_offset, ln_q.weight, ln_q.bias, use_silu)
+    return q_proj(q_ln)
