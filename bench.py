@@ -1,0 +1,361 @@
+"""Benchmark of the Per-Slot-EMA hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference] [--mode fp32|tc_bf16]
+
+One step = one pass of the hot path over one synthetic batch of the 46M configuration (B=56 chunks of T=512,
+d_model=512, 8 heads, N=64 EMA channels, 6 layers, vocabulary 50257):
+    query-side scan -> slot-state snapshots -> per layer [query gate + LayerNorm + q_proj, flash-EMA attention
+    forward, then the backward of both].
+Prints ONE JSON line (rank 0).  `value` is tokens/s with the batch resident in HBM; `e2e` repeats the measurement
+with the batch in pinned host memory, copied in every step, and a result scalar read back.
+For N > 1 every rank processes its own batch (weak scaling) and the parameter gradients of the path plus the
+vocabulary-sized slot-embedding gradient are all-reduced with NCCL inside the step.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CFG = dict(B=56, T=512, D=512, H=8, N=64, L=6, V=50257, min_hl=1024.0, max_hl=4096.0, max_prefix=8192, min_fill=64)
+METRIC = "flash_ema_fwd_bwd_tokens_per_s"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        j = json.load(open(p))
+        return dict(tflops=float(j.get("bf16_tflops_sustained", j.get("bf16_tflops"))), hbm=float(j["hbm_gbs"]),
+                    src="measured (MEASURED_PEAKS.json, sustained bf16)")
+    return dict(tflops=1400.0, hbm=6650.0, src="fallback")
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY,
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [s.strip() for s in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1])); mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            sm.sort()
+            out = {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        return out
+
+
+# --------------------------------------------------------------------------------------------- native arm
+class HotPath:
+    """Device-resident operands of the 6-layer hot path and the step function."""
+
+    def __init__(self, rank, dev, mode):
+        import mathbrain_b200 as mb
+        from mathbrain_b200 import synth
+        self.mb = mb
+        self.dev = dev
+        c = CFG
+        self.host = synth.make_chunk_batch(1000 + rank, c["B"], c["T"], c["N"], vocab=c["V"], max_prefix=c["max_prefix"],
+                                           min_fill=c["min_fill"], min_hl=c["min_hl"], max_hl=c["max_hl"])
+        self.K = self.host["K_max"]
+        self.pinned = {k: self.host[k].pin_memory() for k in ("x", "unique_slots", "pad_mask", "c_base", "fill")}
+        self.h2d_bytes = sum(t.numel() * t.element_size() for t in self.pinned.values())
+        self.rhos = self.host["rhos"].to(dev)
+        g = torch.Generator().manual_seed(2000 + rank)
+        B, T, D, H, N, K = c["B"], c["T"], c["D"], c["H"], c["N"], self.K
+        self.layers = []
+        for _ in range(c["L"]):
+            pe = torch.nn.Linear(N, D, bias=False)
+            ln = torch.nn.LayerNorm(D)
+            qp = torch.nn.Linear(D, D, bias=False)
+            with torch.no_grad():
+                pe.weight.copy_(torch.randn(D, N, generator=g) * 0.02)
+                qp.weight.copy_(torch.randn(D, D, generator=g) * 0.02)
+            lay = dict(pe=pe.to(dev), ln=ln.to(dev), qp=qp.to(dev),
+                       x_q=torch.randn(B, T, D, generator=g).to(dev).requires_grad_(True),
+                       E_k=(torch.randn(B, K, D, generator=g) * 0.02).to(torch.bfloat16).to(dev).requires_grad_(True),
+                       E_v=(torch.randn(B, K, D, generator=g) * 0.02).to(torch.bfloat16).to(dev).requires_grad_(True),
+                       dO=(torch.randn(B, H, T, D // H, generator=g) * 0.02).to(dev))
+            self.layers.append(lay)
+        self.params = [p for lay in self.layers for m in (lay["pe"], lay["ln"], lay["qp"]) for p in m.parameters()]
+        self.mode = mode
+        self.dist = False
+        self.dE_vocab = None
+        self.resident = {k: v.to(dev) for k, v in self.pinned.items()}
+        kb = self.host["pad_mask"].sum(1).double()
+        self.slot_steps = float((kb * c["T"]).sum())          # sum_b T * K_b   (all T steps are computed)
+        self.tokens = B * T
+        self.result = torch.zeros(1, device=dev)
+        self.result_host = torch.zeros(1).pin_memory()
+
+    def zero_grads(self):
+        for lay in self.layers:
+            lay["x_q"].grad = lay["E_k"].grad = lay["E_v"].grad = None
+        for p in self.params:
+            p.grad = None
+
+    def step(self, batch):
+        mb, c = self.mb, CFG
+        B, T, H, D = c["B"], c["T"], c["H"], c["D"]
+        x, unique_slots, pad_mask, c_base = batch["x"], batch["unique_slots"], batch["pad_mask"], batch["c_base"]
+        self.zero_grads()
+        with mb.options(mode=self.mode):
+            # the calls SlotTransformerLM.forward makes (reference mathbrain/model.py:157-183)
+            C_seq = mb.compute_query_ema_history(x, self.rhos, c["V"], c_base, unique_slots)
+            unique_tensor = unique_slots.clone()
+            unique_tensor[~pad_mask] = -1
+            handle = mb.precompute_boundaries(x, unique_tensor, self.rhos, 64, c_init=c_base)
+            acc = None
+            for lay in self.layers:
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    Q_t = mb.fused_apply_symmetric_query_gating(lay["x_q"], C_seq, lay["pe"], lay["ln"], lay["qp"], True)
+                    Q_mha = Q_t.view(B, T, H, D // H).transpose(1, 2).contiguous()
+                    W_pe_t = lay["pe"].weight.t().contiguous()
+                    O = mb.FlashEMAFunction.apply(Q_mha, x, lay["E_k"], lay["E_v"], W_pe_t, self.rhos, c["V"],
+                                                  unique_tensor, self.K, handle, True)
+                O.backward(lay["dO"])
+                s = O.detach().float().sum()
+                acc = s if acc is None else acc + s
+            if self.dist:
+                import torch.distributed as dist
+                if self.dE_vocab is None:
+                    self.dE_vocab = torch.zeros(c["V"], D, device=self.dev)
+                self.dE_vocab.zero_()
+                idx = unique_tensor.clamp_min(0).reshape(-1)
+                for lay in self.layers:
+                    gsum = (lay["E_k"].grad.float() + lay["E_v"].grad.float()) * pad_mask.unsqueeze(-1)
+                    self.dE_vocab.index_add_(0, idx, gsum.reshape(-1, D))
+                flat = torch.cat([p.grad.reshape(-1).float() for p in self.params])
+                dist.all_reduce(flat)
+                dist.all_reduce(self.dE_vocab)
+            self.result.copy_(acc.reshape(1))
+
+    def step_resident(self):
+        self.step(self.resident)
+
+    def step_e2e(self):
+        batch = {k: v.to(self.dev, non_blocking=True) for k, v in self.pinned.items()}
+        self.step(batch)
+        self.result_host.copy_(self.result, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return float(self.result_host[0])
+
+
+def timed(fn, steps, warmup, barrier):
+    for _ in range(warmup):
+        fn()
+    barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    barrier()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / 1000.0
+
+
+def cpu_baseline_sample(host, threads, steps_t=64):
+    """Oracle (CPU port of the reference's PyTorch path) on a bounded sample: sample 0 of the batch, its valid
+    slots, the first `steps_t` steps, ONE layer forward + backward.  Returns (seconds, tokens)."""
+    from oracle import ema_oracle as orc
+    c = CFG
+    torch.set_num_threads(threads)
+    kb = int(host["pad_mask"][0].sum())
+    g = torch.Generator().manual_seed(7)
+    H, D, N = c["H"], c["D"], c["N"]
+    x = host["x"][:1, :steps_t]
+    unique = host["unique_slots"][:1, :kb]
+    Q = torch.randn(1, H, steps_t, D // H, generator=g) * 0.02
+    Ek = torch.randn(1, kb, D, generator=g) * 0.02
+    Ev = torch.randn(1, kb, D, generator=g) * 0.02
+    W = torch.randn(N, D, generator=g) * 0.02
+    dO = torch.randn(1, H, steps_t, D // H, generator=g) * 0.02
+    t0 = time.perf_counter()
+    orc.query_scan(x, host["rhos"], c["V"], host["c_base"][:1, :kb], unique)
+    orc.flash_ema(Q, x, Ek, Ev, W, host["rhos"], c["V"], unique, c_base=host["c_base"][:1, :kb], dO=dO)
+    dt = time.perf_counter() - t0
+    return dt, steps_t, kb
+
+
+def run_reference(args, rank):
+    """Reference arm: the reference's CPU implementation of the path (its PyTorch restatement in oracle/; the
+    reference tree itself is not present on the GPU box) on all host threads, bounded sample per step."""
+    if rank != 0:
+        return
+    from mathbrain_b200 import synth
+    c = CFG
+    threads = os.cpu_count() or 1
+    host = synth.make_chunk_batch(1000, c["B"], c["T"], c["N"], vocab=c["V"], max_prefix=c["max_prefix"],
+                                  min_fill=c["min_fill"], min_hl=c["min_hl"], max_hl=c["max_hl"])
+    steps_t = 32
+    for _ in range(max(1, args.warmup)):
+        cpu_baseline_sample(host, threads, steps_t=8)
+    t0 = time.perf_counter()
+    tok = 0
+    for _ in range(args.steps):
+        _, n, kb = cpu_baseline_sample(host, threads, steps_t)
+        tok += n
+    dt = time.perf_counter() - t0
+    value = tok / (dt * c["L"])            # one layer was timed; the path has L layers per token
+    sample = "sample 0 of the batch (%d valid slots), first %d steps, 1 of %d layers fwd+bwd per step; tokens/s scaled by 1/%d" % (
+        kb, steps_t, c["L"], c["L"])
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1000.0,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "46M-config hot path (B=56,T=512,d=512,H=8,N=64,6 layers,V=50257), CPU sample"},
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--mode", default=os.environ.get("MBEMA_BENCH_MODE", "fp32"), choices=["fp32", "tc_bf16"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import mathbrain_b200 as mb
+    mb._lib.load()                      # fails loudly if the CUDA library is missing
+    assert torch.cuda.is_available(), "bench.py needs a GPU"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist_on = world > 1
+    if dist_on:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+        barrier = dist.barrier
+    else:
+        def barrier():
+            return None
+
+    hp = HotPath(rank, dev, args.mode)
+    hp.dist = dist_on
+    tel = mb.ops.telemetry
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    # device-resident measurement (telemetry on: launch counts + per-entry CUDA events on the launching stream)
+    for _ in range(args.warmup):
+        hp.step_resident()
+    tel.enabled = True
+    tel.reset()
+    secs = timed(hp.step_resident, args.steps, 0, barrier)
+    tel.enabled = False
+    launches = tel.launches
+    bwd_ms = tel.elapsed_ms("mbema_flash_bwd")
+    fwd_ms = tel.elapsed_ms("mbema_flash_fwd")
+    scan_ms = tel.elapsed_ms("mbema_query_scan")
+    gate_ms = tel.elapsed_ms("mbema_qgate_fwd") + tel.elapsed_ms("mbema_qgate_bwd")
+    clocks = sampler.stop() if rank == 0 else None
+    # end-to-end measurement: batch copied from pinned host memory each step, result scalar read back
+    secs_e2e = timed(hp.step_e2e, args.steps, 1, barrier)
+
+    t = torch.tensor([secs, secs_e2e], device=dev, dtype=torch.float64)
+    if dist_on:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    secs, secs_e2e = float(t[0]), float(t[1])
+
+    if rank == 0:
+        c = CFG
+        pk = peaks()
+        tokens = hp.tokens * world
+        flops_bwd = 4.0 * c["N"] * c["D"] * hp.slot_steps      # per launch (one layer), tensor flops only
+        flops_fwd = 2.0 * c["N"] * c["D"] * hp.slot_steps
+        avg_bwd = sum(bwd_ms) / max(1, len(bwd_ms)) / 1000.0
+        avg_fwd = sum(fwd_ms) / max(1, len(fwd_ms)) / 1000.0
+        ach = flops_bwd / avg_bwd / 1e12
+        line = {
+            "metric": METRIC, "value": tokens * args.steps / secs, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / args.steps * 1000.0,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32" if args.mode == "fp32" else "bf16", "data": "synthetic",
+            "config": {"workload": "46M-config hot path: scan + snapshots + 6 x (query gate, flash-EMA fwd, bwd of both)",
+                       "B_per_gpu": c["B"], "T": c["T"], "d_model": c["D"], "heads": c["H"], "N": c["N"],
+                       "layers": c["L"], "vocab": c["V"], "K_max": hp.K, "mean_slots": hp.slot_steps / (c["B"] * c["T"]),
+                       "mode": args.mode, "padding": "all T steps computed, as the reference does",
+                       "l2": "inputs larger than L2 (E_k/E_v are %.0f MB per layer)" % (2 * c["B"] * hp.K * c["D"] * 2 / 1e6),
+                       "parallelism": "dp%d" % world},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "e2e": {"value": tokens * args.steps / secs_e2e, "unit": "tokens/s", "h2d_bytes_per_step": hp.h2d_bytes,
+                    "d2h_bytes_per_step": 4},
+            "roofline": {"bound": "tensor", "kernel": "flash-EMA backward (one layer)", "achieved": ach,
+                         "peak": pk["tflops"], "unit": "TFLOP/s", "frac": ach / pk["tflops"], "traffic": None,
+                         "peak_source": pk["src"], "flops_per_launch": flops_bwd, "ms_per_launch": avg_bwd * 1000.0,
+                         "forward": {"achieved": flops_fwd / avg_fwd / 1e12, "ms_per_launch": avg_fwd * 1000.0},
+                         "scan_ms": sum(scan_ms) / max(1, len(scan_ms)), "gate_ms_per_step": sum(gate_ms) / args.steps},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            cpu_baseline_sample(hp.host, threads, steps_t=4)
+            dt, n, kb = cpu_baseline_sample(hp.host, threads, steps_t=48)
+            line["cpu_baseline"] = {"value": n / (dt * c["L"]), "unit": "tokens/s", "cores": threads, "kind": "port",
+                                    "sample": "oracle (PyTorch CPU port), sample 0 (%d slots), first %d steps, 1 of %d "
+                                              "layers fwd+bwd, scaled by 1/%d; %.1f s" % (kb, n, c["L"], c["L"], dt)}
+        print(json.dumps(line), flush=True)
+    if dist_on:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -102,6 +102,46 @@ def _workspace(nbytes, device):
     return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
 
 
+class _Telemetry:
+    """Optional bookkeeping for the benchmark: kernel-launch counts per entry point and CUDA-event pairs around
+    selected entry points (recorded on the launching stream)."""
+
+    # kernels launched by one call of each C entry point
+    KERNELS = {"mbema_query_scan": 2, "mbema_tile_states": 3, "mbema_qgate_fwd": 1, "mbema_qgate_bwd": 2,
+               "mbema_flash_fwd": 1, "mbema_flash_bwd": 2}
+
+    def __init__(self):
+        self.enabled = False
+        self.launches = 0
+        self.events = {}
+
+    def reset(self):
+        self.launches = 0
+        self.events = {}
+
+    def begin(self, name):
+        if not self.enabled:
+            return None
+        self.launches += self.KERNELS[name]
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(torch.cuda.current_stream())
+        return ev
+
+    def end(self, name, ev):
+        if ev is None:
+            return
+        ev1 = torch.cuda.Event(enable_timing=True)
+        ev1.record(torch.cuda.current_stream())
+        self.events.setdefault(name, []).append((ev, ev1))
+
+    def elapsed_ms(self, name):
+        """Per-call device times (ms) of an entry point; call after a synchronize."""
+        return [a.elapsed_time(b) for a, b in self.events.get(name, [])]
+
+
+telemetry = _Telemetry()
+
+
 # ---------------------------------------------------------------------------------------------
 # query-side scan
 # ---------------------------------------------------------------------------------------------
@@ -132,8 +172,10 @@ def compute_query_ema_history(x, rhos, vocab_size, c_init=None, c_init_keys=None
     C_seq = torch.empty(B, L, N, dtype=torch.float32, device=x.device)
     ws = _workspace(lib.mbema_query_scan_workspace_bytes(B, L), x.device)
     flags = 0
+    _ev = telemetry.begin("mbema_query_scan")
     rc = lib.mbema_query_scan(_ptr(x), _ptr(rhos), _ptr(c_init), _ptr(c_init_keys), _ptr(doc_ids), _ptr(C_seq),
                               B, L, N, K, flags, _ptr(ws), ws.numel(), _stream())
+    telemetry.end("mbema_query_scan", _ev)
     _lib.check(rc, "mbema_query_scan")
     return C_seq
 
@@ -181,8 +223,10 @@ def precompute_boundaries(x, unique_tensor, rhos, Br, c_init=None, doc_ids=None,
     kcount = torch.empty(B, dtype=torch.int32, device=x.device)
     ws = _workspace(lib.mbema_tile_states_workspace_bytes(B, L), x.device)
     flags = _lib.FLAG_CBASE_EXTRA_DECAY if _OPTIONS["cbase_extra_decay"] else 0
+    _ev = telemetry.begin("mbema_tile_states")
     rc = lib.mbema_tile_states(_ptr(x), _ptr(unique), _ptr(rhos), _ptr(c_init), _ptr(tile_state), _ptr(tok_state),
                                _ptr(kcount), B, L, N, K, flags, _ptr(ws), ws.numel(), _stream())
+    telemetry.end("mbema_tile_states", _ev)
     _lib.check(rc, "mbema_tile_states")
     if seq_lens is not None:
         seq_lens = seq_lens.to(torch.int32).contiguous()
@@ -258,10 +302,12 @@ class FlashEMAFunction(torch.autograd.Function):
         mode = _MODES[_OPTIONS["mode"]]
         flags = _flash_flags(use_silu)
         ws = _workspace(lib.mbema_flash_fwd_workspace_bytes(B, H, L, hd, N, K, mode), Q.device)
+        _ev = telemetry.begin("mbema_flash_fwd")
         rc = lib.mbema_flash_fwd(_ptr(Qc), _dt(Qc), _ptr(xx), _ptr(Ek), _ptr(Ev), _dt(Ek), _ptr(W), _ptr(rh),
                                  _ptr(C_bounds.unique), _ptr(C_bounds.tile_state), _ptr(C_bounds.tok_state),
                                  _ptr(C_bounds.kcount), _ptr(C_bounds.seq_lens), _ptr(O), _ptr(LSE),
                                  B, H, L, hd, N, K, int(V_total), flags, mode, _ptr(ws), ws.numel(), _stream())
+        telemetry.end("mbema_flash_fwd", _ev)
         _lib.check(rc, "mbema_flash_fwd")
         ctx.save_for_backward(Qc, xx, Ek, Ev, W, rh, O, LSE)
         ctx.handle = C_bounds
@@ -282,11 +328,13 @@ class FlashEMAFunction(torch.autograd.Function):
         dEv = torch.empty(B, K, D, dtype=torch.float32, device=dO.device)
         dW = torch.empty(N, D, dtype=torch.float32, device=dO.device)
         ws = _workspace(lib.mbema_flash_bwd_workspace_bytes(B, H, L, hd, N, K, mode), dO.device)
+        _ev = telemetry.begin("mbema_flash_bwd")
         rc = lib.mbema_flash_bwd(_ptr(Qc), _dt(Qc), _ptr(xx), _ptr(Ek), _ptr(Ev), _dt(Ek), _ptr(W), _ptr(rh),
                                  _ptr(h.unique), _ptr(h.tile_state), _ptr(h.tok_state), _ptr(h.kcount),
                                  _ptr(h.seq_lens), _ptr(O), _ptr(LSE), _ptr(dOc), _dt(dOc), _ptr(dQ), _ptr(dEk),
                                  _ptr(dEv), _ptr(dW), B, H, L, hd, N, K, V_total, flags, mode, _ptr(ws), ws.numel(),
                                  _stream())
+        telemetry.end("mbema_flash_bwd", _ev)
         _lib.check(rc, "mbema_flash_bwd")
         qd, kd, vd, wd = ctx.in_dtypes
         return (dQ.to(qd), None, dEk.to(kd), dEv.to(vd), dW.to(wd), None, None, None, None, None, None, None)
@@ -314,8 +362,10 @@ class FusedGatingFunction(torch.autograd.Function):
         mu = torch.empty(rows, dtype=torch.float32, device=x_q.device)
         rstd = torch.empty(rows, dtype=torch.float32, device=x_q.device)
         flags = _lib.FLAG_SILU if use_silu else 0
+        _ev = telemetry.begin("mbema_qgate_fwd")
         rc = lib.mbema_qgate_fwd(_ptr(xq), _dt(xq), _ptr(pp), _dt(pp), _ptr(bb), _ptr(lw), _ptr(lb), 1e-5, _ptr(y),
                                  _lib.F32, _ptr(mu), _ptr(rstd), rows, D, flags, _stream())
+        telemetry.end("mbema_qgate_fwd", _ev)
         _lib.check(rc, "mbema_qgate_fwd")
         ctx.save_for_backward(xq, pp, bb, lw, mu, rstd)
         ctx.flags = flags
@@ -336,9 +386,11 @@ class FusedGatingFunction(torch.autograd.Function):
         dlw = torch.empty(D, dtype=torch.float32, device=dev)
         dlb = torch.empty(D, dtype=torch.float32, device=dev)
         ws = _workspace(lib.mbema_qgate_bwd_workspace_bytes(rows, D), dev)
+        _ev = telemetry.begin("mbema_qgate_bwd")
         rc = lib.mbema_qgate_bwd(_ptr(dyc), _dt(dyc), _ptr(xq), _dt(xq), _ptr(pp), _dt(pp), _ptr(bb), _ptr(lw),
                                  _ptr(mu), _ptr(rstd), _ptr(dx), _ptr(dp), _ptr(dbias), _ptr(dlw), _ptr(dlb),
                                  rows, D, ctx.flags, _ptr(ws), ws.numel(), _stream())
+        telemetry.end("mbema_qgate_bwd", _ev)
         _lib.check(rc, "mbema_qgate_bwd")
         d0, d1, d2, d3, d4 = ctx.in_dtypes
         return dx.to(d0), dp.to(d1), dbias.to(d2), dlw.to(d3), dlb.to(d4), None
