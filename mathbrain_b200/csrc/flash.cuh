@@ -25,4 +25,9 @@ int flash_fwd_simt(const FlashArgs& a, cudaStream_t st);
 size_t flash_bwd_simt_ws(int64_t B, int64_t H, int64_t T, int64_t N);
 int flash_bwd_simt(FlashArgs a, float* dW, void* ws, cudaStream_t st);
 
+// tensor-core (tcgen05) path
+bool flash_tc_supported(int H, int N, int K);
+size_t flash_fwd_tc_ws();
+int flash_fwd_tc(const FlashArgs& a, void* ws, cudaStream_t st);
+
 }  // namespace mbema

@@ -8,7 +8,8 @@ static bool dt_ok(int dt) { return dt == MBEMA_F32 || dt == MBEMA_BF16; }
 static int flash_check(int64_t B, int64_t H, int64_t T, int64_t hd, int64_t N, int64_t K, int mode) {
     if (B < 0 || H < 1 || T < 1 || N < 1 || K < 1) return MBEMA_ERR_SHAPE;
     if (hd != 64 || N > 128 || T > 8192 || B > 65535 || H > 65535) return MBEMA_ERR_UNSUPPORTED;
-    if (mode != MBEMA_MODE_FP32) return MBEMA_ERR_UNSUPPORTED;
+    if (mode != MBEMA_MODE_FP32 && mode != MBEMA_MODE_TC_BF16) return MBEMA_ERR_UNSUPPORTED;
+    if (mode == MBEMA_MODE_TC_BF16 && !flash_tc_supported((int)H, (int)N, (int)K)) return MBEMA_ERR_UNSUPPORTED;
     return MBEMA_OK;
 }
 
@@ -38,7 +39,6 @@ extern "C" int mbema_flash_fwd(const void* Q, int q_dtype, const int64_t* x, con
                                const int32_t* seq_lens, float* O, float* LSE, int64_t B, int64_t H, int64_t T,
                                int64_t hd, int64_t N, int64_t K, int64_t V_total, int flags, int mode,
                                void* workspace, size_t workspace_bytes, void* stream) {
-    (void)workspace; (void)workspace_bytes;
     int rc = flash_check(B, H, T, hd, N, K, mode);
     if (rc) return rc;
     if (B == 0) return MBEMA_OK;
@@ -49,6 +49,11 @@ extern "C" int mbema_flash_fwd(const void* Q, int q_dtype, const int64_t* x, con
     FlashArgs a = pack(Q, q_dtype, x, E_k, E_v, e_dtype, W_pe, rhos, unique, tile_state, tok_state, kcount, seq_lens,
                        B, H, T, N, K, V_total, flags);
     a.O = O; a.LSE = LSE;
+    if (mode == MBEMA_MODE_TC_BF16) {
+        if (!workspace) return MBEMA_ERR_NULL;
+        if (workspace_bytes < flash_fwd_tc_ws()) return MBEMA_ERR_WORKSPACE;
+        return flash_fwd_tc(a, workspace, (cudaStream_t)stream);
+    }
     return flash_fwd_simt(a, (cudaStream_t)stream);
 }
 

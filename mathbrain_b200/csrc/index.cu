@@ -4,7 +4,9 @@
 // time axis of every sample is first regrouped by token: one CTA per sample sorts (token, t) pairs in
 // shared memory (bitonic network), which turns every token's occurrences into one contiguous, time-ordered
 // "chain".  A warp then walks a chain with the N channels spread over its lanes (coalesced 4*N-byte rows),
-// carrying the fp32 state in registers:  c_t = (c_s + 1) * rho^(t - s).  No vocabulary-sized scratch is
+// carrying the fp32 state in registers:  c_t = (c_s + 1) * rho^(t - s).  The power is evaluated in double
+// precision and rounded once: a token repeated at every step turns any bias of rho^1 into a state error
+// amplified by 1 / (1 - rho).  No vocabulary-sized scratch is
 // touched (the reference fills [B, V+1, N] floats per call, mathbrain/triton_ema_query.py:141-143).
 #include <math.h>
 
@@ -155,12 +157,13 @@ k_chain_scan(IndexWs w, const float* __restrict__ rhos, const float* __restrict_
     const int j1 = (c + 1 < nch) ? ch_off[c + 1] : T;
     const int sd = w.seed[(size_t)b * T + j0];
 
-    float l2r[4], u[4];
+    double l2r[4];
+    float u[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         int n = lane + 32 * i;
         float r = (n < N) ? rhos[n] : 1.0f;
-        l2r[i] = log2f(r);
+        l2r[i] = log2((double)r);
         u[i] = 0.0f;
         if (sd != NO_SEED && n < N && c_init != nullptr) {
             u[i] = c_init[((size_t)b * K + sd) * N + n];
@@ -178,11 +181,11 @@ k_chain_scan(IndexWs w, const float* __restrict__ rhos, const float* __restrict_
             if (has && d != last_doc) keep = false;
             last_doc = d;
         }
-        const float dt = (float)(t - s_ref);
+        const double dt = (double)(t - s_ref);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             int n = lane + 32 * i;
-            float cval = keep ? u[i] * exp2f(dt * l2r[i]) : 0.0f;
+            float cval = keep ? u[i] * (float)exp2(dt * l2r[i]) : 0.0f;
             if (n < N) out[((size_t)b * T + t) * N + n] = cval;
             u[i] = cval + 1.0f;
         }
@@ -218,12 +221,13 @@ k_tile_states(IndexWs w, const int64_t* __restrict__ unique, const float* __rest
         if (s_tok[m] < key) l = m + 1; else r = m;
     }
     int j = l;
-    float l2r[4], u[4];
+    double l2r[4];
+    float u[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         int n = lane + 32 * i;
         float rr = (n < N) ? rhos[n] : 1.0f;
-        l2r[i] = log2f(rr);
+        l2r[i] = log2((double)rr);
         u[i] = 0.0f;
         if (c_base != nullptr && n < N) {
             u[i] = c_base[((size_t)b * K + k) * N + n];
@@ -235,17 +239,17 @@ k_tile_states(IndexWs w, const int64_t* __restrict__ unique, const float* __rest
         const int t0 = tile * MBEMA_TILE_T;
         while (j < T && s_tok[j] == key && s_pos[j] < t0) {
             const int s = s_pos[j];
-            const float dt = (float)(s - s_ref);
+            const double dt = (double)(s - s_ref);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) u[i] = u[i] * exp2f(dt * l2r[i]) + 1.0f;
+            for (int i = 0; i < 4; ++i) u[i] = u[i] * (float)exp2(dt * l2r[i]) + 1.0f;
             s_ref = s;
             ++j;
         }
-        const float dt = (float)(t0 - s_ref);
+        const double dt = (double)(t0 - s_ref);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             int n = lane + 32 * i;
-            if (n < N) out[(size_t)tile * K * N + n] = u[i] * exp2f(dt * l2r[i]);
+            if (n < N) out[(size_t)tile * K * N + n] = u[i] * (float)exp2(dt * l2r[i]);
         }
     }
 }

@@ -141,6 +141,17 @@ class _Telemetry:
 
 telemetry = _Telemetry()
 
+# workspace of the most recent tensor-core attention call; its first int32 is the kernel's status word
+_last_tc_workspace = None
+
+
+def device_status():
+    """Status word of the most recent tensor-core attention kernel (synchronises): 0 = ok, 1 = a bounded wait
+    inside the kernel expired (the results of that call are invalid)."""
+    if _last_tc_workspace is None:
+        return 0
+    return int(_last_tc_workspace[:4].view(torch.int32).item())
+
 
 # ---------------------------------------------------------------------------------------------
 # query-side scan
@@ -309,6 +320,9 @@ class FlashEMAFunction(torch.autograd.Function):
                                  B, H, L, hd, N, K, int(V_total), flags, mode, _ptr(ws), ws.numel(), _stream())
         telemetry.end("mbema_flash_fwd", _ev)
         _lib.check(rc, "mbema_flash_fwd")
+        if mode == _lib.MODE_TC_BF16:
+            global _last_tc_workspace
+            _last_tc_workspace = ws
         ctx.save_for_backward(Qc, xx, Ek, Ev, W, rh, O, LSE)
         ctx.handle = C_bounds
         ctx.meta = (B, H, L, hd, N, K, int(V_total), flags, mode)

@@ -1,0 +1,77 @@
+"""Tensor-core (tcgen05) attention path against the fp32 oracle; bf16 tolerance 2e-2 (norm-wise relative)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ema_oracle as orc
+from helpers import rel_err
+from test_gpu_parity import make_case, oracle_flash, run_flash, compare_all, cu, TOL_BF16
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def mb():
+    import mathbrain_b200 as m
+    m._lib.load()
+    m.set_options(inactive_mass="full_V", cbase_extra_decay=False, mode="fp32")
+    return m
+
+
+def run_tc(mb, inp, c_base=None, seq_lens=None, dtype=torch.bfloat16, with_grad=True, **opt):
+    with mb.options(mode="tc_bf16", **opt):
+        out = run_flash(mb, inp, c_base, seq_lens=seq_lens, dtype=dtype, with_grad=with_grad)
+    assert mb.device_status() == 0
+    return out
+
+
+@pytest.mark.parametrize("T,H,bursty,vocab", [(64, 2, False, 400), (200, 2, True, 30), (384, 4, False, 2000)])
+def test_tc_forward_vs_oracle(mb, T, H, bursty, vocab):
+    inp, c_base, _ = make_case(300 + T, B=2, T=T, N=64, H=H, vocab=vocab, max_prefix=150, min_hl=1.0, max_hl=300.0,
+                               bursty=bursty)
+    out = run_tc(mb, inp, c_base, with_grad=False)
+    ref = orc.flash_ema(inp["Q"], inp["x"], inp["E_k"], inp["E_v"], inp["W_pe"], inp["rhos"], inp["V"], inp["unique"],
+                        c_base=c_base)
+    assert rel_err(out["O"], ref["O"]) < TOL_BF16
+    # against the oracle computing the gate product with bf16-rounded operands the agreement is much tighter
+    q16 = lambda t: t.to(torch.bfloat16).float()
+    ref16 = orc.flash_ema(q16(inp["Q"]), inp["x"], q16(inp["E_k"]), q16(inp["E_v"]), inp["W_pe"], inp["rhos"], inp["V"],
+                          inp["unique"], c_base=c_base, round_bf16=True)
+    assert rel_err(out["O"], ref16["O"]) < 3e-3
+
+
+def test_tc_forward_backward_config1_shape(mb):
+    from mathbrain_b200 import synth
+    rng = np.random.Generator(np.random.PCG64(0))
+    x = torch.from_numpy(np.stack([synth.Zipf().draw(rng, 128) for _ in range(2)]))
+    unique, K = orc.build_unique_index(x)
+    g = torch.Generator().manual_seed(0)
+    E = torch.randn(synth.VOCAB, 512, generator=g) * 0.02
+    Ea = E[unique.clamp_min(0)] * (unique >= 0).unsqueeze(-1)
+    inp = dict(x=x, unique=unique, rhos=synth.make_rhos(64), V=synth.VOCAB, use_silu=True,
+               Q=torch.randn(2, 8, 128, 64, generator=g) * 0.02, E_k=Ea, E_v=Ea.clone(),
+               W_pe=torch.randn(64, 512, generator=g) * 0.02, dO=torch.randn(2, 8, 128, 64, generator=g) * 0.02)
+    ref = oracle_flash(inp, None)
+    out = run_tc(mb, inp)
+    compare_all(out, ref, TOL_BF16)
+
+
+def test_tc_semantic_switches_and_seq_lens(mb):
+    inp, c_base, fill = make_case(41, B=3, T=300, N=64, H=2, vocab=300, max_prefix=100, min_hl=2.0, max_hl=100.0,
+                                  min_fill=20)
+    inp["dO"] = inp["dO"].clone()
+    for b, n in enumerate(fill.tolist()):
+        inp["dO"][b, :, n:] = 0
+    out = run_tc(mb, inp, c_base, seq_lens=fill, inactive_mass="listed_only", cbase_extra_decay=True)
+    ref = oracle_flash(inp, c_base, inactive_mass="listed_only", extra_decay=True)
+    compare_all(out, ref, TOL_BF16, rows=fill.tolist())
+    inp["use_silu"] = False
+    out = run_tc(mb, inp, c_base)
+    ref = oracle_flash(inp, c_base)
+    compare_all(out, ref, TOL_BF16)
+
+
+def test_tc_unsupported_shape_is_refused(mb):
+    inp, c_base, _ = make_case(5, B=1, T=64, N=16, H=2, vocab=100, max_prefix=10, min_hl=2.0, max_hl=30.0)
+    with pytest.raises(mb._lib.MbemaError):
+        run_tc(mb, inp, c_base, with_grad=False)
