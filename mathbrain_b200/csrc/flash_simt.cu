@@ -19,6 +19,8 @@ static constexpr int FS_HD = 64;
 static constexpr int FS_ZLD = 72;            // padded row length of the backward staging tiles
 
 __device__ __forceinline__ int zcol(int c) { return c + ((c >> 5) << 2); }
+// shared-memory regions start on 16-byte boundaries (float4 accesses) for every N
+__host__ __device__ inline int round4(int v) { return (v + 3) & ~3; }
 
 
 // Row state source for slot `key`: returns the step offset s (within the tile) of the last occurrence of the
@@ -65,8 +67,8 @@ __global__ void __launch_bounds__(FS_THREADS) k_flash_fwd_simt(FlashArgs a) {
     const int N = a.N, ldA = N + 1;
     float* W_sh = smem;
     float* A_sh = W_sh + N * FS_HD;
-    float* l2r_sh = A_sh + FS_ROWS * ldA;
-    int* tok_sh = reinterpret_cast<int*>(l2r_sh + N);
+    float* l2r_sh = A_sh + round4(FS_ROWS * ldA);
+    int* tok_sh = reinterpret_cast<int*>(l2r_sh + round4(N));
 
     const int half = blockIdx.x & 1, tile = blockIdx.x >> 1;
     const int h = blockIdx.y, b = blockIdx.z;
@@ -178,8 +180,8 @@ __global__ void __launch_bounds__(FS_THREADS) k_flash_bwd_simt(FlashArgs a) {
     const int N = a.N, ldA = N + 1;
     float* W_sh = smem;
     float* A_sh = W_sh + N * FS_HD;
-    float* l2r_sh = A_sh + FS_ROWS * ldA;
-    int* tok_sh = reinterpret_cast<int*>(l2r_sh + N);
+    float* l2r_sh = A_sh + round4(FS_ROWS * ldA);
+    int* tok_sh = reinterpret_cast<int*>(l2r_sh + round4(N));
     float* Zk = reinterpret_cast<float*>(tok_sh + MBEMA_TILE_T);
     float* Zv = Zk + FS_ROWS * FS_ZLD;
     float* Zp = Zv + FS_ROWS * FS_ZLD;
@@ -375,7 +377,7 @@ __global__ void k_flash_dw_reduce(const float* __restrict__ part, float* __restr
     dW[(size_t)n * D + col] = s;
 }
 
-static size_t fs_smem_fwd(int N) { return ((size_t)N * FS_HD + (size_t)FS_ROWS * (N + 1) + N + MBEMA_TILE_T) * 4; }
+static size_t fs_smem_fwd(int N) { return ((size_t)N * FS_HD + (size_t)round4(FS_ROWS * (N + 1)) + round4(N) + MBEMA_TILE_T) * 4; }
 static size_t fs_smem_bwd(int N) { return fs_smem_fwd(N) + 3 * (size_t)FS_ROWS * FS_ZLD * 4; }
 
 int flash_fwd_simt(const FlashArgs& a, cudaStream_t st) {

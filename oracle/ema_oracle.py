@@ -118,6 +118,7 @@ def memory_states(x, unique, rhos, c_base=None, extra_decay=False, dtype=torch.f
     if extra_decay:
         C = C * rhos
     valid = unique >= 0
+    C = C * valid.unsqueeze(-1)          # entries that are not slots carry no state
     for t in range(L):
         M[:, t] = C
         match = ((unique == x[:, t:t + 1]) & valid).to(dtype)
