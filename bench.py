@@ -185,6 +185,42 @@ class HotPath:
         return float(self.result_host[0])
 
 
+def profile_case(args):
+    """Small single-kernel workload for profiler captures: B=16 chunks of the 46M configuration, a few launches of
+    the attention forward (and backward) of ONE layer.  Prints per-launch device times; no benchmark line."""
+    import mathbrain_b200 as mb
+    from mathbrain_b200 import synth
+    c = CFG
+    dev = torch.device("cuda", 0)
+    B = 16
+    host = synth.make_chunk_batch(1000, B, c["T"], c["N"], vocab=c["V"], max_prefix=c["max_prefix"],
+                                  min_fill=c["min_fill"], min_hl=c["min_hl"], max_hl=c["max_hl"])
+    K = host["K_max"]
+    w = synth.make_layer_weights(1, B, K, c["D"], c["N"], c["T"], c["H"], dtype=torch.bfloat16)
+    x = host["x"].to(dev)
+    unique = host["unique_slots"].clone()
+    unique[~host["pad_mask"]] = -1
+    unique = unique.to(dev)
+    rhos = host["rhos"].to(dev)
+    with mb.options(mode=args.mode):
+        handle = mb.precompute_boundaries(x, unique, rhos, 64, c_init=host["c_base"].to(dev))
+        Q = w["Q"].to(dev).requires_grad_(True)
+        Ek = w["E_k"].to(dev).requires_grad_(True)
+        Ev = w["E_v"].to(dev).requires_grad_(True)
+        W = w["W_pe"].to(dev).requires_grad_(True)
+        tel = mb.ops.telemetry
+        tel.enabled = True
+        for _ in range(3):
+            O = mb.FlashEMAFunction.apply(Q, x, Ek, Ev, W, rhos, c["V"], unique, K, handle, True)
+            if args.profile_case == "bwd":
+                O.backward(w["dO"].to(dev).float())
+        torch.cuda.synchronize()
+    slot_steps = float(host["pad_mask"].sum(1).double().sum() * c["T"])
+    print(json.dumps({"profile_case": args.profile_case, "mode": args.mode, "B": B, "K_max": K,
+                      "slot_steps": slot_steps, "fwd_ms": tel.elapsed_ms("mbema_flash_fwd"),
+                      "bwd_ms": tel.elapsed_ms("mbema_flash_bwd"), "status": mb.device_status()}))
+
+
 def timed(fn, steps, warmup, barrier):
     for _ in range(warmup):
         fn()
@@ -262,6 +298,8 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--mode", default=os.environ.get("MBEMA_BENCH_MODE", "fp32"), choices=["fp32", "tc_bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd"],
+                    help="run a small one-layer attention workload (for ncu captures) instead of the benchmark")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
 
@@ -274,6 +312,9 @@ def main():
 
     import mathbrain_b200 as mb
     mb._lib.load()                      # fails loudly if the CUDA library is missing
+    if args.profile_case:
+        profile_case(args)
+        return
     assert torch.cuda.is_available(), "bench.py needs a GPU"
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)

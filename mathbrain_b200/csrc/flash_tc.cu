@@ -1,15 +1,18 @@
 // Flash-EMA gated cross-attention on the Blackwell tensor cores (MBEMA_MODE_TC_BF16), forward.
 //
 // One CTA owns (sample b, a 128-step time tile, a pair of heads) and loops over the sample's valid slots.
-// For slot k the 128 x N state tile A[t, :] = M_t[k, :] (bf16, 128-byte-swizzled K-major rows) is rebuilt in
-// shared memory from the tile-start snapshot and a table of decay powers; one elected thread issues
-//     pre[128 x 128] = A[128 x N] @ (W_pe[:, 2 heads])            tcgen05.mma, fp32 accumulators in TMEM
-// and the eight warps (a warpgroup per head; a thread per time step) read their 64 accumulator columns with
-// tcgen05.ld and fuse SiLU, K = E_k*gate, V = E_v*gate, the score, the online softmax and the P.V update, all
-// thread-local.  A tiles and TMEM accumulators are double buffered: while the epilogue of slot i runs, the
-// tensor core already works on slot i+1.  Hand-offs go through mbarriers with bounded waits.
-// The CTA has exactly 8 warps (registers are allocated to warps in groups of four, and a thread needs ~230 of
-// them for q, the output row and 64 accumulator columns); thread 0 doubles as the UMMA issuer.
+// Warp-specialised, 12 warps:
+//   * producer warpgroup (warps 8-11, one thread per time step): for slot k rebuilds the 128 x N state tile
+//     A[t, :] = M_t[k, :] (bf16, 128-byte-swizzled K-major rows) in shared memory from the tile-start snapshot and
+//     a table of decay powers, stages the slot's E_k / E_v rows as fp32, and one of its threads issues
+//         pre[128 x 128] = A[128 x N] @ (W_pe[:, 2 heads])        tcgen05.mma, fp32 accumulators in TMEM;
+//   * two epilogue warpgroups (a warpgroup per head, a thread per time step) read their 64 accumulator columns
+//     with tcgen05.ld and fuse SiLU, K = E_k*gate, V = E_v*gate, the score, the online softmax and the P.V update,
+//     all thread-local.
+// A tiles and TMEM accumulators are multi-buffered, so state generation and the tensor core run ahead of the
+// epilogue.  Registers are rebalanced with setmaxnreg (epilogue threads hold q, the output row and 64 accumulator
+// columns; the per-CTA total, 8*32*216 + 4*32*72, equals the launch allocation 384*168).  Hand-offs go through
+// mbarriers with bounded waits; nothing in here spins without a limit.
 #include "flash.cuh"
 #include "sm100_ptx.cuh"
 
@@ -23,27 +26,30 @@ static constexpr int HPC = 2;                  // heads per CTA
 static constexpr int HD = 64;
 static constexpr int EPI_WARPS = 4 * HPC;
 static constexpr int EPI_THREADS = 32 * EPI_WARPS;
-static constexpr int THREADS = EPI_THREADS;
+static constexpr int PROD_THREADS = 128;
+static constexpr int THREADS = EPI_THREADS + PROD_THREADS;
 static constexpr int ATOM_BYTES = TM * 128;        // one 128-row x 64-column bf16 swizzle atom
-static constexpr int E_STAGES = 8;                 // slot-embedding rows staged ahead (warps drift up to 4 slots apart)
-static constexpr int TMEM_COLS = 2 * HPC * HD;     // two accumulator buffers of HPC*64 fp32 columns
-static constexpr int MAX_SLOTS = 16384;
+static constexpr int NSTAGE = 3;                   // A-tile / accumulator / E-row pipeline depth
+static constexpr int ACC_COLS = HPC * HD;          // fp32 accumulator columns per stage
+static constexpr int TMEM_COLS = 512;              // power of two >= NSTAGE * ACC_COLS
+static constexpr int MAX_SLOTS = 8192;
 
 struct Smem {
     // offsets (bytes) into the dynamic shared memory block, base aligned to 1024
-    int a_off, b_off, r_off, e_off, tok_off, slot_off, bar_off, total;
+    int a_off, b_off, r_off, e_off, tok_off, slot_off, key_off, bar_off, total;
 };
 
 __host__ __device__ inline Smem smem_layout(int N, int K) {
     const int NK = N / 64;
     Smem s;
     int o = 0;
-    s.a_off = o; o += 2 * NK * ATOM_BYTES;
+    s.a_off = o; o += NSTAGE * NK * ATOM_BYTES;
     s.b_off = o; o += NK * ATOM_BYTES;
     s.r_off = o; o += TM * (N + 4) * 4;
-    s.e_off = o; o += E_STAGES * 2 * HPC * HD * 4;
+    s.e_off = o; o += NSTAGE * 2 * HPC * HD * 4;
     s.tok_off = o; o += TM * 4;
     s.slot_off = o; o += ((K * 2 + 15) / 16) * 16;
+    s.key_off = o; o += ((K * 4 + 15) / 16) * 16;
     s.bar_off = o; o += 128;
     s.total = o + 1024;   // slack for the 1024-byte alignment of the base
     return s;
@@ -55,13 +61,16 @@ __device__ __forceinline__ int sw128_off(int row, int col) {
 }
 
 struct Bars {
-    uint64_t a_full[2];
-    uint64_t acc_full[2];
-    uint64_t acc_empty[2];
+    uint64_t acc_full[NSTAGE];    // UMMAs of the stage done + E rows staged   (2 arrivals: commit, issuer)
+    uint64_t acc_empty[NSTAGE];   // every epilogue warp has read the stage's accumulators (EPI_WARPS arrivals)
     uint32_t tmem_base;
     int abort_flag;
     int n_slots;
 };
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 
 __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* status) {
     extern __shared__ unsigned char smem_raw[];
@@ -74,6 +83,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
     float* E_sh = reinterpret_cast<float*>(sm + L.e_off);
     int* tok_sh = reinterpret_cast<int*>(sm + L.tok_off);
     unsigned short* slot_sh = reinterpret_cast<unsigned short*>(sm + L.slot_off);
+    int* key_sh = reinterpret_cast<int*>(sm + L.key_off);
     Bars* bars = reinterpret_cast<Bars*>(sm + L.bar_off);
     volatile int* abort_flag = &bars->abort_flag;
 
@@ -82,57 +92,60 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
     const int D = a.H * HD;
     const int t0 = tile * TM;
     const int Lb = a.seq_lens ? min(max(a.seq_lens[b], 0), a.T) : a.T;
-    const int wg = warp >> 2;                       // head within the pair (epilogue warps)
-    const int row = (warp & 3) * 32 + lane;         // time step within the tile == TMEM lane
-    const int h = hp * HPC + wg;
+    const bool is_epi = warp < EPI_WARPS;
+    const int row = (warp & 3) * 32 + lane;         // time step within the tile (== TMEM lane for epilogue warps)
     const int t = t0 + row;
-    const size_t qoff = (((size_t)b * a.H + h) * a.T + t) * HD;
 
     if (t0 >= Lb) {   // whole tile beyond the valid length: define the outputs and leave (uniform per CTA)
-        if (t < a.T) {
+        if (is_epi && t < a.T) {
+            const int h = hp * HPC + (warp >> 2);
+            const size_t qo = (((size_t)b * a.H + h) * a.T + t) * HD;
 #pragma unroll
-            for (int i = 0; i < HD; i += 4) *reinterpret_cast<float4*>(a.O + qoff + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int i = 0; i < HD; i += 4) *reinterpret_cast<float4*>(a.O + qo + i) = make_float4(0.f, 0.f, 0.f, 0.f);
             a.LSE[((size_t)b * a.H + h) * a.T + t] = 0.f;
         }
         return;
     }
 
-    // ---------------------------------------------------------------- prologue
+    // ---------------------------------------------------------------- prologue (all 12 warps)
     if (tid == 0) {
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&bars->a_full[i], EPI_WARPS);
+        for (int i = 0; i < NSTAGE; ++i) {
             mbar_init(&bars->acc_full[i], 2);
             mbar_init(&bars->acc_empty[i], EPI_WARPS);
         }
-        bars->abort_flag = 0;
+        bars->abort_flag = *reinterpret_cast<volatile int*>(status);   // an earlier CTA already gave up: do nothing
         fence_barrier_init();
     }
-    if (warp == 0) {
+    if (warp == EPI_WARPS) {
         tmem_alloc(&bars->tmem_base, TMEM_COLS);
         tmem_relinquish();
     }
-    if (warp == 1) {
-        // ordered compaction of the valid slot indices
+    if (warp == EPI_WARPS + 1) {   // ordered compaction of the valid slots (index and key)
         int n = 0;
         for (int k0 = 0; k0 < a.K; k0 += 32) {
             const int k = k0 + lane;
-            const bool ok = (k < a.K) && (a.unique[(size_t)b * a.K + k] >= 0);
+            const long long kv = (k < a.K) ? a.unique[(size_t)b * a.K + k] : -1;
+            const bool ok = kv >= 0;
             const unsigned m = __ballot_sync(0xffffffffu, ok);
-            if (ok) slot_sh[n + __popc(m & ((1u << lane) - 1u))] = (unsigned short)k;
+            if (ok) {
+                const int pos = n + __popc(m & ((1u << lane) - 1u));
+                slot_sh[pos] = (unsigned short)k;
+                key_sh[pos] = (int)(kv & 0x7fffffffLL);
+            }
             n += __popc(m);
         }
         if (lane == 0) bars->n_slots = n;
     }
-    // B operand: rows = the pair's 128 output columns, K-major over n; 0.5 * W when the gate is SiLU (the
-    // epilogue evaluates SiLU(x) = h + h * tanh(h) with h = x / 2)
     {
+        // B operand: rows = the pair's 128 output columns, K-major over n; 0.5 * W when the gate is SiLU (the
+        // epilogue evaluates SiLU(x) = h + h * tanh(h) with h = x / 2)
         const float wscale = a.silu ? 0.5f : 1.0f;
         for (int i = tid; i < N * HPC * HD; i += THREADS) {
             const int n = i / (HPC * HD), dd = i % (HPC * HD);
             const float w = a.W[(size_t)n * D + hp * HPC * HD + dd] * wscale;
             *reinterpret_cast<__nv_bfloat16*>(B_sh + (n >> 6) * ATOM_BYTES + sw128_off(dd, n & 63)) = __float2bfloat16(w);
         }
-        for (int i = tid; i < TM * N; i += THREADS) {
+        for (int i = tid; i < TM * N; i += THREADS) {   // decay powers rho_n^r, r = 0..127
             const int r = i / N, n = i % N;
             R_sh[r * ldR + n] = exp2f((float)r * log2f(a.rhos[n]));
         }
@@ -146,165 +159,172 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = bars->tmem_base;
-    const int n_slots = bars->n_slots;
+    const int n_slots = bars->abort_flag ? 0 : bars->n_slots;
 
-    // ---------------------------------------------------------------- per-thread state: one time step of one head
-    const bool row_ok = t < Lb;
-    float q[HD], o[HD];
-#pragma unroll
-    for (int i = 0; i < HD; i += 4) {
-        float4 v = row_ok ? ld4_dyn_f32(a.Q, a.q_dt, qoff + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-        q[i] = v.x * 0.125f; q[i + 1] = v.y * 0.125f; q[i + 2] = v.z * 0.125f; q[i + 3] = v.w * 0.125f;
-        o[i] = o[i + 1] = o[i + 2] = o[i + 3] = 0.f;
-    }
-    const float rest = a.v_total - (float)a.kcount[b];
-    float m, l;
-    if (!a.listed_only && rest > 0.f) { m = 0.f; l = rest; } else { m = -INFINITY; l = 0.f; }
-    const int cc0 = wg * (N / (8 * HPC)), cc1 = cc0 + N / (8 * HPC);   // this warpgroup's 16-byte chunks of a row
-    const uint32_t idesc = umma_idesc_bf16(TM, HPC * HD, 0, 0);
-    const uint32_t a_base = smem_u32(A_sh), b_base = smem_u32(B_sh);
-
-    // Stage slot i: this thread's share of the bf16 state tile A (rows = time steps) and of the slot's E_k / E_v
-    // rows (converted to fp32), then signal "A full".
-    auto stage_slot = [&](int i) {
-        const int k = slot_sh[i];
-        const int key = (int)(a.unique[(size_t)b * a.K + k] & 0x7fffffffLL);
-        {
-            const int which = tid >> 7, col = tid & 127;     // 0: E_k, 1: E_v; column within the head pair
-            const float v = ld_dyn_f32(which ? a.Ev : a.Ek, a.e_dt, ((size_t)b * a.K + k) * D + hp * HPC * HD + col);
-            E_sh[((i % E_STAGES) * 2 + which) * HPC * HD + col] = v;
-        }
-        unsigned w[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) w[j] = __ballot_sync(0xffffffffu, tok_sh[32 * j + lane] == key);
+    if (!is_epi) {
+        // ============================================================ producer warpgroup: one thread per time step
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+        const uint32_t idesc = umma_idesc_bf16(TM, ACC_COLS, 0, 0);
+        const uint32_t a_base = smem_u32(A_sh), b_base = smem_u32(B_sh);
         const int wi = row >> 5, bi = row & 31;
-        int s = -1;
+        for (int i = 0; i < n_slots; ++i) {
+            const int st = i % NSTAGE, u = i / NSTAGE;
+            // stage st (A tile, E rows, accumulators) is free once the epilogue of slot i - NSTAGE has finished
+            if (i >= NSTAGE) mbar_wait(&bars->acc_empty[st], (uint32_t)((u - 1) & 1), abort_flag);
+            const int k = slot_sh[i];
+            const int key = key_sh[i];
+            // E_k / E_v rows of the slot for the head pair, as fp32: thread p handles column p of both
+            {
+                const size_t off = ((size_t)b * a.K + k) * D + hp * ACC_COLS + row;
+                float* dst = E_sh + st * 2 * ACC_COLS + row;
+                dst[0] = ld_dyn_f32(a.Ek, a.e_dt, off);
+                dst[ACC_COLS] = ld_dyn_f32(a.Ev, a.e_dt, off);
+            }
+            // last occurrence of the slot's token strictly before this row, inside the tile
+            int s = -1;
+            {
+                unsigned w[4];
 #pragma unroll
-        for (int j = 3; j >= 0; --j) {
-            unsigned mm = (j > wi) ? 0u : (j == wi ? (w[j] & ((1u << bi) - 1u)) : w[j]);
-            if (s < 0 && mm) s = j * 32 + 31 - __clz(mm);
-        }
-        const float* base;
-        float add;
-        int rr;
-        if (s >= 0) {   // restart from the token's own state at its last occurrence inside the tile
-            base = a.tok_state + ((size_t)b * a.T + t0 + s) * N;
-            add = 1.0f;
-            rr = row - s;
-        } else {        // plain decay of the tile-start snapshot
-            base = a.tile_state + (((size_t)b * a.nT + tile) * a.K + k) * N;
-            add = 0.0f;
-            rr = row;
-        }
-        const float* Rrow = R_sh + rr * ldR;
-        unsigned char* Abuf = A_sh + (i & 1) * NK * ATOM_BYTES;
-        for (int cc = cc0; cc < cc1; ++cc) {
-            const int n0 = cc * 8;
-            const float4 b0 = __ldg(reinterpret_cast<const float4*>(base + n0));
-            const float4 b1 = __ldg(reinterpret_cast<const float4*>(base + n0 + 4));
-            const float4 r0 = *reinterpret_cast<const float4*>(Rrow + n0);
-            const float4 r1 = *reinterpret_cast<const float4*>(Rrow + n0 + 4);
-            uint4 pk;
-            pk.x = pack_bf16x2((b0.x + add) * r0.x, (b0.y + add) * r0.y);
-            pk.y = pack_bf16x2((b0.z + add) * r0.z, (b0.w + add) * r0.w);
-            pk.z = pack_bf16x2((b1.x + add) * r1.x, (b1.y + add) * r1.y);
-            pk.w = pack_bf16x2((b1.z + add) * r1.z, (b1.w + add) * r1.w);
-            *reinterpret_cast<uint4*>(Abuf + (cc >> 3) * ATOM_BYTES + row * 128 + (((cc & 7) ^ (row & 7)) << 4)) = pk;
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->a_full[i & 1]);
-    };
-
-    // Thread 0 only: once every warp has staged slot i (and the accumulator buffer is free), issue its UMMAs.
-    auto issue_slot = [&](int i) {
-        const int buf = i & 1, u = i >> 1;
-        mbar_wait(&bars->a_full[buf], (uint32_t)(u & 1), abort_flag);
-        if (i >= 2) mbar_wait(&bars->acc_empty[buf], (uint32_t)((u - 1) & 1), abort_flag);
-        tc_fence_after_sync();
-        for (int atom = 0; atom < NK; ++atom) {
+                for (int j = 0; j < 4; ++j) w[j] = __ballot_sync(0xffffffffu, tok_sh[32 * j + lane] == key);
 #pragma unroll
-            for (int k16 = 0; k16 < 4; ++k16) {
-                const uint64_t adesc = umma_desc_k_sw128(a_base + (buf * NK + atom) * ATOM_BYTES + k16 * 32);
-                const uint64_t bdesc = umma_desc_k_sw128(b_base + atom * ATOM_BYTES + k16 * 32);
-                umma_bf16_ss(tmem_base + (uint32_t)(buf * HPC * HD), adesc, bdesc, idesc, (atom | k16) != 0 ? 1u : 0u);
+                for (int j = 3; j >= 0; --j) {
+                    unsigned mm = (j > wi) ? 0u : (j == wi ? (w[j] & ((1u << bi) - 1u)) : w[j]);
+                    if (s < 0 && mm) s = j * 32 + 31 - __clz(mm);
+                }
+            }
+            unsigned char* Arow = A_sh + st * NK * ATOM_BYTES + row * 128;
+            if (s >= 0) {   // restart from the token's own state at that occurrence (+1 for the occurrence itself)
+                const float* base = a.tok_state + ((size_t)b * a.T + t0 + s) * N;
+                const float* Rrow = R_sh + (row - s) * ldR;
+                for (int cc = 0; cc < N / 8; ++cc) {
+                    const int n0 = cc * 8;
+                    const float4 b0 = __ldg(reinterpret_cast<const float4*>(base + n0));
+                    const float4 b1 = __ldg(reinterpret_cast<const float4*>(base + n0 + 4));
+                    const float4 r0 = *reinterpret_cast<const float4*>(Rrow + n0);
+                    const float4 r1 = *reinterpret_cast<const float4*>(Rrow + n0 + 4);
+                    uint4 pk;
+                    pk.x = pack_bf16x2(fmaf(b0.x, r0.x, r0.x), fmaf(b0.y, r0.y, r0.y));
+                    pk.y = pack_bf16x2(fmaf(b0.z, r0.z, r0.z), fmaf(b0.w, r0.w, r0.w));
+                    pk.z = pack_bf16x2(fmaf(b1.x, r1.x, r1.x), fmaf(b1.y, r1.y, r1.y));
+                    pk.w = pack_bf16x2(fmaf(b1.z, r1.z, r1.z), fmaf(b1.w, r1.w, r1.w));
+                    *reinterpret_cast<uint4*>(Arow + (cc >> 3) * ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) = pk;
+                }
+            } else {        // plain decay of the tile-start snapshot
+                const float* base = a.tile_state + (((size_t)b * a.nT + tile) * a.K + k) * N;
+                const float* Rrow = R_sh + row * ldR;
+                for (int cc = 0; cc < N / 8; ++cc) {
+                    const int n0 = cc * 8;
+                    const float4 b0 = __ldg(reinterpret_cast<const float4*>(base + n0));
+                    const float4 b1 = __ldg(reinterpret_cast<const float4*>(base + n0 + 4));
+                    const float4 r0 = *reinterpret_cast<const float4*>(Rrow + n0);
+                    const float4 r1 = *reinterpret_cast<const float4*>(Rrow + n0 + 4);
+                    uint4 pk;
+                    pk.x = pack_bf16x2(b0.x * r0.x, b0.y * r0.y);
+                    pk.y = pack_bf16x2(b0.z * r0.z, b0.w * r0.w);
+                    pk.z = pack_bf16x2(b1.x * r1.x, b1.y * r1.y);
+                    pk.w = pack_bf16x2(b1.z * r1.z, b1.w * r1.w);
+                    *reinterpret_cast<uint4*>(Arow + (cc >> 3) * ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) = pk;
+                }
+            }
+            fence_proxy_async_smem();
+            named_bar_sync(1, PROD_THREADS);          // the whole tile and both E rows are in shared memory
+            if (tid == EPI_THREADS) {                 // one thread issues the UMMAs of this slot
+                tc_fence_after_sync();
+                for (int atom = 0; atom < NK; ++atom) {
+#pragma unroll
+                    for (int k16 = 0; k16 < 4; ++k16) {
+                        const uint64_t adesc = umma_desc_k_sw128(a_base + (st * NK + atom) * ATOM_BYTES + k16 * 32);
+                        const uint64_t bdesc = umma_desc_k_sw128(b_base + atom * ATOM_BYTES + k16 * 32);
+                        umma_bf16_ss(tmem_base + (uint32_t)(st * ACC_COLS), adesc, bdesc, idesc, (atom | k16) != 0 ? 1u : 0u);
+                    }
+                }
+                umma_commit(&bars->acc_full[st]);   // first arrival: the UMMAs above have completed
+                mbar_arrive(&bars->acc_full[st]);   // second arrival: releases the staged E rows
             }
         }
-        umma_commit(&bars->acc_full[buf]);   // first arrival: the UMMAs above have completed
-        mbar_arrive(&bars->acc_full[buf]);   // second arrival: releases the staged E rows seen through a_full
-    };
+    } else {
+        // ============================================================ epilogue warpgroups: a thread per time step, a head per warpgroup
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+        const int wg = warp >> 2;
+        const int h = hp * HPC + wg;
+        const size_t qoff = (((size_t)b * a.H + h) * a.T + t) * HD;
+        const bool row_ok = t < Lb;
+        float q[HD], o[HD];
+#pragma unroll
+        for (int i = 0; i < HD; i += 4) {
+            float4 v = row_ok ? ld4_dyn_f32(a.Q, a.q_dt, qoff + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            q[i] = v.x * 0.125f; q[i + 1] = v.y * 0.125f; q[i + 2] = v.z * 0.125f; q[i + 3] = v.w * 0.125f;
+            o[i] = o[i + 1] = o[i + 2] = o[i + 3] = 0.f;
+        }
+        const float rest = a.v_total - (float)a.kcount[b];
+        float m, l;
+        if (!a.listed_only && rest > 0.f) { m = 0.f; l = rest; } else { m = -INFINITY; l = 0.f; }
+        const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(wg * HD);
 
-    if (n_slots > 0) {
-        stage_slot(0);
-        if (tid == 0) issue_slot(0);
-    }
-    for (int i = 0; i < n_slots; ++i) {
-        if (i + 1 < n_slots) {
-            stage_slot(i + 1);
-            if (tid == 0) issue_slot(i + 1);
+        for (int i = 0; i < n_slots; ++i) {
+            const int st = i % NSTAGE, u = i / NSTAGE;
+            mbar_wait(&bars->acc_full[st], (uint32_t)(u & 1), abort_flag);
+            tc_fence_after_sync();
+            float pre[HD];
+            tmem_ld_32x32b_x32(t_lane + st * ACC_COLS, pre);
+            tmem_ld_32x32b_x32(t_lane + st * ACC_COLS + 32, pre + 32);
+            tmem_wait_ld();
+
+            const float* ek = E_sh + st * 2 * ACC_COLS + wg * HD;
+            const float* ev = ek + ACC_COLS;
+            float sp[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < HD; j += 4) {
+                const float4 e = *reinterpret_cast<const float4*>(ek + j);
+                const float ee[4] = {e.x, e.y, e.z, e.w};
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    const float hh = pre[j + v];
+                    const float g = a.silu ? fmaf(hh, tanh_approx(hh), hh) : hh;
+                    pre[j + v] = g;
+                    sp[v] = fmaf(g * q[j + v], ee[v], sp[v]);
+                }
+            }
+            const float s = (sp[0] + sp[1]) + (sp[2] + sp[3]);
+            const float m_new = fmaxf(m, s);
+            if (m_new > m) {
+                const float alpha = __expf(m - m_new);
+                l *= alpha;
+#pragma unroll
+                for (int j = 0; j < HD; ++j) o[j] *= alpha;
+                m = m_new;
+            }
+            const float p = __expf(s - m);
+            l += p;
+#pragma unroll
+            for (int j = 0; j < HD; j += 4) {
+                const float4 e = *reinterpret_cast<const float4*>(ev + j);
+                o[j] = fmaf(p * pre[j], e.x, o[j]);
+                o[j + 1] = fmaf(p * pre[j + 1], e.y, o[j + 1]);
+                o[j + 2] = fmaf(p * pre[j + 2], e.z, o[j + 2]);
+                o[j + 3] = fmaf(p * pre[j + 3], e.w, o[j + 3]);
+            }
+            // accumulators and E rows of this stage are consumed
+            tc_fence_before_sync();
             __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->acc_empty[st]);
         }
-        const int buf = i & 1;
-        mbar_wait(&bars->acc_full[buf], (uint32_t)((i >> 1) & 1), abort_flag);
-        tc_fence_after_sync();
-        float pre[HD];
-        const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(buf * HPC * HD + wg * HD);
-        tmem_ld_32x32b_x32(taddr, pre);
-        tmem_ld_32x32b_x32(taddr + 32, pre + 32);
-        tmem_wait_ld();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
-
-        const float* ek = E_sh + ((i % E_STAGES) * 2 + 0) * HPC * HD + wg * HD;
-        const float* ev = ek + HPC * HD;
-        float s = 0.f;
+        if (t < a.T) {
+            const float inv = (row_ok && l > 0.f) ? 1.0f / l : 0.f;
 #pragma unroll
-        for (int j = 0; j < HD; j += 4) {
-            const float4 e = *reinterpret_cast<const float4*>(ek + j);
-            const float ee[4] = {e.x, e.y, e.z, e.w};
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float hh = pre[j + u];
-                const float g = a.silu ? fmaf(hh, tanh_approx(hh), hh) : hh;
-                pre[j + u] = g;
-                s = fmaf(g * q[j + u], ee[u], s);
-            }
+            for (int i = 0; i < HD; i += 4)
+                *reinterpret_cast<float4*>(a.O + qoff + i) = make_float4(o[i] * inv, o[i + 1] * inv, o[i + 2] * inv, o[i + 3] * inv);
+            a.LSE[((size_t)b * a.H + h) * a.T + t] = (row_ok && l > 0.f) ? m + logf(l) : 0.f;
         }
-        const float m_new = fmaxf(m, s);
-        if (m_new > m) {
-            const float alpha = __expf(m - m_new);
-            l *= alpha;
-#pragma unroll
-            for (int j = 0; j < HD; ++j) o[j] *= alpha;
-            m = m_new;
-        }
-        const float p = __expf(s - m);
-        l += p;
-#pragma unroll
-        for (int j = 0; j < HD; j += 4) {
-            const float4 e = *reinterpret_cast<const float4*>(ev + j);
-            o[j] = fmaf(p * pre[j], e.x, o[j]);
-            o[j + 1] = fmaf(p * pre[j + 1], e.y, o[j + 1]);
-            o[j + 2] = fmaf(p * pre[j + 2], e.z, o[j + 2]);
-            o[j + 3] = fmaf(p * pre[j + 3], e.w, o[j + 3]);
-        }
-    }
-    if (t < a.T) {
-        const float inv = (row_ok && l > 0.f) ? 1.0f / l : 0.f;
-#pragma unroll
-        for (int i = 0; i < HD; i += 4)
-            *reinterpret_cast<float4*>(a.O + qoff + i) = make_float4(o[i] * inv, o[i + 1] * inv, o[i + 2] * inv, o[i + 3] * inv);
-        a.LSE[((size_t)b * a.H + h) * a.T + t] = (row_ok && l > 0.f) ? m + logf(l) : 0.f;
     }
     // ---------------------------------------------------------------- teardown
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 0) {
+    if (warp == EPI_WARPS) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, TMEM_COLS);
     }
-    if (tid == 0 && bars->abort_flag) atomicExch(status, 1);
+    if (tid == 0 && bars->abort_flag) atomicExch(status, 1);   // sticky: later CTAs of this launch skip their work
 }
 
 }  // namespace tc
@@ -317,6 +337,7 @@ int flash_fwd_tc(const FlashArgs& a, void* ws, cudaStream_t st) {
     int* status = reinterpret_cast<int*>((reinterpret_cast<uintptr_t>(ws) + 15) & ~uintptr_t(15));
     MBEMA_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), st));
     const tc::Smem L = tc::smem_layout(a.N, a.K);
+    if (L.total > 227 * 1024) return MBEMA_ERR_UNSUPPORTED;
     MBEMA_CUDA_TRY(cudaFuncSetAttribute(tc::k_flash_fwd_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total));
     dim3 grid(a.nT, a.H / tc::HPC, a.B);
     tc::k_flash_fwd_tc<<<grid, tc::THREADS, L.total, st>>>(a, status);

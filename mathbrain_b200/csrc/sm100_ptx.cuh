@@ -9,7 +9,7 @@
 namespace mbema {
 namespace ptx {
 
-static constexpr unsigned MBEMA_SPIN_LIMIT = 1u << 24;   // ~ a second of polling at worst
+static constexpr unsigned MBEMA_SPIN_LIMIT = 1u << 21;   // polls before a wait gives up (each poll may block briefly)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -39,7 +39,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     for (unsigned it = 0; it < MBEMA_SPIN_LIMIT; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 1023u) == 1023u && *abort_flag) return false;
+        if ((it & 255u) == 255u && *abort_flag) return false;
     }
     *abort_flag = 1;
     return false;
