@@ -87,7 +87,8 @@ int mbema_query_scan(const int64_t* x, const float* rhos, const float* c_init, c
  * kernels need to rebuild the state inside a tile.
  * Replaces precompute_boundaries (mathbrain/triton_flash_ema.py:81-113; kernel :29-78).
  *   unique [B,K] i64 (-1 = not a slot)   c_base [B,K,N] f32 or NULL (zeros)
- *   out: tile_state [B, nT, K, N] f32 with nT = ceil(T / MBEMA_TILE_T)
+ *   out: tile_state [B, nT, K, N] f32 with nT = ceil(T / MBEMA_TILE_T), immediately followed in the same buffer
+ *                   by the same values as bf16 [B, nT, K, N] (6 bytes per element in total)
  *        tok_state  [B, T, N]     f32  state of x[b,t]'s own slot just before step t (0 if unlisted)
  *        kcount     [B]           i32  number of valid (>= 0) entries of unique[b,:]
  *   flags: MBEMA_FLAG_CBASE_EXTRA_DECAY.

@@ -33,10 +33,13 @@ static constexpr int NSTAGE = 3;                   // A-tile / accumulator / E-r
 static constexpr int ACC_COLS = HPC * HD;          // fp32 accumulator columns per stage
 static constexpr int TMEM_COLS = 512;              // power of two >= NSTAGE * ACC_COLS
 static constexpr int MAX_SLOTS = 8192;
+static constexpr int PD = 3;                       // prefetch distance (slots) of the snapshot / E-row ring
+static constexpr int RING = PD + 1;
+static constexpr int RING_STAGE_BYTES = 128 * 4 + 2 * ACC_COLS * 4;   // snapshot row (N <= 128 fp32) + raw E_k, E_v rows
 
 struct Smem {
     // offsets (bytes) into the dynamic shared memory block, base aligned to 1024
-    int a_off, b_off, r_off, e_off, tok_off, slot_off, key_off, bar_off, total;
+    int a_off, b_off, r_off, e_off, ring_off, tok_off, slot_off, key_off, bar_off, total;
 };
 
 __host__ __device__ inline Smem smem_layout(int N, int K) {
@@ -47,6 +50,7 @@ __host__ __device__ inline Smem smem_layout(int N, int K) {
     s.b_off = o; o += NK * ATOM_BYTES;
     s.r_off = o; o += TM * (N + 4) * 4;
     s.e_off = o; o += NSTAGE * 2 * HPC * HD * 4;
+    s.ring_off = o; o += RING * RING_STAGE_BYTES;
     s.tok_off = o; o += TM * 4;
     s.slot_off = o; o += ((K * 2 + 15) / 16) * 16;
     s.key_off = o; o += ((K * 4 + 15) / 16) * 16;
@@ -72,15 +76,19 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// SILU is a compile-time switch: a run-time test inside the unrolled epilogue would put a branch between every
+// pair of gate elements and stop the scheduler from overlapping their MUFU and FMA latencies.
+template <bool SILU, int NK>
 __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* status) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const int N = a.N, NK = N / 64, ldR = N + 4;
+    constexpr int N = NK * 64, ldR = N + 4;
     const Smem L = smem_layout(N, a.K);
     unsigned char* A_sh = sm + L.a_off;
     unsigned char* B_sh = sm + L.b_off;
     float* R_sh = reinterpret_cast<float*>(sm + L.r_off);
     float* E_sh = reinterpret_cast<float*>(sm + L.e_off);
+    unsigned char* ring_sh = sm + L.ring_off;
     int* tok_sh = reinterpret_cast<int*>(sm + L.tok_off);
     unsigned short* slot_sh = reinterpret_cast<unsigned short*>(sm + L.slot_off);
     int* key_sh = reinterpret_cast<int*>(sm + L.key_off);
@@ -139,7 +147,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
     {
         // B operand: rows = the pair's 128 output columns, K-major over n; 0.5 * W when the gate is SiLU (the
         // epilogue evaluates SiLU(x) = h + h * tanh(h) with h = x / 2)
-        const float wscale = a.silu ? 0.5f : 1.0f;
+        const float wscale = SILU ? 0.5f : 1.0f;
         for (int i = tid; i < N * HPC * HD; i += THREADS) {
             const int n = i / (HPC * HD), dd = i % (HPC * HD);
             const float w = a.W[(size_t)n * D + hp * HPC * HD + dd] * wscale;
@@ -167,18 +175,56 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
         const uint32_t idesc = umma_idesc_bf16(TM, ACC_COLS, 0, 0);
         const uint32_t a_base = smem_u32(A_sh), b_base = smem_u32(B_sh);
         const int wi = row >> 5, bi = row & 31;
+        const int esize = (a.e_dt == MBEMA_F32) ? 4 : 2;
+        const int s_chunks = N / 8, e_chunks = ACC_COLS * esize / 16;     // 16-byte chunks per row (bf16 snapshot; raw E)
+        const __nv_bfloat16* snap16 = reinterpret_cast<const __nv_bfloat16*>(a.tile_state + (size_t)a.B * a.nT * a.K * N);
+        // Asynchronous prefetch of slot j's snapshot row and raw E_k / E_v rows into ring stage j % RING.
+        auto prefetch = [&](int j) {
+            if (j < n_slots) {
+                const int k = slot_sh[j];
+                unsigned char* dst = ring_sh + (j % RING) * RING_STAGE_BYTES;
+                const unsigned char* srcS = reinterpret_cast<const unsigned char*>(snap16 + (((size_t)b * a.nT + tile) * a.K + k) * N);
+                const size_t eoff = (((size_t)b * a.K + k) * D + hp * ACC_COLS) * esize;
+                const unsigned char* srcK = reinterpret_cast<const unsigned char*>(a.Ek) + eoff;
+                const unsigned char* srcV = reinterpret_cast<const unsigned char*>(a.Ev) + eoff;
+                for (int c = row; c < s_chunks + 2 * e_chunks; c += PROD_THREADS) {
+                    const unsigned char* src;
+                    unsigned char* d;
+                    if (c < s_chunks) { src = srcS + c * 16; d = dst + c * 16; }
+                    else if (c < s_chunks + e_chunks) { src = srcK + (c - s_chunks) * 16; d = dst + 512 + (c - s_chunks) * 16; }
+                    else { src = srcV + (c - s_chunks - e_chunks) * 16; d = dst + 512 + ACC_COLS * 4 + (c - s_chunks - e_chunks) * 16; }
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(d)), "l"(src) : "memory");
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        // this row's decay powers as packed bf16 pairs (register-resident when N == 64)
+        uint32_t R2[NK == 1 ? 32 : 1];
+        if (NK == 1) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) R2[j] = pack_bf16x2(R_sh[row * ldR + 2 * j], R_sh[row * ldR + 2 * j + 1]);
+        }
+        for (int j = 0; j < PD; ++j) prefetch(j);
+        asm volatile("cp.async.wait_group %0;" ::"n"(PD - 1) : "memory");
+        named_bar_sync(1, PROD_THREADS);                // slot 0's rows are visible to the whole warpgroup
         for (int i = 0; i < n_slots; ++i) {
             const int st = i % NSTAGE, u = i / NSTAGE;
+            prefetch(i + PD);
+            asm volatile("cp.async.wait_group %0;" ::"n"(PD - 1) : "memory");   // this thread's copies for slot i+1 landed
             // stage st (A tile, E rows, accumulators) is free once the epilogue of slot i - NSTAGE has finished
             if (i >= NSTAGE) mbar_wait(&bars->acc_empty[st], (uint32_t)((u - 1) & 1), abort_flag);
-            const int k = slot_sh[i];
             const int key = key_sh[i];
-            // E_k / E_v rows of the slot for the head pair, as fp32: thread p handles column p of both
+            const unsigned char* rg = ring_sh + (i % RING) * RING_STAGE_BYTES;
+            // E_k / E_v rows of the slot for the head pair, as fp32: thread p converts column p of both
             {
-                const size_t off = ((size_t)b * a.K + k) * D + hp * ACC_COLS + row;
                 float* dst = E_sh + st * 2 * ACC_COLS + row;
-                dst[0] = ld_dyn_f32(a.Ek, a.e_dt, off);
-                dst[ACC_COLS] = ld_dyn_f32(a.Ev, a.e_dt, off);
+                if (esize == 4) {
+                    dst[0] = reinterpret_cast<const float*>(rg + 512)[row];
+                    dst[ACC_COLS] = reinterpret_cast<const float*>(rg + 512 + ACC_COLS * 4)[row];
+                } else {
+                    dst[0] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rg + 512)[row]);
+                    dst[ACC_COLS] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rg + 512 + ACC_COLS * 4)[row]);
+                }
             }
             // last occurrence of the slot's token strictly before this row, inside the tile
             int s = -1;
@@ -196,6 +242,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
             if (s >= 0) {   // restart from the token's own state at that occurrence (+1 for the occurrence itself)
                 const float* base = a.tok_state + ((size_t)b * a.T + t0 + s) * N;
                 const float* Rrow = R_sh + (row - s) * ldR;
+#pragma unroll 2
                 for (int cc = 0; cc < N / 8; ++cc) {
                     const int n0 = cc * 8;
                     const float4 b0 = __ldg(reinterpret_cast<const float4*>(base + n0));
@@ -209,26 +256,39 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
                     pk.w = pack_bf16x2(fmaf(b1.z, r1.z, r1.z), fmaf(b1.w, r1.w, r1.w));
                     *reinterpret_cast<uint4*>(Arow + (cc >> 3) * ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) = pk;
                 }
-            } else {        // plain decay of the tile-start snapshot
-                const float* base = a.tile_state + (((size_t)b * a.nT + tile) * a.K + k) * N;
-                const float* Rrow = R_sh + row * ldR;
-                for (int cc = 0; cc < N / 8; ++cc) {
-                    const int n0 = cc * 8;
-                    const float4 b0 = __ldg(reinterpret_cast<const float4*>(base + n0));
-                    const float4 b1 = __ldg(reinterpret_cast<const float4*>(base + n0 + 4));
-                    const float4 r0 = *reinterpret_cast<const float4*>(Rrow + n0);
-                    const float4 r1 = *reinterpret_cast<const float4*>(Rrow + n0 + 4);
-                    uint4 pk;
-                    pk.x = pack_bf16x2(b0.x * r0.x, b0.y * r0.y);
-                    pk.y = pack_bf16x2(b0.z * r0.z, b0.w * r0.w);
-                    pk.z = pack_bf16x2(b1.x * r1.x, b1.y * r1.y);
-                    pk.w = pack_bf16x2(b1.z * r1.z, b1.w * r1.w);
-                    *reinterpret_cast<uint4*>(Arow + (cc >> 3) * ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) = pk;
+            } else {        // plain decay of the tile-start snapshot: bf16 snapshot (prefetched, broadcast reads) times
+                            // this row's decay powers; product rounded to bf16 by the packed multiply
+                if (NK == 1) {
+#pragma unroll
+                    for (int cc = 0; cc < 8; ++cc) {
+                        const uint4 sv = *reinterpret_cast<const uint4*>(rg + cc * 16);
+                        uint4 pk;
+                        pk.x = mul_bf16x2(sv.x, R2[4 * cc]);
+                        pk.y = mul_bf16x2(sv.y, R2[4 * cc + 1]);
+                        pk.z = mul_bf16x2(sv.z, R2[4 * cc + 2]);
+                        pk.w = mul_bf16x2(sv.w, R2[4 * cc + 3]);
+                        *reinterpret_cast<uint4*>(Arow + (((cc & 7) ^ (row & 7)) << 4)) = pk;
+                    }
+                } else {
+                    const float* Rrow = R_sh + row * ldR;
+#pragma unroll 2
+                    for (int cc = 0; cc < N / 8; ++cc) {
+                        const int n0 = cc * 8;
+                        const uint4 sv = *reinterpret_cast<const uint4*>(rg + cc * 16);
+                        const float4 r0 = *reinterpret_cast<const float4*>(Rrow + n0);
+                        const float4 r1 = *reinterpret_cast<const float4*>(Rrow + n0 + 4);
+                        uint4 pk;
+                        pk.x = pack_bf16x2(bf16_lo(sv.x) * r0.x, bf16_hi(sv.x) * r0.y);
+                        pk.y = pack_bf16x2(bf16_lo(sv.y) * r0.z, bf16_hi(sv.y) * r0.w);
+                        pk.z = pack_bf16x2(bf16_lo(sv.z) * r1.x, bf16_hi(sv.z) * r1.y);
+                        pk.w = pack_bf16x2(bf16_lo(sv.w) * r1.z, bf16_hi(sv.w) * r1.w);
+                        *reinterpret_cast<uint4*>(Arow + (cc >> 3) * ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) = pk;
+                    }
                 }
             }
             fence_proxy_async_smem();
             named_bar_sync(1, PROD_THREADS);          // the whole tile and both E rows are in shared memory
-            if (tid == EPI_THREADS) {                 // one thread issues the UMMAs of this slot
+            if (warp == EPI_WARPS + (i & 3) && lane == 0) {   // one thread issues the UMMAs of this slot (the role rotates)
                 tc_fence_after_sync();
                 for (int atom = 0; atom < NK; ++atom) {
 #pragma unroll
@@ -280,7 +340,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
 #pragma unroll
                 for (int v = 0; v < 4; ++v) {
                     const float hh = pre[j + v];
-                    const float g = a.silu ? fmaf(hh, tanh_approx(hh), hh) : hh;
+                    const float g = SILU ? fmaf(hh, tanh_approx(hh), hh) : hh;
                     pre[j + v] = g;
                     sp[v] = fmaf(g * q[j + v], ee[v], sp[v]);
                 }
@@ -338,9 +398,15 @@ int flash_fwd_tc(const FlashArgs& a, void* ws, cudaStream_t st) {
     MBEMA_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), st));
     const tc::Smem L = tc::smem_layout(a.N, a.K);
     if (L.total > 227 * 1024) return MBEMA_ERR_UNSUPPORTED;
-    MBEMA_CUDA_TRY(cudaFuncSetAttribute(tc::k_flash_fwd_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total));
     dim3 grid(a.nT, a.H / tc::HPC, a.B);
-    tc::k_flash_fwd_tc<<<grid, tc::THREADS, L.total, st>>>(a, status);
+#define MBEMA_LAUNCH_FWD(S_, NK_)                                                                                     \
+    do {                                                                                                             \
+        MBEMA_CUDA_TRY(cudaFuncSetAttribute(tc::k_flash_fwd_tc<S_, NK_>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total)); \
+        tc::k_flash_fwd_tc<S_, NK_><<<grid, tc::THREADS, L.total, st>>>(a, status);                                 \
+    } while (0)
+    if (a.N == 64) { if (a.silu) MBEMA_LAUNCH_FWD(true, 1); else MBEMA_LAUNCH_FWD(false, 1); }
+    else { if (a.silu) MBEMA_LAUNCH_FWD(true, 2); else MBEMA_LAUNCH_FWD(false, 2); }
+#undef MBEMA_LAUNCH_FWD
     return check_launch();
 }
 

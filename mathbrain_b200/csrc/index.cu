@@ -209,9 +209,15 @@ k_tile_states(IndexWs w, const int64_t* __restrict__ unique, const float* __rest
     const int32_t* s_tok = w.s_tok + (size_t)b * T;
     const int32_t* s_pos = w.s_pos + (size_t)b * T;
     float* out = tile_state + ((size_t)b * nT * K + k) * N;  // + tile * K * N
+    // the same snapshots in bf16 follow the fp32 block (operand format of the tensor-core attention kernels)
+    __nv_bfloat16* out16 = reinterpret_cast<__nv_bfloat16*>(tile_state + (size_t)gridDim.y * nT * K * N) +
+                           ((size_t)b * nT * K + k) * N;
     if (kv < 0) {
         for (int i = 0; i < nT; ++i)
-            for (int n = lane; n < N; n += 32) out[(size_t)i * K * N + n] = 0.0f;
+            for (int n = lane; n < N; n += 32) {
+                out[(size_t)i * K * N + n] = 0.0f;
+                out16[(size_t)i * K * N + n] = __float2bfloat16(0.0f);
+            }
         return;
     }
     const int key = (int)(kv & 0x7fffffff);
@@ -249,7 +255,11 @@ k_tile_states(IndexWs w, const int64_t* __restrict__ unique, const float* __rest
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             int n = lane + 32 * i;
-            if (n < N) out[(size_t)tile * K * N + n] = u[i] * (float)exp2(dt * l2r[i]);
+            if (n < N) {
+                const float v = u[i] * (float)exp2(dt * l2r[i]);
+                out[(size_t)tile * K * N + n] = v;
+                out16[(size_t)tile * K * N + n] = __float2bfloat16(v);
+            }
         }
     }
 }
