@@ -1,0 +1,525 @@
+// Flash-EMA gated cross-attention on the Blackwell tensor cores (MBEMA_MODE_TC_BF16), backward.
+//
+// Same decomposition as the forward (CTA = sample x 128-step tile x head pair, loop over the valid slots, producer
+// warpgroup + two epilogue warpgroups, a thread per time step), with three tensor-core products per slot:
+//   (1) pre[128 t x 128 d]  = A[t, n] @ W[n, d]                      recompute of the gate pre-activation
+//   (2) dW^T[128 d x N]    += dpre[t, d]^T @ A[t, n]                 accumulated in TMEM over all slots of the CTA
+//   (3) dE_k[d], dE_v[d]    = (ds*q*g)[t, d]^T @ 1,  (p*dO*g)[t, d]^T @ 1     column sums over the tile's time steps
+// The epilogue threads read the accumulators of (1) twice (two passes keep the register footprint at one 32-column
+// chunk): pass 1 forms the score and dO.V, giving p = exp(s - LSE) and ds; pass 2 recomputes the gate and writes the
+// three bf16 operand tiles of (2) and (3) to shared memory (128-byte-swizzled, "MN-major": the tile row is the time
+// step, which is the contraction index).  dQ stays in registers for the whole slot loop.  q and dO are held as
+// packed bf16 pairs.  Every wait is bounded (see sm100_ptx.cuh).
+#include "flash.cuh"
+#include "sm100_ptx.cuh"
+
+namespace mbema {
+namespace tcb {
+
+using namespace ptx;
+
+static constexpr int TM = MBEMA_TILE_T;
+static constexpr int HPC = 2;
+static constexpr int HD = 64;
+static constexpr int N = 64;                       // EMA channels supported by this kernel
+static constexpr int EPI_WARPS = 4 * HPC;
+static constexpr int EPI_THREADS = 32 * EPI_WARPS;
+static constexpr int PROD_THREADS = 128;
+static constexpr int THREADS = EPI_THREADS + PROD_THREADS;
+static constexpr int ATOM_BYTES = TM * 128;
+static constexpr int NA = 3;                       // A-tile / E-row stages in shared memory
+static constexpr int NACC = 2;                     // gate accumulator stages in TMEM
+static constexpr int ACC_COLS = HPC * HD;
+static constexpr int COL_DW = NACC * ACC_COLS;     // TMEM column of dW^T [128 d x N]
+static constexpr int COL_DEK = COL_DW + N;         // TMEM column of the dE_k column sums (16 columns, all equal)
+static constexpr int COL_DEV = COL_DEK + 16;
+static constexpr int TMEM_COLS = 512;
+static constexpr int PD = 3, RING = PD + 1;
+static constexpr int RING_STAGE_BYTES = 256 + 2 * ACC_COLS * 4;
+static constexpr int MAX_SLOTS = 4096;
+
+struct Smem {
+    int a_off, b_off, z_off, ones_off, r_off, e_off, ring_off, tok_off, slot_off, key_off, bar_off, total;
+};
+
+__host__ __device__ inline Smem smem_layout(int K) {
+    Smem s;
+    int o = 0;
+    s.a_off = o; o += NA * ATOM_BYTES;
+    s.b_off = o; o += ATOM_BYTES;                 // W^T for the gate product (K-major over n)
+    s.z_off = o; o += 3 * HPC * ATOM_BYTES;       // dpre, ds*q*g, p*dO*g tiles: [kind][head][128 t][64 d] bf16
+    s.ones_off = o; o += 2048;                    // 16 x 64 bf16 ones (B operand of the column sums)
+    s.r_off = o; o += TM * N * 2;                 // decay powers rho_n^r as bf16 [128][64] (in-tile restarts only)
+    s.e_off = o; o += NA * 2 * ACC_COLS * 4;
+    s.ring_off = o; o += RING * RING_STAGE_BYTES;
+    s.tok_off = o; o += TM * 4;
+    s.slot_off = o; o += ((K * 2 + 15) / 16) * 16;
+    s.key_off = o; o += ((K * 4 + 15) / 16) * 16;
+    s.bar_off = o; o += 128;
+    s.total = o + 1024;
+    return s;
+}
+
+__device__ __forceinline__ int sw128_off(int row, int col) {
+    return row * 128 + ((((col >> 3) ^ (row & 7)) << 4) | ((col & 7) << 1));
+}
+
+struct Bars {
+    uint64_t acc_full[NACC];     // gate UMMAs done + E rows staged                  (2 arrivals)
+    uint64_t acc_empty[NACC];    // all epilogue warps finished reading the stage      (EPI_WARPS arrivals)
+    uint64_t z_full;             // all epilogue warps wrote their part of the Z tiles (EPI_WARPS arrivals)
+    uint64_t z_done;             // products (2) and (3) of the slot have completed    (1 arrival: commit)
+    uint32_t tmem_base;
+    int abort_flag;
+    int n_slots;
+};
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+__device__ __forceinline__ float tmem_ld_1(uint32_t taddr) {
+    uint32_t r;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+    return __uint_as_float(r);
+}
+
+template <bool SILU>
+__global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const Smem L = smem_layout(a.K);
+    unsigned char* A_sh = sm + L.a_off;
+    unsigned char* B_sh = sm + L.b_off;
+    unsigned char* Z_sh = sm + L.z_off;
+    unsigned char* ones_sh = sm + L.ones_off;
+    __nv_bfloat16* R_sh = reinterpret_cast<__nv_bfloat16*>(sm + L.r_off);
+    float* E_sh = reinterpret_cast<float*>(sm + L.e_off);
+    unsigned char* ring_sh = sm + L.ring_off;
+    int* tok_sh = reinterpret_cast<int*>(sm + L.tok_off);
+    unsigned short* slot_sh = reinterpret_cast<unsigned short*>(sm + L.slot_off);
+    int* key_sh = reinterpret_cast<int*>(sm + L.key_off);
+    Bars* bars = reinterpret_cast<Bars*>(sm + L.bar_off);
+    uint64_t* a_free = reinterpret_cast<uint64_t*>(sm + L.bar_off + 96);   // [NA] A/E stage released by product (2)
+    volatile int* abort_flag = &bars->abort_flag;
+
+    const int tile = blockIdx.x, hp = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int D = a.H * HD;
+    const int t0 = tile * TM;
+    const int Lb = a.seq_lens ? min(max(a.seq_lens[b], 0), a.T) : a.T;
+    const bool is_epi = warp < EPI_WARPS;
+    const int row = (warp & 3) * 32 + lane;
+    const int t = t0 + row;
+    float* part_out = a.dW_part + (((size_t)b * (a.H / HPC) + hp) * a.nT + tile) * (size_t)N * ACC_COLS;   // [n][128 d]
+
+    if (t0 >= Lb) {   // nothing to do for this tile: zero dQ rows and the dW partial (uniform per CTA)
+        if (is_epi && t < a.T) {
+            const int h = hp * HPC + (warp >> 2);
+            const size_t qo = (((size_t)b * a.H + h) * a.T + t) * HD;
+#pragma unroll
+            for (int i = 0; i < HD; i += 4) *reinterpret_cast<float4*>(a.dQ + qo + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        for (int i = tid; i < N * ACC_COLS; i += THREADS) part_out[i] = 0.f;
+        return;
+    }
+
+    // ---------------------------------------------------------------- prologue
+    if (tid == 0) {
+        for (int i = 0; i < NACC; ++i) {
+            mbar_init(&bars->acc_full[i], 2);
+            mbar_init(&bars->acc_empty[i], EPI_WARPS);
+        }
+        for (int i = 0; i < NA; ++i) mbar_init(&a_free[i], 1);
+        mbar_init(&bars->z_full, EPI_WARPS);
+        mbar_init(&bars->z_done, 1);
+        bars->abort_flag = *reinterpret_cast<volatile int*>(status);
+        fence_barrier_init();
+    }
+    if (warp == EPI_WARPS) {
+        tmem_alloc(&bars->tmem_base, TMEM_COLS);
+        tmem_relinquish();
+    }
+    if (warp == EPI_WARPS + 1) {
+        int n = 0;
+        for (int k0 = 0; k0 < a.K; k0 += 32) {
+            const int k = k0 + lane;
+            const long long kv = (k < a.K) ? a.unique[(size_t)b * a.K + k] : -1;
+            const bool ok = kv >= 0;
+            const unsigned m = __ballot_sync(0xffffffffu, ok);
+            if (ok) {
+                const int pos = n + __popc(m & ((1u << lane) - 1u));
+                slot_sh[pos] = (unsigned short)k;
+                key_sh[pos] = (int)(kv & 0x7fffffffLL);
+            }
+            n += __popc(m);
+        }
+        if (lane == 0) bars->n_slots = n;
+    }
+    {
+        const float wscale = SILU ? 0.5f : 1.0f;
+        for (int i = tid; i < N * ACC_COLS; i += THREADS) {
+            const int n = i / ACC_COLS, dd = i % ACC_COLS;
+            const float w = a.W[(size_t)n * D + hp * ACC_COLS + dd] * wscale;
+            *reinterpret_cast<__nv_bfloat16*>(B_sh + sw128_off(dd, n)) = __float2bfloat16(w);
+        }
+        for (int i = tid; i < TM * N; i += THREADS) {
+            const int r = i / N, n = i % N;
+            R_sh[i] = __float2bfloat16(exp2f((float)r * log2f(a.rhos[n])));
+        }
+        for (int i = tid; i < 1024; i += THREADS) reinterpret_cast<__nv_bfloat16*>(ones_sh)[i] = __float2bfloat16(1.0f);
+        for (int i = tid; i < TM; i += THREADS) {
+            const int tt = t0 + i;
+            tok_sh[i] = (tt < Lb) ? (int)(a.x[(size_t)b * a.T + tt] & 0x7fffffffLL) : -1;
+        }
+    }
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = bars->tmem_base;
+    const int n_slots = bars->abort_flag ? 0 : bars->n_slots;
+
+    if (!is_epi) {
+        // ============================================================ producer warpgroup
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+        const uint32_t idesc_gate = umma_idesc_bf16(TM, ACC_COLS, 0, 0);      // A, B K-major
+        const uint32_t idesc_dw = umma_idesc_bf16(ACC_COLS, N, 1, 1);         // A = dpre (MN-major), B = state tile (MN-major)
+        const uint32_t idesc_de = umma_idesc_bf16(ACC_COLS, 16, 1, 0);        // A = Z tile (MN-major), B = ones (K-major)
+        const uint32_t a_base = smem_u32(A_sh), b_base = smem_u32(B_sh), z_base = smem_u32(Z_sh), o_base = smem_u32(ones_sh);
+        const int wi = row >> 5, bi = row & 31;
+        const int esize = (a.e_dt == MBEMA_F32) ? 4 : 2;
+        const int s_chunks = N / 8, e_chunks = ACC_COLS * esize / 16;
+        const __nv_bfloat16* snap16 = reinterpret_cast<const __nv_bfloat16*>(a.tile_state + (size_t)a.B * a.nT * a.K * N);
+        auto prefetch = [&](int j) {
+            if (j < n_slots) {
+                const int k = slot_sh[j];
+                unsigned char* dst = ring_sh + (j % RING) * RING_STAGE_BYTES;
+                const unsigned char* srcS = reinterpret_cast<const unsigned char*>(snap16 + (((size_t)b * a.nT + tile) * a.K + k) * N);
+                const size_t eoff = (((size_t)b * a.K + k) * D + hp * ACC_COLS) * esize;
+                const unsigned char* srcK = reinterpret_cast<const unsigned char*>(a.Ek) + eoff;
+                const unsigned char* srcV = reinterpret_cast<const unsigned char*>(a.Ev) + eoff;
+                for (int c = row; c < s_chunks + 2 * e_chunks; c += PROD_THREADS) {
+                    const unsigned char* src;
+                    unsigned char* d;
+                    if (c < s_chunks) { src = srcS + c * 16; d = dst + c * 16; }
+                    else if (c < s_chunks + e_chunks) { src = srcK + (c - s_chunks) * 16; d = dst + 256 + (c - s_chunks) * 16; }
+                    else { src = srcV + (c - s_chunks - e_chunks) * 16; d = dst + 256 + ACC_COLS * 4 + (c - s_chunks - e_chunks) * 16; }
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(d)), "l"(src) : "memory");
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        // products (2) and (3) of slot j: issued by one thread once the epilogue has written the Z tiles
+        auto issue_grad_products = [&](int j) {
+            mbar_wait(&bars->z_full, (uint32_t)(j & 1), abort_flag);
+            tc_fence_after_sync();
+            const uint32_t a_tile = a_base + (j % NA) * ATOM_BYTES;
+#pragma unroll
+            for (int ks = 0; ks < TM / 16; ++ks) {      // contraction over the 128 time steps, 16 per instruction
+                const uint64_t dp = umma_desc_mn_sw128(z_base + 0 * HPC * ATOM_BYTES + ks * 2048, ATOM_BYTES, 1024);
+                const uint64_t st = umma_desc_mn_sw128(a_tile + ks * 2048, ATOM_BYTES, 1024);
+                umma_bf16_ss(tmem_base + COL_DW, dp, st, idesc_dw, (j | ks) != 0 ? 1u : 0u);
+            }
+            const uint64_t ones = umma_desc_k_sw128(o_base);
+#pragma unroll
+            for (int ks = 0; ks < TM / 16; ++ks) {
+                const uint64_t zk = umma_desc_mn_sw128(z_base + 1 * HPC * ATOM_BYTES + ks * 2048, ATOM_BYTES, 1024);
+                const uint64_t zv = umma_desc_mn_sw128(z_base + 2 * HPC * ATOM_BYTES + ks * 2048, ATOM_BYTES, 1024);
+                umma_bf16_ss(tmem_base + COL_DEK, zk, ones, idesc_de, ks != 0 ? 1u : 0u);
+                umma_bf16_ss(tmem_base + COL_DEV, zv, ones, idesc_de, ks != 0 ? 1u : 0u);
+            }
+            umma_commit(&bars->z_done);
+            umma_commit(&a_free[j % NA]);
+        };
+        uint32_t R2[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) R2[j] = *reinterpret_cast<const uint32_t*>(R_sh + row * N + 2 * j);
+        for (int j = 0; j < PD; ++j) prefetch(j);
+        asm volatile("cp.async.wait_group %0;" ::"n"(PD - 1) : "memory");
+        named_bar_sync(1, PROD_THREADS);
+        for (int i = 0; i < n_slots; ++i) {
+            const int sa = i % NA, sc = i % NACC;
+            prefetch(i + PD);
+            asm volatile("cp.async.wait_group %0;" ::"n"(PD - 1) : "memory");
+            if (i >= NA) mbar_wait(&a_free[sa], (uint32_t)((i / NA - 1) & 1), abort_flag);
+            const int key = key_sh[i];
+            const unsigned char* rg = ring_sh + (i % RING) * RING_STAGE_BYTES;
+            {
+                float* dst = E_sh + sa * 2 * ACC_COLS + row;
+                if (esize == 4) {
+                    dst[0] = reinterpret_cast<const float*>(rg + 256)[row];
+                    dst[ACC_COLS] = reinterpret_cast<const float*>(rg + 256 + ACC_COLS * 4)[row];
+                } else {
+                    dst[0] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rg + 256)[row]);
+                    dst[ACC_COLS] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rg + 256 + ACC_COLS * 4)[row]);
+                }
+            }
+            int s = -1;
+            {
+                unsigned w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) w[j] = __ballot_sync(0xffffffffu, tok_sh[32 * j + lane] == key);
+#pragma unroll
+                for (int j = 3; j >= 0; --j) {
+                    unsigned mm = (j > wi) ? 0u : (j == wi ? (w[j] & ((1u << bi) - 1u)) : w[j]);
+                    if (s < 0 && mm) s = j * 32 + 31 - __clz(mm);
+                }
+            }
+            unsigned char* Arow = A_sh + sa * ATOM_BYTES + row * 128;
+            if (s >= 0) {   // restart from the token's own state at its last in-tile occurrence (+1)
+                const float* base = a.tok_state + ((size_t)b * a.T + t0 + s) * N;
+                const uint32_t* Rrow = reinterpret_cast<const uint32_t*>(R_sh + (row - s) * N);
+#pragma unroll 2
+                for (int cc = 0; cc < 8; ++cc) {
+                    const float4 b0 = __ldg(reinterpret_cast<const float4*>(base + cc * 8));
+                    const float4 b1 = __ldg(reinterpret_cast<const float4*>(base + cc * 8 + 4));
+                    const uint4 rr = *reinterpret_cast<const uint4*>(Rrow + cc * 4);
+                    uint4 pk;
+                    pk.x = pack_bf16x2((b0.x + 1.f) * bf16_lo(rr.x), (b0.y + 1.f) * bf16_hi(rr.x));
+                    pk.y = pack_bf16x2((b0.z + 1.f) * bf16_lo(rr.y), (b0.w + 1.f) * bf16_hi(rr.y));
+                    pk.z = pack_bf16x2((b1.x + 1.f) * bf16_lo(rr.z), (b1.y + 1.f) * bf16_hi(rr.z));
+                    pk.w = pack_bf16x2((b1.z + 1.f) * bf16_lo(rr.w), (b1.w + 1.f) * bf16_hi(rr.w));
+                    *reinterpret_cast<uint4*>(Arow + ((cc ^ (row & 7)) << 4)) = pk;
+                }
+            } else {
+#pragma unroll
+                for (int cc = 0; cc < 8; ++cc) {
+                    const uint4 sv = *reinterpret_cast<const uint4*>(rg + cc * 16);
+                    uint4 pk;
+                    pk.x = mul_bf16x2(sv.x, R2[4 * cc]);
+                    pk.y = mul_bf16x2(sv.y, R2[4 * cc + 1]);
+                    pk.z = mul_bf16x2(sv.z, R2[4 * cc + 2]);
+                    pk.w = mul_bf16x2(sv.w, R2[4 * cc + 3]);
+                    *reinterpret_cast<uint4*>(Arow + ((cc ^ (row & 7)) << 4)) = pk;
+                }
+            }
+            fence_proxy_async_smem();
+            named_bar_sync(1, PROD_THREADS);
+            if (tid == EPI_THREADS) {
+                if (i >= NACC) mbar_wait(&bars->acc_empty[sc], (uint32_t)((i / NACC - 1) & 1), abort_flag);
+                tc_fence_after_sync();
+#pragma unroll
+                for (int k16 = 0; k16 < 4; ++k16) {
+                    const uint64_t adesc = umma_desc_k_sw128(a_base + sa * ATOM_BYTES + k16 * 32);
+                    const uint64_t bdesc = umma_desc_k_sw128(b_base + k16 * 32);
+                    umma_bf16_ss(tmem_base + (uint32_t)(sc * ACC_COLS), adesc, bdesc, idesc_gate, k16 != 0 ? 1u : 0u);
+                }
+                umma_commit(&bars->acc_full[sc]);
+                mbar_arrive(&bars->acc_full[sc]);
+                if (i >= 1) issue_grad_products(i - 1);
+            }
+        }
+        if (tid == EPI_THREADS && n_slots > 0) issue_grad_products(n_slots - 1);
+    } else {
+        // ============================================================ epilogue warpgroups: a thread per time step, a head per warpgroup
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+        const int wg = warp >> 2;
+        const int h = hp * HPC + wg;
+        const size_t qoff = (((size_t)b * a.H + h) * a.T + t) * HD;
+        const bool row_ok = t < Lb;
+        uint32_t q2[HD / 2], do2[HD / 2];     // q / sqrt(hd) and dO as packed bf16 pairs
+        float dq[HD];
+        float drow = 0.f;
+#pragma unroll
+        for (int i = 0; i < HD; i += 4) {
+            const float4 v = row_ok ? ld4_dyn_f32(a.Q, a.q_dt, qoff + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 g = row_ok ? ld4_dyn_f32(a.dO, a.do_dt, qoff + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 ov = row_ok ? *reinterpret_cast<const float4*>(a.O + qoff + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            q2[i / 2] = pack_bf16x2(v.x * 0.125f, v.y * 0.125f);
+            q2[i / 2 + 1] = pack_bf16x2(v.z * 0.125f, v.w * 0.125f);
+            do2[i / 2] = pack_bf16x2(g.x, g.y);
+            do2[i / 2 + 1] = pack_bf16x2(g.z, g.w);
+            drow += g.x * ov.x + g.y * ov.y + g.z * ov.z + g.w * ov.w;
+            dq[i] = dq[i + 1] = dq[i + 2] = dq[i + 3] = 0.f;
+        }
+        const float lse = row_ok ? a.LSE[((size_t)b * a.H + h) * a.T + t] : 0.f;
+        const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        unsigned char* zrow = Z_sh + wg * ATOM_BYTES + row * 128;     // + kind * HPC * ATOM_BYTES + swizzled chunk
+        float* dE_out = (wg == 0 ? a.dEk : a.dEv) + (size_t)b * a.K * D + hp * ACC_COLS + row;   // + slot * D
+        const uint32_t t_de = t_lane + (wg == 0 ? COL_DEK : COL_DEV);
+
+        for (int i = 0; i < n_slots; ++i) {
+            const int sa = i % NA, sc = i % NACC;
+            mbar_wait(&bars->acc_full[sc], (uint32_t)((i / NACC) & 1), abort_flag);
+            tc_fence_after_sync();
+            const float* ek = E_sh + sa * 2 * ACC_COLS + wg * HD;
+            const float* ev = ek + ACC_COLS;
+            const uint32_t t_acc = t_lane + (uint32_t)(sc * ACC_COLS + wg * HD);
+            // ---- pass 1: score and dO.V
+            float sp[2] = {0.f, 0.f}, dpp[2] = {0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                float pre[32];
+                tmem_ld_32x32b_x32(t_acc + c * 32, pre);
+                tmem_wait_ld();
+#pragma unroll
+                for (int jj = 0; jj < 32; jj += 4) {
+                    const int j = c * 32 + jj;
+                    const float4 e1 = *reinterpret_cast<const float4*>(ek + j);
+                    const float4 e2 = *reinterpret_cast<const float4*>(ev + j);
+                    const float ee1[4] = {e1.x, e1.y, e1.z, e1.w}, ee2[4] = {e2.x, e2.y, e2.z, e2.w};
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        const uint32_t qq = q2[(j + v) / 2], dd = do2[(j + v) / 2];
+                        const float qv = (v & 1) ? bf16_hi(qq) : bf16_lo(qq);
+                        const float dv = (v & 1) ? bf16_hi(dd) : bf16_lo(dd);
+                        const float hh = pre[jj + v];
+                        const float g = SILU ? fmaf(hh, tanh_approx(hh), hh) : hh;
+                        sp[v & 1] = fmaf(g * qv, ee1[v], sp[v & 1]);
+                        dpp[v & 1] = fmaf(g * dv, ee2[v], dpp[v & 1]);
+                    }
+                }
+            }
+            const float s = sp[0] + sp[1];
+            const float p = row_ok ? __expf(s - lse) : 0.f;
+            const float dsr = p * ((dpp[0] + dpp[1]) - drow);     // d loss / d score
+            const float dsq = dsr * 0.125f;
+            // ---- column sums of the previous slot (also: its Z tiles have been consumed)
+            if (i >= 1) {
+                mbar_wait(&bars->z_done, (uint32_t)((i - 1) & 1), abort_flag);
+                tc_fence_after_sync();
+                const float v = tmem_ld_1(t_de);
+                tmem_wait_ld();
+                atomicAdd(dE_out + (size_t)slot_sh[i - 1] * D, v);
+            }
+            // ---- pass 2: gate again, gradients, operand tiles of the dW / dE products
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                float pre[32];
+                tmem_ld_32x32b_x32(t_acc + c * 32, pre);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j8 = 0; j8 < 4; ++j8) {          // 8 columns -> one 16-byte chunk per tile
+                    uint32_t zp[4], zk[4], zv[4];
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const int j = c * 32 + j8 * 8 + half * 4;
+                        const float4 e1 = *reinterpret_cast<const float4*>(ek + j);
+                        const float4 e2 = *reinterpret_cast<const float4*>(ev + j);
+                        const float ee1[4] = {e1.x, e1.y, e1.z, e1.w}, ee2[4] = {e2.x, e2.y, e2.z, e2.w};
+                        float o_p[4], o_k[4], o_v[4];
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            const uint32_t qq = q2[(j + v) / 2], dd = do2[(j + v) / 2];
+                            const float qv = (v & 1) ? bf16_hi(qq) : bf16_lo(qq);
+                            const float dv = (v & 1) ? bf16_hi(dd) : bf16_lo(dd);
+                            const float hh = pre[j8 * 8 + half * 4 + v];
+                            float g, dsl;
+                            if (SILU) {
+                                const float th = tanh_approx(hh);
+                                g = fmaf(hh, th, hh);
+                                const float sg = fmaf(0.5f, th, 0.5f);
+                                dsl = fmaf((hh + hh) * sg, 1.0f - sg, sg);     // SiLU'(x), x = 2 h
+                            } else {
+                                g = hh;
+                                dsl = 1.0f;
+                            }
+                            dq[j + v] = fmaf(dsq, ee1[v] * g, dq[j + v]);
+                            o_k[v] = dsr * (qv * g);
+                            o_v[v] = p * (dv * g);
+                            o_p[v] = fmaf(dsr, qv * ee1[v], p * (dv * ee2[v])) * dsl;
+                        }
+                        zp[half * 2] = pack_bf16x2(o_p[0], o_p[1]); zp[half * 2 + 1] = pack_bf16x2(o_p[2], o_p[3]);
+                        zk[half * 2] = pack_bf16x2(o_k[0], o_k[1]); zk[half * 2 + 1] = pack_bf16x2(o_k[2], o_k[3]);
+                        zv[half * 2] = pack_bf16x2(o_v[0], o_v[1]); zv[half * 2 + 1] = pack_bf16x2(o_v[2], o_v[3]);
+                    }
+                    const int chunk = ((c * 4 + j8) ^ (row & 7)) << 4;
+                    *reinterpret_cast<uint4*>(zrow + 0 * HPC * ATOM_BYTES + chunk) = make_uint4(zp[0], zp[1], zp[2], zp[3]);
+                    *reinterpret_cast<uint4*>(zrow + 1 * HPC * ATOM_BYTES + chunk) = make_uint4(zk[0], zk[1], zk[2], zk[3]);
+                    *reinterpret_cast<uint4*>(zrow + 2 * HPC * ATOM_BYTES + chunk) = make_uint4(zv[0], zv[1], zv[2], zv[3]);
+                }
+            }
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&bars->z_full);
+                mbar_arrive(&bars->acc_empty[sc]);
+            }
+        }
+        if (n_slots > 0) {
+            mbar_wait(&bars->z_done, (uint32_t)((n_slots - 1) & 1), abort_flag);
+            tc_fence_after_sync();
+            const float v = tmem_ld_1(t_de);
+            tmem_wait_ld();
+            atomicAdd(dE_out + (size_t)slot_sh[n_slots - 1] * D, v);
+        }
+        if (t < a.T) {
+#pragma unroll
+            for (int i = 0; i < HD; i += 4)
+                *reinterpret_cast<float4*>(a.dQ + qoff + i) = make_float4(dq[i], dq[i + 1], dq[i + 2], dq[i + 3]);
+        }
+        if (wg == 0) {   // dW^T accumulator: lane = column d of the head pair, TMEM columns = n
+            float acc[32];
+#pragma unroll
+            for (int c = 0; c < N / 32; ++c) {
+                if (n_slots > 0) {
+                    tmem_ld_32x32b_x32(t_lane + COL_DW + c * 32, acc);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) part_out[(size_t)(c * 32 + j) * ACC_COLS + row] = acc[j];
+            }
+        }
+    }
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == EPI_WARPS) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+    if (tid == 0 && bars->abort_flag) atomicExch(status, 1);
+}
+
+// dW[n, hp*128 + d] = sum over (b, tile) of part[b][hp][tile][n][d]      (fixed order -> deterministic)
+__global__ void k_flash_dw_reduce_tc(const float* __restrict__ part, float* __restrict__ dW, int B, int HP, int nT, int D) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= N * D) return;
+    const int n = idx / D, col = idx % D, hp = col / ACC_COLS, d = col % ACC_COLS;
+    float s = 0.f;
+    for (int b = 0; b < B; ++b)
+        for (int tl = 0; tl < nT; ++tl)
+            s += part[((((size_t)b * HP + hp) * nT + tl) * N + n) * ACC_COLS + d];
+    dW[(size_t)n * D + col] = s;
+}
+
+}  // namespace tcb
+
+bool flash_bwd_tc_supported(int H, int N, int K) {
+    return (H % tcb::HPC) == 0 && N == tcb::N && K <= tcb::MAX_SLOTS && tcb::smem_layout(K).total <= 227 * 1024;
+}
+
+size_t flash_bwd_tc_ws(int64_t B, int64_t H, int64_t T) {
+    const int64_t nT = (T + MBEMA_TILE_T - 1) / MBEMA_TILE_T;
+    return 256 + (size_t)(B * (H / tcb::HPC) * nT) * tcb::N * tcb::ACC_COLS * sizeof(float) + 256;
+}
+
+int flash_bwd_tc(FlashArgs a, float* dW, void* ws, cudaStream_t st) {
+    const int D = a.H * tcb::HD;
+    int* status = reinterpret_cast<int*>((reinterpret_cast<uintptr_t>(ws) + 255) & ~uintptr_t(255));
+    a.dW_part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(status) + 256);
+    MBEMA_CUDA_TRY(cudaMemsetAsync(status, 0, 256, st));
+    MBEMA_CUDA_TRY(cudaMemsetAsync(a.dEk, 0, (size_t)a.B * a.K * D * sizeof(float), st));
+    MBEMA_CUDA_TRY(cudaMemsetAsync(a.dEv, 0, (size_t)a.B * a.K * D * sizeof(float), st));
+    const tcb::Smem L = tcb::smem_layout(a.K);
+    dim3 grid(a.nT, a.H / tcb::HPC, a.B);
+    if (a.silu) {
+        MBEMA_CUDA_TRY(cudaFuncSetAttribute(tcb::k_flash_bwd_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total));
+        tcb::k_flash_bwd_tc<true><<<grid, tcb::THREADS, L.total, st>>>(a, status);
+    } else {
+        MBEMA_CUDA_TRY(cudaFuncSetAttribute(tcb::k_flash_bwd_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total));
+        tcb::k_flash_bwd_tc<false><<<grid, tcb::THREADS, L.total, st>>>(a, status);
+    }
+    int rc = check_launch();
+    if (rc) return rc;
+    const int total = tcb::N * D;
+    tcb::k_flash_dw_reduce_tc<<<(total + 255) / 256, 256, 0, st>>>(a.dW_part, dW, a.B, a.H / tcb::HPC, a.nT, D);
+    return check_launch();
+}
+
+}  // namespace mbema

@@ -352,6 +352,9 @@ class FlashEMAFunction(torch.autograd.Function):
                                  _stream())
         telemetry.end("mbema_flash_bwd", _ev)
         _lib.check(rc, "mbema_flash_bwd")
+        if mode == _lib.MODE_TC_BF16:
+            global _last_tc_workspace
+            _last_tc_workspace = ws
         qd, kd, vd, wd = ctx.in_dtypes
         return (dQ.to(qd), None, dEk.to(kd), dEv.to(vd), dW.to(wd), None, None, None, None, None, None, None)
 
