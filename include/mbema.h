@@ -60,6 +60,7 @@ extern "C" {
 #define MBEMA_ERR_CUDA 5
 #define MBEMA_ERR_DTYPE 6
 #define MBEMA_ERR_ALIGN 7
+#define MBEMA_ERR_STATIC_LIMIT 8
 
 int mbema_version(void);
 const char* mbema_strerror(int code);
@@ -81,6 +82,25 @@ size_t mbema_query_scan_workspace_bytes(int64_t B, int64_t T);
 int mbema_query_scan(const int64_t* x, const float* rhos, const float* c_init, const int64_t* c_init_keys,
                      const int32_t* doc_ids, float* C_seq, int64_t B, int64_t T, int64_t N, int64_t K,
                      int flags, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Query-side scan for callers that cannot allocate device memory (no counterpart in the reference).
+ * Some hosts hand a library nothing but input and output buffers: a serving loop with a fixed memory budget
+ * where cudaMalloc (and the device-wide synchronisation it implies) is off limits, or a plugin boundary that
+ * offers no allocator at all.  This variant of mbema_query_scan takes no workspace: its index scratch is a fixed
+ * array inside the library's device image (about 0.5 MB, resident on every GPU that loads the library until the
+ * process exits).  It performs no cudaMalloc / cudaFree and calls no allocating library routine.
+ *   limits: B * T <= 32768 tokens and B <= 1024, otherwise MBEMA_ERR_STATIC_LIMIT; all other arguments, limits
+ *           and results as mbema_query_scan.
+ *   The first call on each device looks up the array's device address (cudaGetSymbolAddress) with that device
+ *   current; make that first call outside of any stream capture.
+ *   All calls share the one array and it keeps the previous call's contents (nothing in it needs to start at
+ *   zero: every entry that is read is written earlier in the same call).  Two calls that overlap on the GPU,
+ *   e.g. on different streams, race on it: serialise them.
+ * ---------------------------------------------------------------------------------------------- */
+int mbema_query_scan_static(const int64_t* x, const float* rhos, const float* c_init, const int64_t* c_init_keys,
+                            const int32_t* doc_ids, float* C_seq, int64_t B, int64_t T, int64_t N, int64_t K,
+                            int flags, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Slot-state snapshots at the start of every MBEMA_TILE_T-step time tile, plus what the attention

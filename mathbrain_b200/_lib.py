@@ -22,6 +22,7 @@ SIGNATURES = {
     "mbema_last_cuda_error": (ctypes.c_char_p, []),
     "mbema_query_scan_workspace_bytes": (_sz, [_i64, _i64]),
     "mbema_query_scan": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
+    "mbema_query_scan_static": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
     "mbema_tile_states_workspace_bytes": (_sz, [_i64, _i64]),
     "mbema_tile_states": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
     "mbema_qgate_fwd": (_i32, [_vp, _i32, _vp, _i32, _vp, _vp, _vp, _f32, _vp, _i32, _vp, _vp, _i64, _i64, _i32, _vp]),

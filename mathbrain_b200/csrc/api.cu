@@ -26,6 +26,7 @@ extern "C" const char* mbema_strerror(int code) {
         case MBEMA_ERR_CUDA: return "CUDA runtime error (see mbema_last_cuda_error)";
         case MBEMA_ERR_DTYPE: return "unknown dtype code";
         case MBEMA_ERR_ALIGN: return "pointer not 16-byte aligned";
+        case MBEMA_ERR_STATIC_LIMIT: return "problem larger than the fixed scratch of the allocation-free entry point (B*T <= 32768, B <= 1024)";
         default: return "unknown error code";
     }
 }

@@ -337,3 +337,45 @@ extern "C" int mbema_tile_states(const int64_t* x, const int64_t* unique, const 
     MBEMA_CUDA_TRY(cudaMemcpyAsync(kcount, w.n_valid, (size_t)B * sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
     return MBEMA_OK;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Query scan without any allocation on the caller's side: the index scratch lives in a fixed device array.
+// ------------------------------------------------------------------------------------------------
+#define MBEMA_STATIC_SCAN_MAX_TOKENS 32768   /* B * T */
+#define MBEMA_STATIC_SCAN_MAX_BATCH 1024
+
+namespace mbema {
+// Scratch of the allocation-free scan: 4 int32 per token + 2 per sample, plus alignment slack (~0.5 MB).  Every GPU
+// that loads the library carries this array until the process exits.
+static __device__ __align__(256) int32_t g_static_scan_scratch[4 * MBEMA_STATIC_SCAN_MAX_TOKENS + 2 * MBEMA_STATIC_SCAN_MAX_BATCH + 128];
+static constexpr int MAX_DEVICES = 64;
+static void* g_static_scan_addr[MAX_DEVICES] = {nullptr};   // device address of the array, per device, filled on first use
+}  // namespace mbema
+
+extern "C" int mbema_query_scan_static(const int64_t* x, const float* rhos, const float* c_init,
+                                       const int64_t* c_init_keys, const int32_t* doc_ids, float* C_seq, int64_t B,
+                                       int64_t T, int64_t N, int64_t K, int flags, void* stream) {
+    int rc = check_index_args(B, T, N, K);
+    if (rc) return rc;
+    if (B == 0) return MBEMA_OK;
+    if (B * T > MBEMA_STATIC_SCAN_MAX_TOKENS || B > MBEMA_STATIC_SCAN_MAX_BATCH) return MBEMA_ERR_STATIC_LIMIT;
+    if (!x || !rhos || !C_seq) return MBEMA_ERR_NULL;
+    if ((c_init == nullptr) != (c_init_keys == nullptr)) return MBEMA_ERR_NULL;
+    int dev = 0;
+    MBEMA_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES) return MBEMA_ERR_UNSUPPORTED;
+    if (g_static_scan_addr[dev] == nullptr) {
+        // In host code the array's name is only a handle; the kernels need its address on the current device.
+        void* p = nullptr;
+        MBEMA_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scan_scratch));
+        g_static_scan_addr[dev] = p;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    IndexWs w = carve_index_ws(g_static_scan_addr[dev], B, T);
+    rc = launch_sort_link(x, c_init_keys, w, B, T, c_init_keys ? K : 0, st);
+    if (rc) return rc;
+    dim3 grid((unsigned)((T + CHAIN_WARPS - 1) / CHAIN_WARPS), (unsigned)B);
+    k_chain_scan<<<grid, CHAIN_WARPS * 32, 0, st>>>(w, rhos, c_init, doc_ids, C_seq, (int)T, (int)N, (int)K,
+                                                    (flags & MBEMA_FLAG_CBASE_EXTRA_DECAY) ? 1 : 0);
+    return check_launch();
+}
