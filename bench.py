@@ -296,7 +296,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--mode", default=os.environ.get("MBEMA_BENCH_MODE", "fp32"), choices=["fp32", "tc_bf16"])
+    ap.add_argument("--mode", default=os.environ.get("MBEMA_BENCH_MODE", "tc_bf16"), choices=["fp32", "tc_bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd"],
                     help="run a small one-layer attention workload (for ncu captures) instead of the benchmark")

@@ -8,8 +8,8 @@
 // The epilogue threads read the accumulators of (1) twice (two passes keep the register footprint at one 32-column
 // chunk): pass 1 forms the score and dO.V, giving p = exp(s - LSE) and ds; pass 2 recomputes the gate and writes the
 // three bf16 operand tiles of (2) and (3) to shared memory (128-byte-swizzled, "MN-major": the tile row is the time
-// step, which is the contraction index).  dQ stays in registers for the whole slot loop.  q and dO are held as
-// packed bf16 pairs.  Every wait is bounded (see sm100_ptx.cuh).
+// step, which is the contraction index).  dQ is accumulated in the thread's own TMEM lane (tcgen05.ld / tcgen05.st),
+// which keeps 64 registers free; q and dO are held as packed bf16 pairs.  Every wait is bounded (see sm100_ptx.cuh).
 #include "flash.cuh"
 #include "sm100_ptx.cuh"
 
@@ -33,6 +33,7 @@ static constexpr int ACC_COLS = HPC * HD;
 static constexpr int COL_DW = NACC * ACC_COLS;     // TMEM column of dW^T [128 d x N]
 static constexpr int COL_DEK = COL_DW + N;         // TMEM column of the dE_k column sums (16 columns, all equal)
 static constexpr int COL_DEV = COL_DEK + 16;
+static constexpr int COL_DQ = 384;                 // dQ accumulators [128 t x (2 heads x 64)] fp32, one row per thread
 static constexpr int TMEM_COLS = 512;
 static constexpr int PD = 3, RING = PD + 1;
 static constexpr int RING_STAGE_BYTES = 256 + 2 * ACC_COLS * 4;
@@ -319,7 +320,6 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
         const size_t qoff = (((size_t)b * a.H + h) * a.T + t) * HD;
         const bool row_ok = t < Lb;
         uint32_t q2[HD / 2], do2[HD / 2];     // q / sqrt(hd) and dO as packed bf16 pairs
-        float dq[HD];
         float drow = 0.f;
 #pragma unroll
         for (int i = 0; i < HD; i += 4) {
@@ -331,10 +331,18 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             do2[i / 2] = pack_bf16x2(g.x, g.y);
             do2[i / 2 + 1] = pack_bf16x2(g.z, g.w);
             drow += g.x * ov.x + g.y * ov.y + g.z * ov.z + g.w * ov.w;
-            dq[i] = dq[i + 1] = dq[i + 2] = dq[i + 3] = 0.f;
         }
         const float lse = row_ok ? a.LSE[((size_t)b * a.H + h) * a.T + t] : 0.f;
         const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t t_dq = t_lane + (uint32_t)(COL_DQ + wg * HD);
+        {
+            float z16[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) z16[j] = 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_st_32x32b_x16(t_dq + c * 16, z16);
+            tmem_wait_st();
+        }
         unsigned char* zrow = Z_sh + wg * ATOM_BYTES + row * 128;     // + kind * HPC * ATOM_BYTES + swizzled chunk
         float* dE_out = (wg == 0 ? a.dEk : a.dEv) + (size_t)b * a.K * D + hp * ACC_COLS + row;   // + slot * D
         const uint32_t t_de = t_lane + (wg == 0 ? COL_DEK : COL_DEV);
@@ -383,28 +391,29 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                 tmem_wait_ld();
                 atomicAdd(dE_out + (size_t)slot_sh[i - 1] * D, v);
             }
-            // ---- pass 2: gate again, gradients, operand tiles of the dW / dE products
+            // ---- pass 2: gate again, gradients, operand tiles of the dW / dE products (16 columns at a time)
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                float pre[32];
-                tmem_ld_32x32b_x32(t_acc + c * 32, pre);
+            for (int c = 0; c < 4; ++c) {
+                float pre[16], dq[16];
+                tmem_ld_32x32b_x16(t_acc + c * 16, pre);
+                tmem_ld_32x32b_x16(t_dq + c * 16, dq);
                 tmem_wait_ld();
 #pragma unroll
-                for (int j8 = 0; j8 < 4; ++j8) {          // 8 columns -> one 16-byte chunk per tile
+                for (int j8 = 0; j8 < 2; ++j8) {          // 8 columns -> one 16-byte chunk per tile
                     uint32_t zp[4], zk[4], zv[4];
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        const int j = c * 32 + j8 * 8 + half * 4;
-                        const float4 e1 = *reinterpret_cast<const float4*>(ek + j);
-                        const float4 e2 = *reinterpret_cast<const float4*>(ev + j);
-                        const float ee1[4] = {e1.x, e1.y, e1.z, e1.w}, ee2[4] = {e2.x, e2.y, e2.z, e2.w};
-                        float o_p[4], o_k[4], o_v[4];
+                    for (int pr = 0; pr < 4; ++pr) {      // column pairs
+                        const int j = c * 16 + j8 * 8 + pr * 2;
+                        const float2 e1 = *reinterpret_cast<const float2*>(ek + j);
+                        const float2 e2 = *reinterpret_cast<const float2*>(ev + j);
+                        const uint32_t qq = q2[j / 2], dd = do2[j / 2];
+                        const float qv[2] = {bf16_lo(qq), bf16_hi(qq)};
+                        const float dv[2] = {bf16_lo(dd), bf16_hi(dd)};
+                        const float ee1[2] = {e1.x, e1.y}, ee2[2] = {e2.x, e2.y};
+                        float o_p[2], o_k[2], o_v[2];
 #pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            const uint32_t qq = q2[(j + v) / 2], dd = do2[(j + v) / 2];
-                            const float qv = (v & 1) ? bf16_hi(qq) : bf16_lo(qq);
-                            const float dv = (v & 1) ? bf16_hi(dd) : bf16_lo(dd);
-                            const float hh = pre[j8 * 8 + half * 4 + v];
+                        for (int v = 0; v < 2; ++v) {
+                            const float hh = pre[j8 * 8 + pr * 2 + v];
                             float g, dsl;
                             if (SILU) {
                                 const float th = tanh_approx(hh);
@@ -415,21 +424,23 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                                 g = hh;
                                 dsl = 1.0f;
                             }
-                            dq[j + v] = fmaf(dsq, ee1[v] * g, dq[j + v]);
-                            o_k[v] = dsr * (qv * g);
-                            o_v[v] = p * (dv * g);
-                            o_p[v] = fmaf(dsr, qv * ee1[v], p * (dv * ee2[v])) * dsl;
+                            dq[j8 * 8 + pr * 2 + v] = fmaf(dsq, ee1[v] * g, dq[j8 * 8 + pr * 2 + v]);
+                            o_k[v] = dsr * (qv[v] * g);
+                            o_v[v] = p * (dv[v] * g);
+                            o_p[v] = fmaf(dsr, qv[v] * ee1[v], p * (dv[v] * ee2[v])) * dsl;
                         }
-                        zp[half * 2] = pack_bf16x2(o_p[0], o_p[1]); zp[half * 2 + 1] = pack_bf16x2(o_p[2], o_p[3]);
-                        zk[half * 2] = pack_bf16x2(o_k[0], o_k[1]); zk[half * 2 + 1] = pack_bf16x2(o_k[2], o_k[3]);
-                        zv[half * 2] = pack_bf16x2(o_v[0], o_v[1]); zv[half * 2 + 1] = pack_bf16x2(o_v[2], o_v[3]);
+                        zp[pr] = pack_bf16x2(o_p[0], o_p[1]);
+                        zk[pr] = pack_bf16x2(o_k[0], o_k[1]);
+                        zv[pr] = pack_bf16x2(o_v[0], o_v[1]);
                     }
-                    const int chunk = ((c * 4 + j8) ^ (row & 7)) << 4;
-                    *reinterpret_cast<uint4*>(zrow + 0 * HPC * ATOM_BYTES + chunk) = make_uint4(zp[0], zp[1], zp[2], zp[3]);
-                    *reinterpret_cast<uint4*>(zrow + 1 * HPC * ATOM_BYTES + chunk) = make_uint4(zk[0], zk[1], zk[2], zk[3]);
-                    *reinterpret_cast<uint4*>(zrow + 2 * HPC * ATOM_BYTES + chunk) = make_uint4(zv[0], zv[1], zv[2], zv[3]);
+                    const int chunk = ((c * 2 + j8) ^ (row & 7)) << 4;
+                    st_shared_v4(zrow + 0 * HPC * ATOM_BYTES + chunk, zp[0], zp[1], zp[2], zp[3]);
+                    st_shared_v4(zrow + 1 * HPC * ATOM_BYTES + chunk, zk[0], zk[1], zk[2], zk[3]);
+                    st_shared_v4(zrow + 2 * HPC * ATOM_BYTES + chunk, zv[0], zv[1], zv[2], zv[3]);
                 }
+                tmem_st_32x32b_x16(t_dq + c * 16, dq);
             }
+            tmem_wait_st();
             fence_proxy_async_smem();
             tc_fence_before_sync();
             __syncwarp();
@@ -445,10 +456,16 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             tmem_wait_ld();
             atomicAdd(dE_out + (size_t)slot_sh[n_slots - 1] * D, v);
         }
-        if (t < a.T) {
 #pragma unroll
-            for (int i = 0; i < HD; i += 4)
-                *reinterpret_cast<float4*>(a.dQ + qoff + i) = make_float4(dq[i], dq[i + 1], dq[i + 2], dq[i + 3]);
+        for (int c = 0; c < 4; ++c) {
+            float dq[16];
+            tmem_ld_32x32b_x16(t_dq + c * 16, dq);
+            tmem_wait_ld();
+            if (t < a.T) {
+#pragma unroll
+                for (int i = 0; i < 16; i += 4)
+                    *reinterpret_cast<float4*>(a.dQ + qoff + c * 16 + i) = make_float4(dq[i], dq[i + 1], dq[i + 2], dq[i + 3]);
+            }
         }
         if (wg == 0) {   // dW^T accumulator: lane = column d of the head pair, TMEM columns = n
             float acc[32];
