@@ -110,7 +110,8 @@ int mbema_query_scan_static(const int64_t* x, const float* rhos, const float* c_
  *   out: tile_state [B, nT, K, N] f32 with nT = ceil(T / MBEMA_TILE_T), immediately followed in the same buffer
  *                   by the same values as bf16 [B, nT, K, N] (6 bytes per element in total)
  *        tok_state  [B, T, N]     f32  state of x[b,t]'s own slot just before step t (0 if unlisted)
- *        kcount     [B]           i32  number of valid (>= 0) entries of unique[b,:]
+ *        kcount     [2B]          i32  [0,B): number of valid (>= 0) entries of unique[b,:];
+ *                                       [B,2B): sample indices by decreasing count (launch order of the attention CTAs)
  *   flags: MBEMA_FLAG_CBASE_EXTRA_DECAY.
  * ---------------------------------------------------------------------------------------------- */
 size_t mbema_tile_states_workspace_bytes(int64_t B, int64_t T);

@@ -12,6 +12,7 @@ struct FlashArgs {
     const long long* unique;
     const float* tile_state; const float* tok_state;
     const int* kcount; const int* seq_lens;
+    const int* order;   // [B] sample processed by blockIdx.z (heaviest first), or null
     float* O; float* LSE;
     // backward only
     const void* dO; int do_dt;

@@ -21,6 +21,7 @@ static FlashArgs pack(const void* Q, int q_dtype, const int64_t* x, const void* 
     a.Q = Q; a.q_dt = q_dtype; a.x = (const long long*)x; a.Ek = E_k; a.Ev = E_v; a.e_dt = e_dtype;
     a.W = W_pe; a.rhos = rhos; a.unique = (const long long*)unique; a.tile_state = tile_state;
     a.tok_state = tok_state; a.kcount = kcount; a.seq_lens = seq_lens;
+    a.order = kcount + B;
     a.B = (int)B; a.H = (int)H; a.T = (int)T; a.N = (int)N; a.K = (int)K;
     a.nT = (int)((T + MBEMA_TILE_T - 1) / MBEMA_TILE_T);
     a.v_total = (float)V_total;

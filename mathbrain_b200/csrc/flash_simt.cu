@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(FS_THREADS) k_flash_fwd_simt(FlashArgs a) {
     int* tok_sh = reinterpret_cast<int*>(l2r_sh + round4(N));
 
     const int half = blockIdx.x & 1, tile = blockIdx.x >> 1;
-    const int h = blockIdx.y, b = blockIdx.z;
+    const int h = blockIdx.y, b = a.order ? a.order[blockIdx.z] : (int)blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31;
     const int tr = tid >> 2, dg = tid & 3;
     const int D = a.H * FS_HD;
@@ -187,7 +187,7 @@ __global__ void __launch_bounds__(FS_THREADS) k_flash_bwd_simt(FlashArgs a) {
     float* Zp = Zv + FS_ROWS * FS_ZLD;
 
     const int half = blockIdx.x & 1, tile = blockIdx.x >> 1;
-    const int h = blockIdx.y, b = blockIdx.z;
+    const int h = blockIdx.y, b = a.order ? a.order[blockIdx.z] : (int)blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31;
     const int tr = tid >> 2, dg = tid & 3;
     const int D = a.H * FS_HD;

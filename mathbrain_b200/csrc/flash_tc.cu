@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
     Bars* bars = reinterpret_cast<Bars*>(sm + L.bar_off);
     volatile int* abort_flag = &bars->abort_flag;
 
-    const int tile = blockIdx.x, hp = blockIdx.y, b = blockIdx.z;
+    const int tile = blockIdx.x, hp = blockIdx.y, b = a.order ? a.order[blockIdx.z] : (int)blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int D = a.H * HD;
     const int t0 = tile * TM;

@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
     uint64_t* a_free = reinterpret_cast<uint64_t*>(sm + L.bar_off + 96);   // [NA] A/E stage released by product (2)
     volatile int* abort_flag = &bars->abort_flag;
 
-    const int tile = blockIdx.x, hp = blockIdx.y, b = blockIdx.z;
+    const int tile = blockIdx.x, hp = blockIdx.y, b = a.order ? a.order[blockIdx.z] : (int)blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int D = a.H * HD;
     const int t0 = tile * TM;
@@ -183,7 +183,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
 
     if (!is_epi) {
         // ============================================================ producer warpgroup
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
         const uint32_t idesc_gate = umma_idesc_bf16(TM, ACC_COLS, 0, 0);      // A, B K-major
         const uint32_t idesc_dw = umma_idesc_bf16(ACC_COLS, N, 1, 1);         // A = dpre (MN-major), B = state tile (MN-major)
         const uint32_t idesc_de = umma_idesc_bf16(ACC_COLS, 16, 1, 0);        // A = Z tile (MN-major), B = ones (K-major)
@@ -314,7 +314,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
         if (tid == EPI_THREADS && n_slots > 0) issue_grad_products(n_slots - 1);
     } else {
         // ============================================================ epilogue warpgroups: a thread per time step, a head per warpgroup
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
         const int wg = warp >> 2;
         const int h = hp * HPC + wg;
         const size_t qoff = (((size_t)b * a.H + h) * a.T + t) * HD;
@@ -370,8 +370,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
 #pragma unroll
                     for (int v = 0; v < 4; ++v) {
                         const uint32_t qq = q2[(j + v) / 2], dd = do2[(j + v) / 2];
-                        const float qv = (v & 1) ? bf16_hi(qq) : bf16_lo(qq);
-                        const float dv = (v & 1) ? bf16_hi(dd) : bf16_lo(dd);
+                        const float qv = (v & 1) ? bf16_hi_pinned(qq) : bf16_lo_pinned(qq);
+                        const float dv = (v & 1) ? bf16_hi_pinned(dd) : bf16_lo_pinned(dd);
                         const float hh = pre[jj + v];
                         const float g = SILU ? fmaf(hh, tanh_approx(hh), hh) : hh;
                         sp[v & 1] = fmaf(g * qv, ee1[v], sp[v & 1]);
@@ -407,8 +407,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                         const float2 e1 = *reinterpret_cast<const float2*>(ek + j);
                         const float2 e2 = *reinterpret_cast<const float2*>(ev + j);
                         const uint32_t qq = q2[j / 2], dd = do2[j / 2];
-                        const float qv[2] = {bf16_lo(qq), bf16_hi(qq)};
-                        const float dv[2] = {bf16_lo(dd), bf16_hi(dd)};
+                        const float qv[2] = {bf16_lo_pinned(qq), bf16_hi_pinned(qq)};
+                        const float dv[2] = {bf16_lo_pinned(dd), bf16_hi_pinned(dd)};
                         const float ee1[2] = {e1.x, e1.y}, ee2[2] = {e2.x, e2.y};
                         float o_p[2], o_k[2], o_v[2];
 #pragma unroll

@@ -264,6 +264,24 @@ k_tile_states(IndexWs w, const int64_t* __restrict__ unique, const float* __rest
     }
 }
 
+// order[r] = sample with the r-th largest number of valid slots (ties by index): heavy samples are scheduled first
+__global__ void k_slot_order(const int32_t* __restrict__ n_valid, int32_t* __restrict__ kcount, int B) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B) return;
+    const int mine = n_valid[b];
+    kcount[b] = mine;
+    int rank = 0;
+    if (B <= 4096) {
+        for (int j = 0; j < B; ++j) {
+            const int o = n_valid[j];
+            rank += (o > mine || (o == mine && j < b)) ? 1 : 0;
+        }
+    } else {
+        rank = b;
+    }
+    kcount[B + rank] = b;
+}
+
 static int launch_sort_link(const int64_t* x, const int64_t* keys, IndexWs w, int64_t B, int64_t T, int64_t K,
                             cudaStream_t st) {
     int Tp = 2;
@@ -334,8 +352,8 @@ extern "C" int mbema_tile_states(const int64_t* x, const int64_t* unique, const 
     k_tile_states<<<g2, CHAIN_WARPS * 32, 0, st>>>(w, unique, rhos, c_base, tile_state, (int)T, (int)N, (int)K, nT, extra);
     rc = check_launch();
     if (rc) return rc;
-    MBEMA_CUDA_TRY(cudaMemcpyAsync(kcount, w.n_valid, (size_t)B * sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
-    return MBEMA_OK;
+    k_slot_order<<<(unsigned)((B + 127) / 128), 128, 0, st>>>(w.n_valid, kcount, (int)B);
+    return check_launch();
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -209,5 +209,18 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
+// Unpack variants the compiler may not hoist out of a loop: keeping loop-invariant operands packed in registers is
+// the point (hoisting the unpack would double their register footprint).
+__device__ __forceinline__ float bf16_lo_pinned(uint32_t v) {
+    uint32_t r;
+    asm volatile("shl.b32 %0, %1, 16;" : "=r"(r) : "r"(v));
+    return __uint_as_float(r);
+}
+__device__ __forceinline__ float bf16_hi_pinned(uint32_t v) {
+    uint32_t r;
+    asm volatile("and.b32 %0, %1, 0xffff0000;" : "=r"(r) : "r"(v));
+    return __uint_as_float(r);
+}
+
 }  // namespace ptx
 }  // namespace mbema

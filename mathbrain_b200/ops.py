@@ -107,7 +107,7 @@ class _Telemetry:
     selected entry points (recorded on the launching stream)."""
 
     # kernels launched by one call of each C entry point
-    KERNELS = {"mbema_query_scan": 2, "mbema_tile_states": 3, "mbema_qgate_fwd": 1, "mbema_qgate_bwd": 2,
+    KERNELS = {"mbema_query_scan": 2, "mbema_tile_states": 4, "mbema_qgate_fwd": 1, "mbema_qgate_bwd": 2,
                "mbema_flash_fwd": 1, "mbema_flash_bwd": 2}
 
     def __init__(self):
@@ -199,7 +199,7 @@ class TileStates:
     """Opaque result of precompute_boundaries, consumed by FlashEMAFunction."""
     tile_state: torch.Tensor            # [B, nT, K, N] f32 view of a buffer that also holds a bf16 copy behind it
     tok_state: torch.Tensor             # [B, T, N] f32
-    kcount: torch.Tensor                # [B] i32
+    kcount: torch.Tensor                # [2B] i32: valid-slot counts, then the sample order (heaviest first)
     seq_lens: Optional[torch.Tensor]    # [B] i32 or None
     unique: torch.Tensor                # [B, K] i64, the slot list the snapshots were built for
     shape: tuple                        # (B, T, K, N)
@@ -233,7 +233,7 @@ def precompute_boundaries(x, unique_tensor, rhos, Br, c_init=None, doc_ids=None,
     tile_buf = torch.empty(n_el * 6 + 16, dtype=torch.uint8, device=x.device)   # fp32 block, then the bf16 copy
     tile_state = tile_buf[: n_el * 4].view(torch.float32).view(B, nT, K, N)
     tok_state = torch.empty(B, L, N, dtype=torch.float32, device=x.device)
-    kcount = torch.empty(B, dtype=torch.int32, device=x.device)
+    kcount = torch.empty(2 * B, dtype=torch.int32, device=x.device)   # counts, then samples by decreasing count
     ws = _workspace(lib.mbema_tile_states_workspace_bytes(B, L), x.device)
     flags = _lib.FLAG_CBASE_EXTRA_DECAY if _OPTIONS["cbase_extra_decay"] else 0
     _ev = telemetry.begin("mbema_tile_states")
