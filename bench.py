@@ -161,17 +161,10 @@ class HotPath:
                 s = O.detach().float().sum()
                 acc = s if acc is None else acc + s
             if self.dist:
-                import torch.distributed as dist
-                if self.dE_vocab is None:
-                    self.dE_vocab = torch.zeros(c["V"], D, device=self.dev)
-                self.dE_vocab.zero_()
-                idx = unique_tensor.clamp_min(0).reshape(-1)
-                for lay in self.layers:
-                    gsum = (lay["E_k"].grad.float() + lay["E_v"].grad.float()) * pad_mask.unsqueeze(-1)
-                    self.dE_vocab.index_add_(0, idx, gsum.reshape(-1, D))
-                flat = torch.cat([p.grad.reshape(-1).float() for p in self.params])
-                dist.all_reduce(flat)
-                dist.all_reduce(self.dE_vocab)
+                from mathbrain_b200 import dp
+                grads = [lay[k].grad for lay in self.layers for k in ("E_k", "E_v")]
+                self.dE_vocab = dp.slot_embedding_grad(grads, unique_tensor, c["V"], out=self.dE_vocab)
+                dp.allreduce_gradients(self.params, extra=[self.dE_vocab])
             self.result.copy_(acc.reshape(1))
 
     def step_resident(self):

@@ -1,0 +1,45 @@
+"""Data-parallel plumbing of the hot path: one process per GPU, batch sharded, one gradient exchange per step.
+
+Samples are independent on this path (no cross-sample operation), so ranks never exchange activations; the only
+collective is the sum of the parameter gradients and of the vocabulary-sized slot-embedding gradient
+(`torch.distributed` all-reduce; NCCL over NVLink on GPUs, gloo in the CPU tests).
+"""
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(n_items, rank, world):
+    """Contiguous, balanced split of n_items over `world` ranks: [lo, hi) of `rank`."""
+    base, rem = divmod(n_items, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+def slot_embedding_grad(dE_list, unique_tensor, vocab, out=None):
+    """Scatter-add per-sample slot gradients [B, K, D] (one tensor per layer / per K,V) into a [vocab, D] fp32
+    buffer: what the embedding table receives from the listed slots.  Entries of `unique_tensor` < 0 are skipped."""
+    D = dE_list[0].shape[-1]
+    if out is None:
+        out = torch.zeros(vocab, D, dtype=torch.float32, device=dE_list[0].device)
+    else:
+        out.zero_()
+    valid = (unique_tensor >= 0).unsqueeze(-1)
+    idx = unique_tensor.clamp_min(0).reshape(-1)
+    for g in dE_list:
+        out.index_add_(0, idx, (g.float() * valid).reshape(-1, D))
+    return out
+
+
+def allreduce_gradients(params, extra=(), group=None):
+    """Sum the .grad of `params` (flattened into one bucket) and every tensor in `extra` over all ranks, in place."""
+    grads = [p.grad for p in params if p.grad is not None]
+    if grads:
+        flat = torch.cat([g.reshape(-1).float() for g in grads])
+        dist.all_reduce(flat, group=group)
+        off = 0
+        for g in grads:
+            n = g.numel()
+            g.copy_(flat[off:off + n].view_as(g))
+            off += n
+    for t in extra:
+        dist.all_reduce(t, group=group)
