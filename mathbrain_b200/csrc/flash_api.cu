@@ -61,7 +61,8 @@ extern "C" int mbema_flash_fwd(const void* Q, int q_dtype, const int64_t* x, con
 extern "C" size_t mbema_flash_bwd_workspace_bytes(int64_t B, int64_t H, int64_t T, int64_t hd, int64_t N, int64_t K,
                                                   int mode) {
     (void)hd;
-    size_t need = flash_bwd_simt_ws(B, H, T, N);
+    // in tensor-core mode the first 512 bytes hold the kernel status word, whichever kernel ends up running
+    size_t need = flash_bwd_simt_ws(B, H, T, N) + (mode == MBEMA_MODE_TC_BF16 ? 512 : 0);
     if (mode == MBEMA_MODE_TC_BF16 && flash_bwd_tc_supported((int)H, (int)N, (int)K)) {
         const size_t tc = flash_bwd_tc_ws(B, H, T);
         if (tc > need) need = tc;
@@ -96,6 +97,10 @@ extern "C" int mbema_flash_bwd(const void* Q, int q_dtype, const int64_t* x, con
     a.O = const_cast<float*>(O); a.LSE = const_cast<float*>(LSE);
     a.dO = dO; a.do_dt = do_dtype; a.dQ = dQ; a.dEk = dE_k; a.dEv = dE_v;
     // tensor-core backward where the shape fits its shared-memory budget (N == 64); otherwise the fp32 kernels
-    if (mode == MBEMA_MODE_TC_BF16 && flash_bwd_tc_supported((int)H, (int)N, (int)K)) return flash_bwd_tc(a, dW_pe, workspace, st);
+    if (mode == MBEMA_MODE_TC_BF16) {
+        if (flash_bwd_tc_supported((int)H, (int)N, (int)K)) return flash_bwd_tc(a, dW_pe, workspace, st);
+        MBEMA_CUDA_TRY(cudaMemsetAsync(workspace, 0, 512, st));   // status word: the fp32 kernels have no bounded waits
+        return flash_bwd_simt(a, dW_pe, static_cast<unsigned char*>(workspace) + 512, st);
+    }
     return flash_bwd_simt(a, dW_pe, workspace, st);
 }

@@ -71,6 +71,32 @@ def test_tc_semantic_switches_and_seq_lens(mb):
     compare_all(out, ref, TOL_BF16)
 
 
+def test_tc_n128_forward_and_mixed_backward(mb):
+    # N = 128 (the long-chunk configuration): tensor-core forward; the backward of this shape runs the fp32 kernels
+    # operand scale 0.1: with 128 bf16 products per pre-activation the bf16 error budget (2e-2) holds for |pre| of a few units
+    inp, c_base, _ = make_case(77, B=2, T=300, N=128, H=2, vocab=500, max_prefix=200, min_hl=4.0, max_hl=500.0, std=0.1)
+    out = run_tc(mb, inp, c_base)
+    ref = oracle_flash(inp, c_base)
+    compare_all(out, ref, TOL_BF16)
+
+
+def test_tc_long_chunk_property(mb):
+    """T = 4096 with bursty repeats (long-chunk stress shape, reduced batch): one chunk equals two half chunks
+    chained through the slot states, and matches the fp32 kernels."""
+    inp, c_base, _ = make_case(91, B=1, T=4096, N=64, H=2, vocab=3000, max_prefix=0, min_hl=1024.0, max_hl=4096.0,
+                               std=0.02, bursty=True, min_fill=4096, holes=False)   # weights at the model's init scale
+    full = run_tc(mb, inp, c_base, with_grad=False)["O"]
+    with mb.options(mode="fp32"):
+        ref = run_flash(mb, inp, c_base, with_grad=False)["O"]
+    assert rel_err(full, ref) < TOL_BF16
+    M = orc.memory_states(inp["x"][:, :2049], inp["unique"], inp["rhos"], c_base, dtype=torch.float64)
+    second = dict(inp)
+    second["x"] = inp["x"][:, 2048:].contiguous()
+    second["Q"] = inp["Q"][:, :, 2048:].contiguous()
+    tail = run_tc(mb, second, M[:, 2048].float(), with_grad=False)["O"]
+    assert rel_err(tail, full[:, :, 2048:]) < 5e-3
+
+
 def test_tc_unsupported_shape_is_refused(mb):
     inp, c_base, _ = make_case(5, B=1, T=64, N=16, H=2, vocab=100, max_prefix=10, min_hl=2.0, max_hl=30.0)
     with pytest.raises(mb._lib.MbemaError):
