@@ -40,7 +40,7 @@ static constexpr int RING_STAGE_BYTES = 256 + 2 * ACC_COLS * 4;
 static constexpr int MAX_SLOTS = 4096;
 
 struct Smem {
-    int a_off, b_off, z_off, ones_off, r_off, e_off, ring_off, tok_off, slot_off, key_off, bar_off, total;
+    int a_off, b_off, z_off, ones_off, r_off, e_off, e2_off, ring_off, tok_off, slot_off, key_off, bar_off, total;
 };
 
 __host__ __device__ inline Smem smem_layout(int K) {
@@ -51,7 +51,8 @@ __host__ __device__ inline Smem smem_layout(int K) {
     s.z_off = o; o += 3 * HPC * ATOM_BYTES;       // dpre, ds*q*g, p*dO*g tiles: [kind][head][128 t][64 d] bf16
     s.ones_off = o; o += 2048;                    // 16 x 64 bf16 ones (B operand of the column sums)
     s.r_off = o; o += TM * N * 2;                 // decay powers rho_n^r as bf16 [128][64] (in-tile restarts only)
-    s.e_off = o; o += NA * 2 * ACC_COLS * 4;
+    s.e_off = o; o += NA * 2 * ACC_COLS * 4;      // E_k / E_v rows as fp32 ...
+    s.e2_off = o; o += NA * 2 * ACC_COLS * 2;     // ... and as bf16 (operands of the packed tile arithmetic)
     s.ring_off = o; o += RING * RING_STAGE_BYTES;
     s.tok_off = o; o += TM * 4;
     s.slot_off = o; o += ((K * 2 + 15) / 16) * 16;
@@ -96,6 +97,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
     unsigned char* ones_sh = sm + L.ones_off;
     __nv_bfloat16* R_sh = reinterpret_cast<__nv_bfloat16*>(sm + L.r_off);
     float* E_sh = reinterpret_cast<float*>(sm + L.e_off);
+    __nv_bfloat16* E2_sh = reinterpret_cast<__nv_bfloat16*>(sm + L.e2_off);
     unsigned char* ring_sh = sm + L.ring_off;
     int* tok_sh = reinterpret_cast<int*>(sm + L.tok_off);
     unsigned short* slot_sh = reinterpret_cast<unsigned short*>(sm + L.slot_off);
@@ -247,14 +249,18 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             const int key = key_sh[i];
             const unsigned char* rg = ring_sh + (i % RING) * RING_STAGE_BYTES;
             {
-                float* dst = E_sh + sa * 2 * ACC_COLS + row;
+                float ekv, evv;
                 if (esize == 4) {
-                    dst[0] = reinterpret_cast<const float*>(rg + 256)[row];
-                    dst[ACC_COLS] = reinterpret_cast<const float*>(rg + 256 + ACC_COLS * 4)[row];
+                    ekv = reinterpret_cast<const float*>(rg + 256)[row];
+                    evv = reinterpret_cast<const float*>(rg + 256 + ACC_COLS * 4)[row];
                 } else {
-                    dst[0] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rg + 256)[row]);
-                    dst[ACC_COLS] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rg + 256 + ACC_COLS * 4)[row]);
+                    ekv = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rg + 256)[row]);
+                    evv = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rg + 256 + ACC_COLS * 4)[row]);
                 }
+                E_sh[sa * 2 * ACC_COLS + row] = ekv;
+                E_sh[sa * 2 * ACC_COLS + ACC_COLS + row] = evv;
+                E2_sh[sa * 2 * ACC_COLS + row] = __float2bfloat16(ekv);
+                E2_sh[sa * 2 * ACC_COLS + ACC_COLS + row] = __float2bfloat16(evv);
             }
             int s = -1;
             {
@@ -354,35 +360,47 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             const float* ek = E_sh + sa * 2 * ACC_COLS + wg * HD;
             const float* ev = ek + ACC_COLS;
             const uint32_t t_acc = t_lane + (uint32_t)(sc * ACC_COLS + wg * HD);
-            // ---- pass 1: score and dO.V
+            // ---- pass 1: gate, its derivative, score and dO.V; gate and derivative are kept as packed bf16 pairs
+            uint32_t g2[HD / 2], dsl2[HD / 2];
             float sp[2] = {0.f, 0.f}, dpp[2] = {0.f, 0.f};
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                float pre[32];
-                tmem_ld_32x32b_x32(t_acc + c * 32, pre);
+            for (int c = 0; c < 4; ++c) {
+                float pre[16];
+                tmem_ld_32x32b_x16(t_acc + c * 16, pre);
                 tmem_wait_ld();
 #pragma unroll
-                for (int jj = 0; jj < 32; jj += 4) {
-                    const int j = c * 32 + jj;
-                    const float4 e1 = *reinterpret_cast<const float4*>(ek + j);
-                    const float4 e2 = *reinterpret_cast<const float4*>(ev + j);
-                    const float ee1[4] = {e1.x, e1.y, e1.z, e1.w}, ee2[4] = {e2.x, e2.y, e2.z, e2.w};
+                for (int pr = 0; pr < 8; ++pr) {
+                    const int j = c * 16 + pr * 2;
+                    const float2 e1 = *reinterpret_cast<const float2*>(ek + j);
+                    const float2 e2 = *reinterpret_cast<const float2*>(ev + j);
+                    const uint32_t qq = q2[j / 2], dd = do2[j / 2];
+                    const float qv[2] = {bf16_lo_pinned(qq), bf16_hi_pinned(qq)};
+                    const float dv[2] = {bf16_lo_pinned(dd), bf16_hi_pinned(dd)};
+                    const float ee1[2] = {e1.x, e1.y}, ee2[2] = {e2.x, e2.y};
+                    float g[2], dsl[2];
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        const uint32_t qq = q2[(j + v) / 2], dd = do2[(j + v) / 2];
-                        const float qv = (v & 1) ? bf16_hi_pinned(qq) : bf16_lo_pinned(qq);
-                        const float dv = (v & 1) ? bf16_hi_pinned(dd) : bf16_lo_pinned(dd);
-                        const float hh = pre[jj + v];
-                        const float g = SILU ? fmaf(hh, tanh_approx(hh), hh) : hh;
-                        sp[v & 1] = fmaf(g * qv, ee1[v], sp[v & 1]);
-                        dpp[v & 1] = fmaf(g * dv, ee2[v], dpp[v & 1]);
+                    for (int v = 0; v < 2; ++v) {
+                        const float hh = pre[pr * 2 + v];
+                        if (SILU) {     // h = x / 2:  SiLU(x) = h + h*th,  SiLU'(x) = (1 + th)/2 * (1 + h - h*th),  th = tanh(h)
+                            const float th = tanh_approx(hh);
+                            g[v] = fmaf(hh, th, hh);
+                            dsl[v] = fmaf(0.5f, th, 0.5f) * (fmaf(hh, 2.0f, 1.0f) - g[v]);
+                        } else {
+                            g[v] = hh;
+                            dsl[v] = 1.0f;
+                        }
+                        sp[v] = fmaf(g[v] * qv[v], ee1[v], sp[v]);
+                        dpp[v] = fmaf(g[v] * dv[v], ee2[v], dpp[v]);
                     }
+                    g2[j / 2] = pack_bf16x2(g[0], g[1]);
+                    dsl2[j / 2] = pack_bf16x2(dsl[0], dsl[1]);
                 }
             }
             const float s = sp[0] + sp[1];
             const float p = row_ok ? __expf(s - lse) : 0.f;
             const float dsr = p * ((dpp[0] + dpp[1]) - drow);     // d loss / d score
             const float dsq = dsr * 0.125f;
+            const uint32_t dsr2 = pack_bf16x2(dsr, dsr), p2 = pack_bf16x2(p, p);
             // ---- column sums of the previous slot (also: its Z tiles have been consumed)
             if (i >= 1) {
                 mbar_wait(&bars->z_done, (uint32_t)((i - 1) & 1), abort_flag);
@@ -391,52 +409,44 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                 tmem_wait_ld();
                 atomicAdd(dE_out + (size_t)slot_sh[i - 1] * D, v);
             }
-            // ---- pass 2: gate again, gradients, operand tiles of the dW / dE products (16 columns at a time)
+            // ---- pass 2: operand tiles of the dW / dE products in packed bf16 arithmetic, dQ in fp32 (TMEM)
+            const uint32_t* ek2 = reinterpret_cast<const uint32_t*>(E2_sh + sa * 2 * ACC_COLS + wg * HD);
+            const uint32_t* ev2 = ek2 + ACC_COLS / 2;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                float pre[16], dq[16];
-                tmem_ld_32x32b_x16(t_acc + c * 16, pre);
+                float dq[16];
                 tmem_ld_32x32b_x16(t_dq + c * 16, dq);
-                tmem_wait_ld();
 #pragma unroll
                 for (int j8 = 0; j8 < 2; ++j8) {          // 8 columns -> one 16-byte chunk per tile
+                    const int w0 = (c * 16 + j8 * 8) / 2;   // first packed pair of the chunk
+                    const uint4 ekp = *reinterpret_cast<const uint4*>(ek2 + w0);
+                    const uint4 evp = *reinterpret_cast<const uint4*>(ev2 + w0);
+                    const uint32_t ekw[4] = {ekp.x, ekp.y, ekp.z, ekp.w}, evw[4] = {evp.x, evp.y, evp.z, evp.w};
                     uint32_t zp[4], zk[4], zv[4];
 #pragma unroll
-                    for (int pr = 0; pr < 4; ++pr) {      // column pairs
-                        const int j = c * 16 + j8 * 8 + pr * 2;
-                        const float2 e1 = *reinterpret_cast<const float2*>(ek + j);
-                        const float2 e2 = *reinterpret_cast<const float2*>(ev + j);
-                        const uint32_t qq = q2[j / 2], dd = do2[j / 2];
-                        const float qv[2] = {bf16_lo_pinned(qq), bf16_hi_pinned(qq)};
-                        const float dv[2] = {bf16_lo_pinned(dd), bf16_hi_pinned(dd)};
-                        const float ee1[2] = {e1.x, e1.y}, ee2[2] = {e2.x, e2.y};
-                        float o_p[2], o_k[2], o_v[2];
-#pragma unroll
-                        for (int v = 0; v < 2; ++v) {
-                            const float hh = pre[j8 * 8 + pr * 2 + v];
-                            float g, dsl;
-                            if (SILU) {
-                                const float th = tanh_approx(hh);
-                                g = fmaf(hh, th, hh);
-                                const float sg = fmaf(0.5f, th, 0.5f);
-                                dsl = fmaf((hh + hh) * sg, 1.0f - sg, sg);     // SiLU'(x), x = 2 h
-                            } else {
-                                g = hh;
-                                dsl = 1.0f;
-                            }
-                            dq[j8 * 8 + pr * 2 + v] = fmaf(dsq, ee1[v] * g, dq[j8 * 8 + pr * 2 + v]);
-                            o_k[v] = dsr * (qv[v] * g);
-                            o_v[v] = p * (dv[v] * g);
-                            o_p[v] = fmaf(dsr, qv[v] * ee1[v], p * (dv[v] * ee2[v])) * dsl;
-                        }
-                        zp[pr] = pack_bf16x2(o_p[0], o_p[1]);
-                        zk[pr] = pack_bf16x2(o_k[0], o_k[1]);
-                        zv[pr] = pack_bf16x2(o_v[0], o_v[1]);
+                    for (int pr = 0; pr < 4; ++pr) {
+                        const uint32_t qq = q2[w0 + pr], dd = do2[w0 + pr], gg = g2[w0 + pr];
+                        zk[pr] = mul_bf16x2(dsr2, mul_bf16x2(qq, gg));                    // ds * q * g
+                        zv[pr] = mul_bf16x2(p2, mul_bf16x2(dd, gg));                      // p * dO * g
+                        const uint32_t t1 = mul_bf16x2(dsr2, mul_bf16x2(qq, ekw[pr]));    // ds * q * E_k
+                        const uint32_t t2 = mul_bf16x2(dd, evw[pr]);                      // dO * E_v
+                        zp[pr] = mul_bf16x2(fma_bf16x2(p2, t2, t1), dsl2[w0 + pr]);       // dgate * SiLU'
                     }
                     const int chunk = ((c * 2 + j8) ^ (row & 7)) << 4;
                     st_shared_v4(zrow + 0 * HPC * ATOM_BYTES + chunk, zp[0], zp[1], zp[2], zp[3]);
                     st_shared_v4(zrow + 1 * HPC * ATOM_BYTES + chunk, zk[0], zk[1], zk[2], zk[3]);
                     st_shared_v4(zrow + 2 * HPC * ATOM_BYTES + chunk, zv[0], zv[1], zv[2], zv[3]);
+                }
+                tmem_wait_ld();
+#pragma unroll
+                for (int jj = 0; jj < 16; jj += 4) {
+                    const int j = c * 16 + jj;
+                    const float4 e1 = *reinterpret_cast<const float4*>(ek + j);
+                    const uint32_t ga = g2[j / 2], gb = g2[j / 2 + 1];
+                    dq[jj] = fmaf(dsq, e1.x * bf16_lo(ga), dq[jj]);
+                    dq[jj + 1] = fmaf(dsq, e1.y * bf16_hi(ga), dq[jj + 1]);
+                    dq[jj + 2] = fmaf(dsq, e1.z * bf16_lo(gb), dq[jj + 2]);
+                    dq[jj + 3] = fmaf(dsq, e1.w * bf16_hi(gb), dq[jj + 3]);
                 }
                 tmem_st_32x32b_x16(t_dq + c * 16, dq);
             }
