@@ -70,7 +70,7 @@ struct Bars {
     uint64_t acc_full[NACC];     // gate UMMAs done + E rows staged                  (2 arrivals)
     uint64_t acc_empty[NACC];    // all epilogue warps finished reading the stage      (EPI_WARPS arrivals)
     uint64_t z_full;             // all epilogue warps wrote their part of the Z tiles (EPI_WARPS arrivals)
-    uint64_t z_done;             // products (2) and (3) of the slot have completed    (1 arrival: commit)
+    uint64_t z_done;             // products (2) and (3) of the slot have completed    (3 arrivals: one commit per issuing warp)
     uint32_t tmem_base;
     int abort_flag;
     int n_slots;
@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
         }
         for (int i = 0; i < NA; ++i) mbar_init(&a_free[i], 1);
         mbar_init(&bars->z_full, EPI_WARPS);
-        mbar_init(&bars->z_done, 1);
+        mbar_init(&bars->z_done, 3);
         bars->abort_flag = *reinterpret_cast<volatile int*>(status);
         fence_barrier_init();
     }
@@ -213,27 +213,35 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        // products (2) and (3) of slot j: issued by one thread once the epilogue has written the Z tiles
+        // products (2) and (3) of slot j, once the epilogue has written the Z tiles.  Issuing a UMMA costs its thread
+        // on the order of a hundred cycles, so the 24 instructions are spread over three warps (dW^T, dE_k, dE_v;
+        // the gate product has the fourth), each committing its own group.
+        const uint64_t d_zp = umma_desc_mn_sw128(z_base + 0 * HPC * ATOM_BYTES, ATOM_BYTES, 1024);
+        const uint64_t d_zk = umma_desc_mn_sw128(z_base + 1 * HPC * ATOM_BYTES, ATOM_BYTES, 1024);
+        const uint64_t d_zv = umma_desc_mn_sw128(z_base + 2 * HPC * ATOM_BYTES, ATOM_BYTES, 1024);
+        const uint64_t d_ones = umma_desc_k_sw128(o_base);
+        const uint64_t d_a0 = umma_desc_mn_sw128(a_base, ATOM_BYTES, 1024);
+        const uint64_t d_ak0 = umma_desc_k_sw128(a_base), d_b0 = umma_desc_k_sw128(b_base);
+        const int role = warp - EPI_WARPS;          // 0: gate, 1: dW^T, 2: dE_k, 3: dE_v
         auto issue_grad_products = [&](int j) {
             mbar_wait(&bars->z_full, (uint32_t)(j & 1), abort_flag);
             tc_fence_after_sync();
-            const uint32_t a_tile = a_base + (j % NA) * ATOM_BYTES;
+            if (role == 1) {
+                const uint64_t d_at = d_a0 + (uint64_t)(((j % NA) * ATOM_BYTES) >> 4);
 #pragma unroll
-            for (int ks = 0; ks < TM / 16; ++ks) {      // contraction over the 128 time steps, 16 per instruction
-                const uint64_t dp = umma_desc_mn_sw128(z_base + 0 * HPC * ATOM_BYTES + ks * 2048, ATOM_BYTES, 1024);
-                const uint64_t st = umma_desc_mn_sw128(a_tile + ks * 2048, ATOM_BYTES, 1024);
-                umma_bf16_ss(tmem_base + COL_DW, dp, st, idesc_dw, (j | ks) != 0 ? 1u : 0u);
-            }
-            const uint64_t ones = umma_desc_k_sw128(o_base);
+                for (int ks = 0; ks < TM / 16; ++ks)      // contraction over the 128 time steps, 16 per instruction
+                    umma_bf16_ss(tmem_base + COL_DW, d_zp + (uint64_t)(ks * (2048 >> 4)), d_at + (uint64_t)(ks * (2048 >> 4)),
+                                 idesc_dw, (j | ks) != 0 ? 1u : 0u);
+                umma_commit(&bars->z_done);
+                umma_commit(&a_free[j % NA]);
+            } else {
+                const uint64_t dz = (role == 2) ? d_zk : d_zv;
+                const uint32_t col = (role == 2) ? COL_DEK : COL_DEV;
 #pragma unroll
-            for (int ks = 0; ks < TM / 16; ++ks) {
-                const uint64_t zk = umma_desc_mn_sw128(z_base + 1 * HPC * ATOM_BYTES + ks * 2048, ATOM_BYTES, 1024);
-                const uint64_t zv = umma_desc_mn_sw128(z_base + 2 * HPC * ATOM_BYTES + ks * 2048, ATOM_BYTES, 1024);
-                umma_bf16_ss(tmem_base + COL_DEK, zk, ones, idesc_de, ks != 0 ? 1u : 0u);
-                umma_bf16_ss(tmem_base + COL_DEV, zv, ones, idesc_de, ks != 0 ? 1u : 0u);
+                for (int ks = 0; ks < TM / 16; ++ks)
+                    umma_bf16_ss(tmem_base + col, dz + (uint64_t)(ks * (2048 >> 4)), d_ones, idesc_de, ks != 0 ? 1u : 0u);
+                umma_commit(&bars->z_done);
             }
-            umma_commit(&bars->z_done);
-            umma_commit(&a_free[j % NA]);
         };
         uint32_t R2[32];
 #pragma unroll
@@ -303,21 +311,22 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             }
             fence_proxy_async_smem();
             named_bar_sync(1, PROD_THREADS);
-            if (tid == EPI_THREADS) {
-                if (i >= NACC) mbar_wait(&bars->acc_empty[sc], (uint32_t)((i / NACC - 1) & 1), abort_flag);
-                tc_fence_after_sync();
+            if (lane == 0) {
+                if (role == 0) {
+                    if (i >= NACC) mbar_wait(&bars->acc_empty[sc], (uint32_t)((i / NACC - 1) & 1), abort_flag);
+                    tc_fence_after_sync();
 #pragma unroll
-                for (int k16 = 0; k16 < 4; ++k16) {
-                    const uint64_t adesc = umma_desc_k_sw128(a_base + sa * ATOM_BYTES + k16 * 32);
-                    const uint64_t bdesc = umma_desc_k_sw128(b_base + k16 * 32);
-                    umma_bf16_ss(tmem_base + (uint32_t)(sc * ACC_COLS), adesc, bdesc, idesc_gate, k16 != 0 ? 1u : 0u);
+                    for (int k16 = 0; k16 < 4; ++k16)
+                        umma_bf16_ss(tmem_base + (uint32_t)(sc * ACC_COLS), d_ak0 + (uint64_t)((sa * ATOM_BYTES + k16 * 32) >> 4),
+                                     d_b0 + (uint64_t)((k16 * 32) >> 4), idesc_gate, k16 != 0 ? 1u : 0u);
+                    umma_commit(&bars->acc_full[sc]);
+                    mbar_arrive(&bars->acc_full[sc]);
+                } else if (i >= 1) {
+                    issue_grad_products(i - 1);
                 }
-                umma_commit(&bars->acc_full[sc]);
-                mbar_arrive(&bars->acc_full[sc]);
-                if (i >= 1) issue_grad_products(i - 1);
             }
         }
-        if (tid == EPI_THREADS && n_slots > 0) issue_grad_products(n_slots - 1);
+        if (lane == 0 && role != 0 && n_slots > 0) issue_grad_products(n_slots - 1);
     } else {
         // ============================================================ epilogue warpgroups: a thread per time step, a head per warpgroup
         asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
