@@ -219,6 +219,52 @@ def profile_case(args):
                       "bwd_ms": tel.elapsed_ms("mbema_flash_bwd"), "status": mb.device_status()}))
 
 
+def decode_case(args):
+    """Streaming decode (64 sequences, V=50257, N=64, 4096 slots seen per sequence, 6 layers): device time per step
+    of [6 x attend, update].  Weights and projected slot embeddings are random; no benchmark line."""
+    import mathbrain_b200 as mb
+    from mathbrain_b200 import synth
+    from mathbrain_b200.decode import DecodeState
+    c = CFG
+    dev = torch.device("cuda", 0)
+    B, V, N, H, D, L, K = 64, c["V"], c["N"], c["H"], c["D"], c["L"], 4096
+    g = torch.Generator().manual_seed(0)
+    rhos = synth.make_rhos(N, c["min_hl"], c["max_hl"]).to(dev)
+    st = DecodeState(B, V, rhos, capacity=K + 512)
+    # warm state: every sequence has seen K distinct slots at random earlier steps
+    for b in range(B):
+        seen = torch.randperm(V, generator=g)[:K]
+        st.active[b, :K] = seen.to(torch.int32).to(dev)
+        st.last_t[b, seen.to(dev)] = torch.randint(0, 8192, (K,), generator=g).to(torch.int32).to(dev)
+        st.state[b, seen.to(dev)] = (torch.rand(K, N, generator=g) * 3 + 1).to(dev)
+    st.n_active.fill_(K)
+    E_k = [(torch.randn(V, D, generator=g) * 0.02).to(torch.bfloat16).to(dev) for _ in range(L)]
+    E_v = [(torch.randn(V, D, generator=g) * 0.02).to(torch.bfloat16).to(dev) for _ in range(L)]
+    W = [(torch.randn(N, D, generator=g) * 0.02).to(dev) for _ in range(L)]
+    q = (torch.randn(B, H, D // H, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+    zipf = synth.Zipf(V)
+    import numpy as np
+    rng = np.random.Generator(np.random.PCG64(1))
+    toks = torch.from_numpy(zipf.draw(rng, B * 40).reshape(40, B)).to(dev)
+    times = []
+    for step in range(40):
+        t_now = 8192 + step
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for l in range(L):
+            st.attend(q, E_k[l], E_v[l], W[l], t_now)
+        st.update(toks[step], t_now)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    st.check_overflow()
+    ms = sorted(times[8:])[len(times[8:]) // 2]
+    bytes_step = B * L * K * (N * 4 + 4 + 2 * D * 2)            # state rows + last_t + E_k/E_v rows per active slot
+    print(json.dumps({"profile_case": "decode", "sequences": B, "active_slots": K, "layers": L, "ms_per_step": ms,
+                      "tokens_per_s": B / ms * 1000.0, "algorithmic_GB_per_step": bytes_step / 1e9,
+                      "achieved_GBps": bytes_step / ms / 1e6, "hbm_peak_GBps": peaks()["hbm"]}))
+
+
 def timed(fn, steps, warmup, barrier):
     for _ in range(warmup):
         fn()
@@ -306,7 +352,7 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--mode", default=os.environ.get("MBEMA_BENCH_MODE", "tc_bf16"), choices=["fp32", "tc_bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd"],
+    ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd", "decode"],
                     help="run a small one-layer attention workload (for ncu captures) instead of the benchmark")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
@@ -320,6 +366,9 @@ def main():
 
     import mathbrain_b200 as mb
     mb._lib.load()                      # fails loudly if the CUDA library is missing
+    if args.profile_case == "decode":
+        decode_case(args)
+        return
     if args.profile_case:
         profile_case(args)
         return

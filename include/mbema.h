@@ -169,6 +169,27 @@ int mbema_flash_bwd(const void* Q, int q_dtype, const int64_t* x, const void* E_
                     float* dW_pe, int64_t B, int64_t H, int64_t T, int64_t hd, int64_t N, int64_t K,
                     int64_t V_total, int flags, int mode, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Streaming decode with resident per-sequence slot state.  The reference has no decode loop; one step is one
+ * iteration of the loop body of mathbrain/flash_ema_attention.py:46-82 (attention over the slots, then the
+ * "+1" of the current token) plus the query-side read of mathbrain/triton_ema_query.py:36-64.
+ *   state [B,V,N] f32: value of every slot right after its last update; last_t [B,V] i32: step of that update
+ *   (-1 = never); active [B,Kcap] i32 + n_active [B] i32: the slots seen so far.  All caller-owned, resident.
+ * mbema_decode_attend: O[b,h,:] = softmax over all V_total slots of q.K/sqrt(hd) times V with
+ *   K = E_k * gate(M W_pe), V = E_v * gate(M W_pe), M[v] = state[v] * rho^(t_now - last_t[v]); call it BEFORE
+ *   mbema_decode_update of the same step.   q [B,H,64], E_k/E_v [V,H*64] (shared by all sequences), O [B,H,64] f32.
+ * mbema_decode_update: C_q[b,:] = M[tok[b]] (query-side state, 0 if never seen), then state[tok] = C_q + 1,
+ *   last_t[tok] = t_now, and tok joins the active list.  *overflow is set to 1 if a list is full, 2 if a token
+ *   is outside [0, V).
+ * ---------------------------------------------------------------------------------------------- */
+int mbema_decode_attend(const void* q, int q_dtype, const void* E_k, const void* E_v, int e_dtype, const float* W_pe,
+                        const float* rhos, const float* state, const int32_t* last_t, const int32_t* active,
+                        const int32_t* n_active, float* O, int64_t B, int64_t H, int64_t hd, int64_t V, int64_t N,
+                        int64_t Kcap, int64_t t_now, int64_t V_total, int flags, void* stream);
+int mbema_decode_update(const int64_t* tok, const float* rhos, float* state, int32_t* last_t, int32_t* active,
+                        int32_t* n_active, float* C_q, int32_t* overflow, int64_t B, int64_t V, int64_t N,
+                        int64_t Kcap, int64_t t_now, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

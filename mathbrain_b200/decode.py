@@ -1,0 +1,63 @@
+"""Streaming decode: per-sequence slot state resident on the GPU, one new token per step.
+
+    st = DecodeState(batch, vocab, rhos, capacity=4096, device="cuda")
+    for t, tok in enumerate(stream):                 # tok: int64 [batch]
+        O = st.attend(q, E_k, E_v, W_pe, t)          # [batch, H, 64] for every layer, BEFORE the update of step t
+        C_q = st.update(tok, t)                      # query-side state of tok (for the query gate), then tok's slot += 1
+
+The reference has no decode loop; this is one iteration of the loop body of its PyTorch attention
+(mathbrain/flash_ema_attention.py:46-82) with the [V, N] state kept between steps.
+"""
+import torch
+
+from . import _lib
+from .ops import _dt, _ptr, _require_cuda, _stream
+
+
+class DecodeState:
+    def __init__(self, batch, vocab, rhos, capacity=4096, device="cuda"):
+        _require_cuda(rhos)
+        self.B, self.V, self.N, self.cap = int(batch), int(vocab), int(rhos.shape[0]), int(capacity)
+        self.rhos = rhos.float().contiguous()
+        dev = rhos.device if device is None else torch.device(device)
+        self.state = torch.zeros(self.B, self.V, self.N, dtype=torch.float32, device=dev)
+        self.last_t = torch.full((self.B, self.V), -1, dtype=torch.int32, device=dev)
+        self.active = torch.zeros(self.B, self.cap, dtype=torch.int32, device=dev)
+        self.n_active = torch.zeros(self.B, dtype=torch.int32, device=dev)
+        self.overflow = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def attend(self, q, E_k, E_v, W_pe, t_now, V_total=None, use_silu=True, listed_only=False):
+        """O [B, H, 64] float32.  q [B, H, 64]; E_k, E_v [V, H*64] projected slot embeddings; W_pe [N, H*64]."""
+        _require_cuda(q, E_k, E_v, W_pe)
+        lib = _lib.load()
+        B, H, hd = q.shape
+        q = q.contiguous()
+        E_k = E_k.contiguous()
+        E_v = E_v.to(E_k.dtype).contiguous()
+        W = W_pe.float().contiguous()
+        O = torch.empty(B, H, hd, dtype=torch.float32, device=q.device)
+        flags = (_lib.FLAG_SILU if use_silu else 0) | (_lib.FLAG_LISTED_ONLY if listed_only else 0)
+        rc = lib.mbema_decode_attend(_ptr(q), _dt(q), _ptr(E_k), _ptr(E_v), _dt(E_k), _ptr(W), _ptr(self.rhos),
+                                     _ptr(self.state), _ptr(self.last_t), _ptr(self.active), _ptr(self.n_active),
+                                     _ptr(O), B, H, hd, self.V, self.N, self.cap, int(t_now),
+                                     int(self.V if V_total is None else V_total), flags, _stream())
+        _lib.check(rc, "mbema_decode_attend")
+        return O
+
+    def update(self, tok, t_now):
+        """Query-side state C_q [B, N] of the new tokens (before their update), then the slot update of step t_now."""
+        _require_cuda(tok)
+        lib = _lib.load()
+        tok = tok.long().contiguous()
+        C_q = torch.empty(self.B, self.N, dtype=torch.float32, device=tok.device)
+        rc = lib.mbema_decode_update(_ptr(tok), _ptr(self.rhos), _ptr(self.state), _ptr(self.last_t), _ptr(self.active),
+                                     _ptr(self.n_active), _ptr(C_q), _ptr(self.overflow), self.B, self.V, self.N,
+                                     self.cap, int(t_now), _stream())
+        _lib.check(rc, "mbema_decode_update")
+        return C_q
+
+    def check_overflow(self):
+        """Synchronises; raises if an active list overflowed or a token was out of range."""
+        code = int(self.overflow.item())
+        if code:
+            raise _lib.MbemaError("decode state: " + ("active-slot list full" if code == 1 else "token outside the vocabulary"))

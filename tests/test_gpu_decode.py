@@ -1,0 +1,46 @@
+"""Streaming decode kernels against the dense CPU oracle (one iteration of the reference's attention loop per step)."""
+import pytest
+import torch
+
+from oracle import ema_oracle as orc
+from helpers import rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("B,V,N,H,steps,dt", [(3, 40, 8, 1, 30, torch.float32), (2, 300, 64, 2, 150, torch.float32),
+                                               (2, 120, 16, 2, 80, torch.bfloat16)])
+def test_decode_matches_dense_loop(B, V, N, H, steps, dt):
+    from mathbrain_b200.decode import DecodeState
+    from mathbrain_b200 import synth
+    torch.manual_seed(B + V)
+    D = 64 * H
+    rhos = synth.make_rhos(N, 2.0, 64.0)
+    E_k = (torch.randn(V, D) * 0.3).to(dt)
+    E_v = (torch.randn(V, D) * 0.3).to(dt)
+    W = torch.randn(N, D) * 0.3
+    x = torch.randint(0, V, (B, steps))
+    Q = (torch.randn(B, H, steps, 64) * 0.3).to(dt)
+    st = DecodeState(B, V, rhos.cuda(), capacity=64 if V > 64 else V)
+    state = torch.zeros(B, V, N)
+    last = torch.full((B, V), -1, dtype=torch.long)
+    cap = st.cap
+    for t in range(steps):
+        if int((last >= 0).sum(1).max()) >= cap and not bool(((last[torch.arange(B), x[:, t]]) >= 0).all()):
+            break                                    # the next token would overflow the active list of this small test
+        O = st.attend(Q[:, :, t].cuda(), E_k.cuda(), E_v.cuda(), W.cuda(), t)
+        Cq = st.update(x[:, t].cuda(), t)
+        O_ref, Cq_ref = orc.decode_step(state, last, t, x[:, t], Q[:, :, t].float(), E_k.float(), E_v.float(), W, rhos, V)
+        assert rel_err(O.cpu(), O_ref) < (1e-4 if dt == torch.float32 else 2e-2), t
+        assert torch.allclose(Cq.cpu(), Cq_ref, atol=1e-5, rtol=1e-5), t
+    st.check_overflow()
+
+
+def test_decode_overflow_is_reported():
+    from mathbrain_b200.decode import DecodeState
+    from mathbrain_b200 import _lib, synth
+    st = DecodeState(1, 10, synth.make_rhos(4, 2.0, 8.0).cuda(), capacity=2)
+    for t, tok in enumerate([1, 2, 3]):
+        st.update(torch.tensor([tok]).cuda(), t)
+    with pytest.raises(_lib.MbemaError):
+        st.check_overflow()
