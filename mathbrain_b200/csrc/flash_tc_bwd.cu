@@ -390,10 +390,10 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
 #pragma unroll
                     for (int v = 0; v < 2; ++v) {
                         const float hh = pre[pr * 2 + v];
-                        if (SILU) {     // h = x / 2:  SiLU(x) = h + h*th,  SiLU'(x) = (1 + th)/2 * (1 + h - h*th),  th = tanh(h)
+                        if (SILU) {     // h = x / 2, th = tanh(h), sg = sigmoid(x) = (1 + th)/2:  SiLU = h + h*th,  SiLU' = sg + SiLU*(1 - sg)
                             const float th = tanh_approx(hh);
                             g[v] = fmaf(hh, th, hh);
-                            dsl[v] = fmaf(0.5f, th, 0.5f) * (fmaf(hh, 2.0f, 1.0f) - g[v]);
+                            dsl[v] = fmaf(g[v], fmaf(-0.5f, th, 0.5f), fmaf(0.5f, th, 0.5f));
                         } else {
                             g[v] = hh;
                             dsl[v] = 1.0f;
@@ -434,12 +434,12 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                     uint32_t zp[4], zk[4], zv[4];
 #pragma unroll
                     for (int pr = 0; pr < 4; ++pr) {
-                        const uint32_t qq = q2[w0 + pr], dd = do2[w0 + pr], gg = g2[w0 + pr];
-                        zk[pr] = mul_bf16x2(dsr2, mul_bf16x2(qq, gg));                    // ds * q * g
-                        zv[pr] = mul_bf16x2(p2, mul_bf16x2(dd, gg));                      // p * dO * g
-                        const uint32_t t1 = mul_bf16x2(dsr2, mul_bf16x2(qq, ekw[pr]));    // ds * q * E_k
-                        const uint32_t t2 = mul_bf16x2(dd, evw[pr]);                      // dO * E_v
-                        zp[pr] = mul_bf16x2(fma_bf16x2(p2, t2, t1), dsl2[w0 + pr]);       // dgate * SiLU'
+                        const uint32_t gg = g2[w0 + pr];
+                        const uint32_t aq = mul_bf16x2(dsr2, q2[w0 + pr]);                // ds * q
+                        const uint32_t bd = mul_bf16x2(p2, do2[w0 + pr]);                 // p * dO
+                        zk[pr] = mul_bf16x2(aq, gg);                                      // ds * q * g
+                        zv[pr] = mul_bf16x2(bd, gg);                                      // p * dO * g
+                        zp[pr] = mul_bf16x2(fma_bf16x2(bd, evw[pr], mul_bf16x2(aq, ekw[pr])), dsl2[w0 + pr]);   // dgate * SiLU'
                     }
                     const int chunk = ((c * 2 + j8) ^ (row & 7)) << 4;
                     st_shared_v4(zrow + 0 * HPC * ATOM_BYTES + chunk, zp[0], zp[1], zp[2], zp[3]);
