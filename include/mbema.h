@@ -46,6 +46,7 @@ extern "C" {
                                    /* V_total slots, unlisted ones with score 0 and value 0, as            */
                                    /* mathbrain/flash_ema_attention.py:76-79                               */
 #define MBEMA_FLAG_CBASE_EXTRA_DECAY 4 /* M_0 = rho * c_base (mathbrain/triton_flash_ema.py:48-50,185)     */
+#define MBEMA_FLAG_FP32_BACKWARD 8     /* MBEMA_MODE_TC_BF16 only: run the backward with the fp32 kernels      */
 
 /* compute modes of the attention kernels */
 #define MBEMA_MODE_FP32 0          /* fp32 arithmetic on the CUDA cores                                    */

@@ -31,7 +31,7 @@ bool flash_tc_supported(int H, int N, int K);
 size_t flash_fwd_tc_ws();
 int flash_fwd_tc(const FlashArgs& a, void* ws, cudaStream_t st);
 bool flash_bwd_tc_supported(int H, int N, int K);
-size_t flash_bwd_tc_ws(int64_t B, int64_t H, int64_t T);
+size_t flash_bwd_tc_ws(int64_t B, int64_t H, int64_t T, int64_t N);
 int flash_bwd_tc(FlashArgs a, float* dW, void* ws, cudaStream_t st);
 
 }  // namespace mbema

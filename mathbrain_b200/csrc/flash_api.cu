@@ -64,7 +64,7 @@ extern "C" size_t mbema_flash_bwd_workspace_bytes(int64_t B, int64_t H, int64_t 
     // in tensor-core mode the first 512 bytes hold the kernel status word, whichever kernel ends up running
     size_t need = flash_bwd_simt_ws(B, H, T, N) + (mode == MBEMA_MODE_TC_BF16 ? 512 : 0);
     if (mode == MBEMA_MODE_TC_BF16 && flash_bwd_tc_supported((int)H, (int)N, (int)K)) {
-        const size_t tc = flash_bwd_tc_ws(B, H, T);
+        const size_t tc = flash_bwd_tc_ws(B, H, T, N);
         if (tc > need) need = tc;
     }
     return need;
@@ -98,7 +98,8 @@ extern "C" int mbema_flash_bwd(const void* Q, int q_dtype, const int64_t* x, con
     a.dO = dO; a.do_dt = do_dtype; a.dQ = dQ; a.dEk = dE_k; a.dEv = dE_v;
     // tensor-core backward where the shape fits its shared-memory budget (N == 64); otherwise the fp32 kernels
     if (mode == MBEMA_MODE_TC_BF16) {
-        if (flash_bwd_tc_supported((int)H, (int)N, (int)K)) return flash_bwd_tc(a, dW_pe, workspace, st);
+        if (!(flags & MBEMA_FLAG_FP32_BACKWARD) && flash_bwd_tc_supported((int)H, (int)N, (int)K))
+            return flash_bwd_tc(a, dW_pe, workspace, st);
         MBEMA_CUDA_TRY(cudaMemsetAsync(workspace, 0, 512, st));   // status word: the fp32 kernels have no bounded waits
         return flash_bwd_simt(a, dW_pe, static_cast<unsigned char*>(workspace) + 512, st);
     }

@@ -247,8 +247,13 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
                     const int n0 = cc * 8;
                     const float4 b0 = __ldg(reinterpret_cast<const float4*>(base + n0));
                     const float4 b1 = __ldg(reinterpret_cast<const float4*>(base + n0 + 4));
-                    const float4 r0 = *reinterpret_cast<const float4*>(Rrow + n0);
-                    const float4 r1 = *reinterpret_cast<const float4*>(Rrow + n0 + 4);
+                    float4 r0 = *reinterpret_cast<const float4*>(Rrow + n0);
+                    float4 r1 = *reinterpret_cast<const float4*>(Rrow + n0 + 4);
+                    if (NK == 1) {   // N = 64 multiplies by bf16-rounded powers everywhere (cold rows use packed bf16 pairs;
+                                     // the backward rebuilds the same tiles from a bf16 table)
+                        r0 = make_float4(bf16_round(r0.x), bf16_round(r0.y), bf16_round(r0.z), bf16_round(r0.w));
+                        r1 = make_float4(bf16_round(r1.x), bf16_round(r1.y), bf16_round(r1.z), bf16_round(r1.w));
+                    }
                     uint4 pk;
                     pk.x = pack_bf16x2(fmaf(b0.x, r0.x, r0.x), fmaf(b0.y, r0.y, r0.y));
                     pk.y = pack_bf16x2(fmaf(b0.z, r0.z, r0.z), fmaf(b0.w, r0.w, r0.w));

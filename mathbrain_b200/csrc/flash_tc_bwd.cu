@@ -21,19 +21,24 @@ using namespace ptx;
 static constexpr int TM = MBEMA_TILE_T;
 static constexpr int HPC = 2;
 static constexpr int HD = 64;
-static constexpr int N = 64;                       // EMA channels supported by this kernel
 static constexpr int EPI_WARPS = 4 * HPC;
 static constexpr int EPI_THREADS = 32 * EPI_WARPS;
 static constexpr int PROD_THREADS = 128;
 static constexpr int THREADS = EPI_THREADS + PROD_THREADS;
 static constexpr int ATOM_BYTES = TM * 128;
-static constexpr int NA = 3;                       // A-tile / E-row stages in shared memory
-static constexpr int NACC = 2;                     // gate accumulator stages in TMEM
 static constexpr int ACC_COLS = HPC * HD;
-static constexpr int COL_DW = NACC * ACC_COLS;     // TMEM column of dW^T [128 d x N]
-static constexpr int COL_DEK = COL_DW + N;         // TMEM column of the dE_k column sums (16 columns, all equal)
-static constexpr int COL_DEV = COL_DEK + 16;
-static constexpr int COL_DQ = 384;                 // dQ accumulators [128 t x (2 heads x 64)] fp32, one row per thread
+// Per channel count N = 64 * NK (NK = 1, 2): stages and the TMEM map
+//   NK = 1: gate 2 x 128 | dW^T 64  | dE_k 16 | dE_v 16 | ... | dQ 128 at column 384
+//   NK = 2: gate 1 x 128 | dW^T 128 | dE_k 16 | dE_v 16 | ... | dQ 128 at column 384
+template <int NK> struct Cfg {
+    static constexpr int N = 64 * NK;
+    static constexpr int NA = NK == 1 ? 3 : 2;         // A-tile / E-row stages in shared memory
+    static constexpr int NACC = NK == 1 ? 2 : 1;       // gate accumulator stages in TMEM
+    static constexpr int COL_DW = NACC * ACC_COLS;     // dW^T [128 d x N]
+    static constexpr int COL_DEK = COL_DW + N;         // dE_k column sums (16 columns, all equal)
+    static constexpr int COL_DEV = COL_DEK + 16;
+    static constexpr int COL_DQ = 384;                 // dQ accumulators [128 t x (2 heads x 64)] fp32, one row per thread
+};
 static constexpr int TMEM_COLS = 512;
 static constexpr int PD = 3, RING = PD + 1;
 static constexpr int RING_STAGE_BYTES = 256 + 2 * ACC_COLS * 4;
@@ -43,14 +48,18 @@ struct Smem {
     int a_off, b_off, z_off, ones_off, r_off, e_off, e2_off, ring_off, tok_off, slot_off, key_off, bar_off, total;
 };
 
-__host__ __device__ inline Smem smem_layout(int K) {
+__host__ __device__ inline Smem smem_layout(int K, int NK) {
+    const int NA = NK == 1 ? 3 : 2;
     Smem s;
     int o = 0;
-    s.a_off = o; o += NA * ATOM_BYTES;
-    s.b_off = o; o += ATOM_BYTES;                 // W^T for the gate product (K-major over n)
+    s.a_off = o; o += NA * NK * ATOM_BYTES;
+    s.b_off = o; o += NK * ATOM_BYTES;            // W^T for the gate product (K-major over n)
     s.z_off = o; o += 3 * HPC * ATOM_BYTES;       // dpre, ds*q*g, p*dO*g tiles: [kind][head][128 t][64 d] bf16
     s.ones_off = o; o += 2048;                    // 16 x 64 bf16 ones (B operand of the column sums)
-    s.r_off = o; o += TM * N * 2;                 // decay powers rho_n^r as bf16 [128][64] (in-tile restarts only)
+    // decay powers rho_n^r.  NK = 1: bf16 table [128][64] (the forward kernel multiplies bf16 snapshots by bf16 powers;
+    // the recompute must build bit-identical state tiles or p = exp(s - LSE) stops summing to one);
+    // NK = 2: fp32, two levels [8][128] (r / 16) and [16][128] (r % 16), product rounded once like the forward's fp32 table
+    s.r_off = o; o += NK == 1 ? TM * 64 * 2 : 24 * 128 * 4;
     s.e_off = o; o += NA * 2 * ACC_COLS * 4;      // E_k / E_v rows as fp32 ...
     s.e2_off = o; o += NA * 2 * ACC_COLS * 2;     // ... and as bf16 (operands of the packed tile arithmetic)
     s.ring_off = o; o += RING * RING_STAGE_BYTES;
@@ -67,8 +76,8 @@ __device__ __forceinline__ int sw128_off(int row, int col) {
 }
 
 struct Bars {
-    uint64_t acc_full[NACC];     // gate UMMAs done + E rows staged                  (2 arrivals)
-    uint64_t acc_empty[NACC];    // all epilogue warps finished reading the stage      (EPI_WARPS arrivals)
+    uint64_t acc_full[2];        // gate UMMAs done + E rows staged                  (2 arrivals)
+    uint64_t acc_empty[2];       // all epilogue warps finished reading the stage      (EPI_WARPS arrivals)
     uint64_t z_full;             // all epilogue warps wrote their part of the Z tiles (EPI_WARPS arrivals)
     uint64_t z_done;             // products (2) and (3) of the slot have completed    (3 arrivals: one commit per issuing warp)
     uint32_t tmem_base;
@@ -86,16 +95,20 @@ __device__ __forceinline__ float tmem_ld_1(uint32_t taddr) {
     return __uint_as_float(r);
 }
 
-template <bool SILU>
+template <bool SILU, int NK>
 __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* status) {
+    constexpr int N = Cfg<NK>::N, NA = Cfg<NK>::NA, NACC = Cfg<NK>::NACC;
+    constexpr int COL_DW = Cfg<NK>::COL_DW, COL_DEK = Cfg<NK>::COL_DEK, COL_DEV = Cfg<NK>::COL_DEV, COL_DQ = Cfg<NK>::COL_DQ;
+    constexpr int STAGE_BYTES = NK * ATOM_BYTES;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const Smem L = smem_layout(a.K);
+    const Smem L = smem_layout(a.K, NK);
     unsigned char* A_sh = sm + L.a_off;
     unsigned char* B_sh = sm + L.b_off;
     unsigned char* Z_sh = sm + L.z_off;
     unsigned char* ones_sh = sm + L.ones_off;
-    __nv_bfloat16* R_sh = reinterpret_cast<__nv_bfloat16*>(sm + L.r_off);
+    float* R_sh = reinterpret_cast<float*>(sm + L.r_off);                       // NK = 2
+    __nv_bfloat16* Rb_sh = reinterpret_cast<__nv_bfloat16*>(sm + L.r_off);      // NK = 1
     float* E_sh = reinterpret_cast<float*>(sm + L.e_off);
     __nv_bfloat16* E2_sh = reinterpret_cast<__nv_bfloat16*>(sm + L.e2_off);
     unsigned char* ring_sh = sm + L.ring_off;
@@ -164,11 +177,19 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
         for (int i = tid; i < N * ACC_COLS; i += THREADS) {
             const int n = i / ACC_COLS, dd = i % ACC_COLS;
             const float w = a.W[(size_t)n * D + hp * ACC_COLS + dd] * wscale;
-            *reinterpret_cast<__nv_bfloat16*>(B_sh + sw128_off(dd, n)) = __float2bfloat16(w);
+            *reinterpret_cast<__nv_bfloat16*>(B_sh + (n >> 6) * ATOM_BYTES + sw128_off(dd, n & 63)) = __float2bfloat16(w);
         }
-        for (int i = tid; i < TM * N; i += THREADS) {
-            const int r = i / N, n = i % N;
-            R_sh[i] = __float2bfloat16(exp2f((float)r * log2f(a.rhos[n])));
+        if (NK == 1) {
+            for (int i = tid; i < TM * N; i += THREADS) {
+                const int r = i / N, n = i % N;
+                Rb_sh[i] = __float2bfloat16(exp2f((float)r * log2f(a.rhos[n])));
+            }
+        } else {   // rho^r = rho^(16 (r / 16)) * rho^(r % 16): rows 0..7 hold the first factor, rows 8..23 the second
+            for (int i = tid; i < 24 * N; i += THREADS) {
+                const int r = i / N, n = i % N;
+                const float e = (r < 8) ? 16.0f * (float)r : (float)(r - 8);
+                R_sh[i] = exp2f(e * log2f(a.rhos[n]));
+            }
         }
         for (int i = tid; i < 1024; i += THREADS) reinterpret_cast<__nv_bfloat16*>(ones_sh)[i] = __float2bfloat16(1.0f);
         for (int i = tid; i < TM; i += THREADS) {
@@ -227,7 +248,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             mbar_wait(&bars->z_full, (uint32_t)(j & 1), abort_flag);
             tc_fence_after_sync();
             if (role == 1) {
-                const uint64_t d_at = d_a0 + (uint64_t)(((j % NA) * ATOM_BYTES) >> 4);
+                const uint64_t d_at = d_a0 + (uint64_t)(((j % NA) * STAGE_BYTES) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < TM / 16; ++ks)      // contraction over the 128 time steps, 16 per instruction
                     umma_bf16_ss(tmem_base + COL_DW, d_zp + (uint64_t)(ks * (2048 >> 4)), d_at + (uint64_t)(ks * (2048 >> 4)),
@@ -243,9 +264,28 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                 umma_commit(&bars->z_done);
             }
         };
-        uint32_t R2[32];
+        // decay powers rho^r for 8 consecutive channels starting at n0 (r = steps since the reference state), as fp32
+        // values: bf16-exact for NK = 1 (see the table comment), full fp32 for NK = 2
+        auto decay8 = [&](int r, int n0, float* out) {
+            if (NK == 1) {
+                const uint4 x = *reinterpret_cast<const uint4*>(Rb_sh + r * N + n0);
+                out[0] = bf16_lo(x.x); out[1] = bf16_hi(x.x); out[2] = bf16_lo(x.y); out[3] = bf16_hi(x.y);
+                out[4] = bf16_lo(x.z); out[5] = bf16_hi(x.z); out[6] = bf16_lo(x.w); out[7] = bf16_hi(x.w);
+            } else {
+                const float* hi = R_sh + (r >> 4) * N + n0;
+                const float* lo = R_sh + (8 + (r & 15)) * N + n0;
+                const float4 h0 = *reinterpret_cast<const float4*>(hi), h1 = *reinterpret_cast<const float4*>(hi + 4);
+                const float4 l0 = *reinterpret_cast<const float4*>(lo), l1 = *reinterpret_cast<const float4*>(lo + 4);
+                out[0] = h0.x * l0.x; out[1] = h0.y * l0.y; out[2] = h0.z * l0.z; out[3] = h0.w * l0.w;
+                out[4] = h1.x * l1.x; out[5] = h1.y * l1.y; out[6] = h1.z * l1.z; out[7] = h1.w * l1.w;
+            }
+        };
+        // NK = 1: this row's powers as packed bf16 pairs, register-resident (cold rows: packed multiply, as the forward)
+        uint32_t R2[NK == 1 ? 32 : 1];
+        if (NK == 1) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) R2[j] = *reinterpret_cast<const uint32_t*>(R_sh + row * N + 2 * j);
+            for (int j = 0; j < 32; ++j) R2[j] = *reinterpret_cast<const uint32_t*>(Rb_sh + row * N + 2 * j);
+        }
         for (int j = 0; j < PD; ++j) prefetch(j);
         asm volatile("cp.async.wait_group %0;" ::"n"(PD - 1) : "memory");
         named_bar_sync(1, PROD_THREADS);
@@ -281,32 +321,41 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                     if (s < 0 && mm) s = j * 32 + 31 - __clz(mm);
                 }
             }
-            unsigned char* Arow = A_sh + sa * ATOM_BYTES + row * 128;
+            unsigned char* Arow = A_sh + sa * STAGE_BYTES + row * 128;
             if (s >= 0) {   // restart from the token's own state at its last in-tile occurrence (+1)
                 const float* base = a.tok_state + ((size_t)b * a.T + t0 + s) * N;
-                const uint32_t* Rrow = reinterpret_cast<const uint32_t*>(R_sh + (row - s) * N);
 #pragma unroll 2
-                for (int cc = 0; cc < 8; ++cc) {
+                for (int cc = 0; cc < N / 8; ++cc) {
                     const float4 b0 = __ldg(reinterpret_cast<const float4*>(base + cc * 8));
                     const float4 b1 = __ldg(reinterpret_cast<const float4*>(base + cc * 8 + 4));
-                    const uint4 rr = *reinterpret_cast<const uint4*>(Rrow + cc * 4);
+                    float rr[8];
+                    decay8(row - s, cc * 8, rr);
                     uint4 pk;
-                    pk.x = pack_bf16x2((b0.x + 1.f) * bf16_lo(rr.x), (b0.y + 1.f) * bf16_hi(rr.x));
-                    pk.y = pack_bf16x2((b0.z + 1.f) * bf16_lo(rr.y), (b0.w + 1.f) * bf16_hi(rr.y));
-                    pk.z = pack_bf16x2((b1.x + 1.f) * bf16_lo(rr.z), (b1.y + 1.f) * bf16_hi(rr.z));
-                    pk.w = pack_bf16x2((b1.z + 1.f) * bf16_lo(rr.w), (b1.w + 1.f) * bf16_hi(rr.w));
-                    *reinterpret_cast<uint4*>(Arow + ((cc ^ (row & 7)) << 4)) = pk;
+                    pk.x = pack_bf16x2(fmaf(b0.x, rr[0], rr[0]), fmaf(b0.y, rr[1], rr[1]));
+                    pk.y = pack_bf16x2(fmaf(b0.z, rr[2], rr[2]), fmaf(b0.w, rr[3], rr[3]));
+                    pk.z = pack_bf16x2(fmaf(b1.x, rr[4], rr[4]), fmaf(b1.y, rr[5], rr[5]));
+                    pk.w = pack_bf16x2(fmaf(b1.z, rr[6], rr[6]), fmaf(b1.w, rr[7], rr[7]));
+                    *reinterpret_cast<uint4*>(Arow + (cc >> 3) * ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) = pk;
                 }
             } else {
 #pragma unroll
-                for (int cc = 0; cc < 8; ++cc) {
+                for (int cc = 0; cc < N / 8; ++cc) {
                     const uint4 sv = *reinterpret_cast<const uint4*>(rg + cc * 16);
                     uint4 pk;
-                    pk.x = mul_bf16x2(sv.x, R2[4 * cc]);
-                    pk.y = mul_bf16x2(sv.y, R2[4 * cc + 1]);
-                    pk.z = mul_bf16x2(sv.z, R2[4 * cc + 2]);
-                    pk.w = mul_bf16x2(sv.w, R2[4 * cc + 3]);
-                    *reinterpret_cast<uint4*>(Arow + ((cc ^ (row & 7)) << 4)) = pk;
+                    if (NK == 1) {
+                        pk.x = mul_bf16x2(sv.x, R2[(4 * cc) & 31]);
+                        pk.y = mul_bf16x2(sv.y, R2[(4 * cc + 1) & 31]);
+                        pk.z = mul_bf16x2(sv.z, R2[(4 * cc + 2) & 31]);
+                        pk.w = mul_bf16x2(sv.w, R2[(4 * cc + 3) & 31]);
+                    } else {
+                        float rr[8];
+                        decay8(row, cc * 8, rr);
+                        pk.x = pack_bf16x2(bf16_lo(sv.x) * rr[0], bf16_hi(sv.x) * rr[1]);
+                        pk.y = pack_bf16x2(bf16_lo(sv.y) * rr[2], bf16_hi(sv.y) * rr[3]);
+                        pk.z = pack_bf16x2(bf16_lo(sv.z) * rr[4], bf16_hi(sv.z) * rr[5]);
+                        pk.w = pack_bf16x2(bf16_lo(sv.w) * rr[6], bf16_hi(sv.w) * rr[7]);
+                    }
+                    *reinterpret_cast<uint4*>(Arow + (cc >> 3) * ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) = pk;
                 }
             }
             fence_proxy_async_smem();
@@ -316,9 +365,11 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                     if (i >= NACC) mbar_wait(&bars->acc_empty[sc], (uint32_t)((i / NACC - 1) & 1), abort_flag);
                     tc_fence_after_sync();
 #pragma unroll
-                    for (int k16 = 0; k16 < 4; ++k16)
-                        umma_bf16_ss(tmem_base + (uint32_t)(sc * ACC_COLS), d_ak0 + (uint64_t)((sa * ATOM_BYTES + k16 * 32) >> 4),
-                                     d_b0 + (uint64_t)((k16 * 32) >> 4), idesc_gate, k16 != 0 ? 1u : 0u);
+                    for (int k16 = 0; k16 < 4 * NK; ++k16) {     // contraction over n, 16 per instruction, 64 per swizzle atom
+                        const int off = (k16 >> 2) * ATOM_BYTES + (k16 & 3) * 32;
+                        umma_bf16_ss(tmem_base + (uint32_t)(sc * ACC_COLS), d_ak0 + (uint64_t)((sa * STAGE_BYTES + off) >> 4),
+                                     d_b0 + (uint64_t)(off >> 4), idesc_gate, k16 != 0 ? 1u : 0u);
+                    }
                     umma_commit(&bars->acc_full[sc]);
                     mbar_arrive(&bars->acc_full[sc]);
                 } else if (i >= 1) {
@@ -513,7 +564,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
 }
 
 // dW[n, hp*128 + d] = sum over (b, tile) of part[b][hp][tile][n][d]      (fixed order -> deterministic)
-__global__ void k_flash_dw_reduce_tc(const float* __restrict__ part, float* __restrict__ dW, int B, int HP, int nT, int D) {
+__global__ void k_flash_dw_reduce_tc(const float* __restrict__ part, float* __restrict__ dW, int B, int HP, int nT, int D, int N) {
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= N * D) return;
     const int n = idx / D, col = idx % D, hp = col / ACC_COLS, d = col % ACC_COLS;
@@ -527,12 +578,12 @@ __global__ void k_flash_dw_reduce_tc(const float* __restrict__ part, float* __re
 }  // namespace tcb
 
 bool flash_bwd_tc_supported(int H, int N, int K) {
-    return (H % tcb::HPC) == 0 && N == tcb::N && K <= tcb::MAX_SLOTS && tcb::smem_layout(K).total <= 227 * 1024;
+    return (H % tcb::HPC) == 0 && (N == 64 || N == 128) && K <= tcb::MAX_SLOTS && tcb::smem_layout(K, N / 64).total <= 227 * 1024;
 }
 
-size_t flash_bwd_tc_ws(int64_t B, int64_t H, int64_t T) {
+size_t flash_bwd_tc_ws(int64_t B, int64_t H, int64_t T, int64_t N) {
     const int64_t nT = (T + MBEMA_TILE_T - 1) / MBEMA_TILE_T;
-    return 256 + (size_t)(B * (H / tcb::HPC) * nT) * tcb::N * tcb::ACC_COLS * sizeof(float) + 256;
+    return 256 + (size_t)(B * (H / tcb::HPC) * nT) * N * tcb::ACC_COLS * sizeof(float) + 256;
 }
 
 int flash_bwd_tc(FlashArgs a, float* dW, void* ws, cudaStream_t st) {
@@ -542,19 +593,20 @@ int flash_bwd_tc(FlashArgs a, float* dW, void* ws, cudaStream_t st) {
     MBEMA_CUDA_TRY(cudaMemsetAsync(status, 0, 256, st));
     MBEMA_CUDA_TRY(cudaMemsetAsync(a.dEk, 0, (size_t)a.B * a.K * D * sizeof(float), st));
     MBEMA_CUDA_TRY(cudaMemsetAsync(a.dEv, 0, (size_t)a.B * a.K * D * sizeof(float), st));
-    const tcb::Smem L = tcb::smem_layout(a.K);
+    const tcb::Smem L = tcb::smem_layout(a.K, a.N / 64);
     dim3 grid(a.nT, a.H / tcb::HPC, a.B);
-    if (a.silu) {
-        MBEMA_CUDA_TRY(cudaFuncSetAttribute(tcb::k_flash_bwd_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total));
-        tcb::k_flash_bwd_tc<true><<<grid, tcb::THREADS, L.total, st>>>(a, status);
-    } else {
-        MBEMA_CUDA_TRY(cudaFuncSetAttribute(tcb::k_flash_bwd_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total));
-        tcb::k_flash_bwd_tc<false><<<grid, tcb::THREADS, L.total, st>>>(a, status);
-    }
+#define MBEMA_LAUNCH_BWD(S_, NK_)                                                                                     \
+    do {                                                                                                             \
+        MBEMA_CUDA_TRY(cudaFuncSetAttribute(tcb::k_flash_bwd_tc<S_, NK_>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total)); \
+        tcb::k_flash_bwd_tc<S_, NK_><<<grid, tcb::THREADS, L.total, st>>>(a, status);                               \
+    } while (0)
+    if (a.N == 64) { if (a.silu) MBEMA_LAUNCH_BWD(true, 1); else MBEMA_LAUNCH_BWD(false, 1); }
+    else { if (a.silu) MBEMA_LAUNCH_BWD(true, 2); else MBEMA_LAUNCH_BWD(false, 2); }
+#undef MBEMA_LAUNCH_BWD
     int rc = check_launch();
     if (rc) return rc;
-    const int total = tcb::N * D;
-    tcb::k_flash_dw_reduce_tc<<<(total + 255) / 256, 256, 0, st>>>(a.dW_part, dW, a.B, a.H / tcb::HPC, a.nT, D);
+    const int total = a.N * D;
+    tcb::k_flash_dw_reduce_tc<<<(total + 255) / 256, 256, 0, st>>>(a.dW_part, dW, a.B, a.H / tcb::HPC, a.nT, D, a.N);
     return check_launch();
 }
 

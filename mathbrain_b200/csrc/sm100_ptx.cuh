@@ -3,6 +3,7 @@
 // Every wait is bounded: after MBEMA_SPIN_LIMIT polls it gives up, raises the CTA's abort flag and returns,
 // so a protocol error ends the kernel with an error status instead of hanging the GPU.
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -211,6 +212,7 @@ __device__ __forceinline__ uint32_t fma_bf16x2(uint32_t a, uint32_t b, uint32_t 
     asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 

@@ -26,12 +26,12 @@ from . import _lib
 # mathbrain/model.py takes its GPU operator path when this name is truthy.
 HAS_TRITON = True
 
-_OPTIONS = {"inactive_mass": "full_V", "cbase_extra_decay": False, "mode": "fp32"}
+_OPTIONS = {"inactive_mass": "full_V", "cbase_extra_decay": False, "mode": "fp32", "fp32_backward": False}
 _MODES = {"fp32": _lib.MODE_FP32, "tc_bf16": _lib.MODE_TC_BF16}
 
 
 def set_options(inactive_mass: Optional[str] = None, cbase_extra_decay: Optional[bool] = None,
-                mode: Optional[str] = None):
+                mode: Optional[str] = None, fp32_backward: Optional[bool] = None):
     """Semantics and precision switches of the attention operator.
 
     inactive_mass      "full_V" (default): softmax over all V_total vocabulary slots, as the PyTorch reference
@@ -41,7 +41,10 @@ def set_options(inactive_mass: Optional[str] = None, cbase_extra_decay: Optional
                        (mathbrain/data.py:128-140); True: rho * c_base, the Triton kernels' convention
                        (mathbrain/triton_flash_ema.py:48-50,185).
     mode               "fp32": fp32 arithmetic on the CUDA cores; "tc_bf16": gate product on the tensor cores.
+    fp32_backward      with mode "tc_bf16": keep the tensor-core forward but run the backward with the fp32 kernels.
     """
+    if fp32_backward is not None:
+        _OPTIONS["fp32_backward"] = bool(fp32_backward)
     if inactive_mass is not None:
         if inactive_mass not in ("full_V", "listed_only"):
             raise ValueError(inactive_mass)
@@ -273,6 +276,8 @@ def _flash_flags(use_silu):
     f = _lib.FLAG_SILU if use_silu else 0
     if _OPTIONS["inactive_mass"] == "listed_only":
         f |= _lib.FLAG_LISTED_ONLY
+    if _OPTIONS["fp32_backward"]:
+        f |= _lib.FLAG_FP32_BACKWARD
     return f
 
 
