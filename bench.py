@@ -246,13 +246,17 @@ def decode_case(args):
     import numpy as np
     rng = np.random.Generator(np.random.PCG64(1))
     toks = torch.from_numpy(zipf.draw(rng, B * 40).reshape(40, B)).to(dev)
+    mode = "tc_bf16" if args.mode == "tc_bf16" else "fp32"
+    o_tc = st.attend(q, E_k[0], E_v[0], W[0], 8192, mode=mode)
+    o_32 = st.attend(q, E_k[0], E_v[0], W[0], 8192, mode="fp32")
+    diff = float((o_tc - o_32).abs().max() / o_32.abs().max())
     times = []
     for step in range(40):
         t_now = 8192 + step
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for l in range(L):
-            st.attend(q, E_k[l], E_v[l], W[l], t_now)
+            st.attend(q, E_k[l], E_v[l], W[l], t_now, mode=mode)
         st.update(toks[step], t_now)
         e1.record()
         torch.cuda.synchronize()
@@ -260,7 +264,7 @@ def decode_case(args):
     st.check_overflow()
     ms = sorted(times[8:])[len(times[8:]) // 2]
     bytes_step = B * L * K * (N * 4 + 4 + 2 * D * 2)            # state rows + last_t + E_k/E_v rows per active slot
-    print(json.dumps({"profile_case": "decode", "sequences": B, "active_slots": K, "layers": L, "ms_per_step": ms,
+    print(json.dumps({"profile_case": "decode", "mode": mode, "rel_diff_vs_fp32_kernel": diff, "sequences": B, "active_slots": K, "layers": L, "ms_per_step": ms,
                       "tokens_per_s": B / ms * 1000.0, "algorithmic_GB_per_step": bytes_step / 1e9,
                       "achieved_GBps": bytes_step / ms / 1e6, "hbm_peak_GBps": peaks()["hbm"]}))
 

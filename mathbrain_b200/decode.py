@@ -11,7 +11,7 @@ The reference has no decode loop; this is one iteration of the loop body of its 
 import torch
 
 from . import _lib
-from .ops import _dt, _ptr, _require_cuda, _stream
+from .ops import _dt, _ptr, _require_cuda, _stream, get_options
 
 
 class DecodeState:
@@ -25,9 +25,13 @@ class DecodeState:
         self.active = torch.zeros(self.B, self.cap, dtype=torch.int32, device=dev)
         self.n_active = torch.zeros(self.B, dtype=torch.int32, device=dev)
         self.overflow = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._ws = None
 
-    def attend(self, q, E_k, E_v, W_pe, t_now, V_total=None, use_silu=True, listed_only=False):
-        """O [B, H, 64] float32.  q [B, H, 64]; E_k, E_v [V, H*64] projected slot embeddings; W_pe [N, H*64]."""
+    def attend(self, q, E_k, E_v, W_pe, t_now, V_total=None, use_silu=True, listed_only=False, mode=None):
+        """O [B, H, 64] float32.  q [B, H, 64]; E_k, E_v [V, H*64] projected slot embeddings; W_pe [N, H*64].
+
+        mode "fp32" (exact kernel) or "tc_bf16" (tensor cores; N = 64, H even); default: the package option `mode`,
+        falling back to fp32 where the tensor-core kernel does not apply."""
         _require_cuda(q, E_k, E_v, W_pe)
         lib = _lib.load()
         B, H, hd = q.shape
@@ -37,6 +41,22 @@ class DecodeState:
         W = W_pe.float().contiguous()
         O = torch.empty(B, H, hd, dtype=torch.float32, device=q.device)
         flags = (_lib.FLAG_SILU if use_silu else 0) | (_lib.FLAG_LISTED_ONLY if listed_only else 0)
+        tc_ok = self.N == 64 and hd == 64 and H % 2 == 0
+        if mode is None:
+            mode = "tc_bf16" if (get_options()["mode"] == "tc_bf16" and tc_ok) else "fp32"
+        if mode == "tc_bf16":
+            need = lib.mbema_decode_attend_tc_workspace_bytes(B, H, self.cap)
+            if self._ws is None or self._ws.numel() < need:
+                self._ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+            rc = lib.mbema_decode_attend_tc(_ptr(q), _dt(q), _ptr(E_k), _ptr(E_v), _dt(E_k), _ptr(W), _ptr(self.rhos),
+                                            _ptr(self.state), _ptr(self.last_t), _ptr(self.active),
+                                            _ptr(self.n_active), _ptr(O), B, H, hd, self.V, self.N, self.cap,
+                                            int(t_now), int(self.V if V_total is None else V_total), flags,
+                                            _ptr(self._ws), self._ws.numel(), _stream())
+            _lib.check(rc, "mbema_decode_attend_tc")
+            return O
+        if mode != "fp32":
+            raise ValueError("mode must be 'fp32' or 'tc_bf16'")
         rc = lib.mbema_decode_attend(_ptr(q), _dt(q), _ptr(E_k), _ptr(E_v), _dt(E_k), _ptr(W), _ptr(self.rhos),
                                      _ptr(self.state), _ptr(self.last_t), _ptr(self.active), _ptr(self.n_active),
                                      _ptr(O), B, H, hd, self.V, self.N, self.cap, int(t_now),

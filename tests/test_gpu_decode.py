@@ -44,3 +44,47 @@ def test_decode_overflow_is_reported():
         st.update(torch.tensor([tok]).cuda(), t)
     with pytest.raises(_lib.MbemaError):
         st.check_overflow()
+
+
+@pytest.mark.parametrize("B,V,H,steps,silu,dt", [(2, 700, 2, 300, True, torch.bfloat16), (3, 200, 4, 140, False, torch.float32),
+                                                  (2, 500, 2, 260, True, torch.float32)])
+def test_decode_tensor_core_matches_dense_loop(B, V, H, steps, silu, dt):
+    """tcgen05 decode (bf16 operands) against the dense loop; several 128-slot tiles, the last one ragged."""
+    from mathbrain_b200.decode import DecodeState
+    from mathbrain_b200 import synth
+    torch.manual_seed(V + H)
+    N, D = 64, 64 * H
+    rhos = synth.make_rhos(N, 2.0, 64.0)
+    E_k = (torch.randn(V, D) * 0.2).to(dt)
+    E_v = (torch.randn(V, D) * 0.2).to(dt)
+    W = torch.randn(N, D) * 0.1
+    x = torch.randint(0, V, (B, steps))
+    Q = (torch.randn(B, H, steps, 64)).to(dt)
+    st = DecodeState(B, V, rhos.cuda(), capacity=384)
+    st_ref = DecodeState(B, V, rhos.cuda(), capacity=384)
+    state = torch.zeros(B, V, N)
+    last = torch.full((B, V), -1, dtype=torch.long)
+    worst = 0.0
+    for t in range(steps):
+        q = Q[:, :, t].cuda()
+        O = st.attend(q, E_k.cuda(), E_v.cuda(), W.cuda(), t, use_silu=silu, mode="tc_bf16")
+        if t % 37 == 0 or t == steps - 1:
+            O32 = st_ref.attend(q, E_k.cuda(), E_v.cuda(), W.cuda(), t, use_silu=silu, mode="fp32")
+            assert rel_err(O.cpu(), O32.cpu()) < 2e-2, t
+        st.update(x[:, t].cuda(), t)
+        st_ref.update(x[:, t].cuda(), t)
+        O_ref, _ = orc.decode_step(state, last, t, x[:, t], Q[:, :, t].float(), E_k.float(), E_v.float(), W, rhos, V,
+                                   use_silu=silu)
+        worst = max(worst, rel_err(O.cpu(), O_ref))
+        assert worst < 2e-2, t
+    st.check_overflow()
+    assert int(st._ws[:4].view(torch.int32).item()) == 0
+
+
+def test_decode_tensor_core_refuses_other_shapes():
+    from mathbrain_b200.decode import DecodeState
+    from mathbrain_b200 import _lib, synth
+    st = DecodeState(1, 50, synth.make_rhos(16, 2.0, 8.0).cuda(), capacity=32)
+    with pytest.raises(_lib.MbemaError):
+        st.attend(torch.zeros(1, 2, 64).cuda(), torch.zeros(50, 128).cuda(), torch.zeros(50, 128).cuda(),
+                  torch.zeros(16, 128).cuda(), 0, mode="tc_bf16")
