@@ -187,7 +187,8 @@ int mbema_decode_attend(const void* q, int q_dtype, const void* E_k, const void*
                         const float* rhos, const float* state, const int32_t* last_t, const int32_t* active,
                         const int32_t* n_active, float* O, int64_t B, int64_t H, int64_t hd, int64_t V, int64_t N,
                         int64_t Kcap, int64_t t_now, int64_t V_total, int flags, void* stream);
-/* Tensor-core variant of mbema_decode_attend (bf16 operands, fp32 accumulation; N = 64, hd = 64, H even): two
+/* Tensor-core variant of mbema_decode_attend (bf16 operands, fp32 accumulation; N = 64, hd = 64, H even, E_k/E_v
+ * stored as bf16): two
  * tcgen05 passes over 128-slot tiles with a softmax over all V_total slots between them.  Same arguments plus a
  * workspace of mbema_decode_attend_tc_workspace_bytes(B, H, Kcap) bytes; O is zeroed and accumulated by the call.
  * A bounded wait that ran out sets the int32 status word at the 256-byte aligned start of the workspace. */

@@ -1,31 +1,39 @@
-// Streaming decode on the tensor cores (MBEMA_MODE_TC_BF16, N = 64): attention of ONE query per sequence over the
-// slots seen so far.  Rows of the tile are SLOTS here (a thread per slot), so the softmax runs across threads; it is
-// split in three launches instead of an online update:
-//   pass 1   per (sequence, 128-slot tile, head pair): decayed state tile -> tcgen05.mma -> gate -> score s[b,h,k]
+// Streaming decode on the tensor cores (MBEMA_MODE_TC_BF16, N = 64, bf16 slot embeddings): attention of ONE query
+// per sequence over the slots seen so far.  Rows of the tile are SLOTS here (a thread per slot), so the softmax runs
+// across threads; it is split in three launches instead of an online update:
+//   pass 1   per (sequence, head pair, split): decayed state tile -> tcgen05.mma -> gate -> score s[b,h,k]
 //   softmax  per (sequence, head): probabilities over all V_total slots (the never-seen ones add exp(0 - max) each)
-//   pass 2   same tile product again, P.V: the bf16 tile (p * gate * E_v)[k, d] is summed over its 128 slots by a
-//            second tcgen05.mma against a ones operand (the column-sum trick of the training backward) and added to
-//            O[b,h,:] with fp32 atomics.
-// One tile per CTA, no pipeline inside the CTA: eight warps, several CTAs per SM overlap each other's latencies.
+//   pass 2   same tile product again, then P.V: the bf16 tile (p * gate * E_v)[k, d] is summed over its 128 slots by
+//            a second tcgen05.mma against a ones operand (the column-sum trick of the training backward), accumulated
+//            in TMEM over all tiles of the CTA and added to O[b,h,:] with one fp32 atomic per column.
+// A CTA walks up to MAXT 128-slot tiles.  All gathers (state rows, embedding rows) are cp.async copies two tiles
+// ahead into shared-memory rings, so no thread holds a gathered row in registers while it is in flight; the state
+// tile of tile i+1 is converted and its UMMA issued before the epilogue of tile i.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
+#include <algorithm>
 namespace mbema {
 namespace dtc {
 
 using namespace ptx;
 
-static constexpr int TM = 128, HD = 64, HPC = 2, N = 64, ACC_COLS = HPC * HD, THREADS = 256;
+static constexpr int TM = 128, HD = 64, HPC = 2, N = 64, ACC_COLS = HPC * HD, THREADS = 512, MAXT = 16;
 static constexpr int ATOM_BYTES = TM * 128;
+static constexpr int STAGE_BYTES = 2 * ATOM_BYTES;            // one state stage (128 rows x 256 B) or one E stage (2 heads)
+static constexpr int OFF_B = 0, OFF_A = ATOM_BYTES, OFF_S = 2 * ATOM_BYTES, OFF_E = OFF_S + 2 * STAGE_BYTES,
+                     OFF_V = OFF_E + 2 * STAGE_BYTES, OFF_ONES = OFF_V + 2 * ATOM_BYTES, OFF_Q = OFF_ONES + 2048,
+                     OFF_L2R = OFF_Q + 512, OFF_IDS = OFF_L2R + 256, OFF_DTS = OFF_IDS + MAXT * TM * 4,
+                     OFF_BARS = OFF_DTS + MAXT * TM * 4, SMEM_BYTES = OFF_BARS + 64 + 1024;
 
 struct Args {
     const void* q; int q_dt;
-    const void* Ek; const void* Ev; int e_dt;
+    const __nv_bfloat16* Ek; const __nv_bfloat16* Ev;
     const float* W; const float* rhos;
     const float* state; const int* last_t; const int* active; const int* n_active;
     float* scores;                 // [B, H, Kcap]: scores after pass 1, probabilities after the softmax
     float* O;                      // [B, H, 64]
-    int B, H, V, Kcap, t_now;
+    int B, H, V, Kcap, t_now, S;   // S: CTAs per (sequence, head pair); CTA s takes tiles s, s + S, ...
     float v_total;
     int listed_only;
 };
@@ -33,172 +41,271 @@ struct Args {
 __device__ __forceinline__ int sw128_off(int row, int col) {
     return row * 128 + ((((col >> 3) ^ (row & 7)) << 4) | ((col & 7) << 1));
 }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+template <int K>
+__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(K) : "memory"); }
 
-struct Bars { uint64_t acc_full; uint64_t pv_done; uint32_t tmem_base; int abort_flag; };
+struct Bars { uint64_t acc_full[2]; uint64_t pv_done; uint32_t tmem_base; int abort_flag; };
 
-// dynamic smem (base aligned to 1024): A 16 KB | B 16 KB | Vg 32 KB | ones 2 KB | q 512 B | l2r 256 B | bars
 template <int PASS, bool SILU>
-__global__ void __launch_bounds__(THREADS) k_decode_tc(Args a, int* status) {
+__global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    unsigned char* A_sh = sm;
-    unsigned char* B_sh = sm + ATOM_BYTES;
-    unsigned char* V_sh = sm + 2 * ATOM_BYTES;                 // [head][128 k][64 d] bf16, MN-major operand of pass 2
-    unsigned char* ones_sh = sm + 4 * ATOM_BYTES;
-    float* q_sh = reinterpret_cast<float*>(sm + 4 * ATOM_BYTES + 2048);            // q / sqrt(hd) of the two heads
-    float* l2r_sh = reinterpret_cast<float*>(sm + 4 * ATOM_BYTES + 2048 + 512);
-    Bars* bars = reinterpret_cast<Bars*>(sm + 4 * ATOM_BYTES + 2048 + 768);
+    unsigned char* A_sh = sm + OFF_A;
+    unsigned char* B_sh = sm + OFF_B;
+    unsigned char* S_st = sm + OFF_S;       // [2][128 rows][16 chunks of 4 floats, chunk ^ (row & 15)]
+    unsigned char* E_st = sm + OFF_E;       // [2][head][128 rows][8 chunks of 8 bf16, chunk ^ (row & 7)]
+    unsigned char* V_sh = sm + OFF_V;       // [head][128 k][64 d] bf16, MN-major operand of the column sum
+    unsigned char* ones_sh = sm + OFF_ONES;
+    float* q_sh = reinterpret_cast<float*>(sm + OFF_Q);                 // q / sqrt(hd) of the two heads
+    float* l2r_sh = reinterpret_cast<float*>(sm + OFF_L2R);
+    int* ids_sh = reinterpret_cast<int*>(sm + OFF_IDS);                 // slot of every row of this CTA's tiles, -1 = none
+    float* dts_sh = reinterpret_cast<float*>(sm + OFF_DTS);             // steps since that slot's last update
+    Bars* bars = reinterpret_cast<Bars*>(sm + OFF_BARS);
     volatile int* abort_flag = &bars->abort_flag;
 
-    const int tile = blockIdx.x, hp = blockIdx.y, b = blockIdx.z;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int wg = tid >> 7, row = tid & 127;
+    const int split = blockIdx.x, hp = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int cg = tid >> 7, row = tid & 127;                   // column group: head cg >> 1 of the pair, 32-column half cg & 1
+    const int hh = cg >> 1, half = cg & 1;
     const int D = a.H * HD;
     const int na = min(a.n_active[b], a.Kcap);
-    if (tile * TM >= na) return;                                // uniform per CTA
-    const int h = hp * HPC + wg;
-    const int k = tile * TM + row;
-    const bool ok = k < na;
-    const int v = ok ? a.active[(size_t)b * a.Kcap + k] : 0;
+    const int ntile_b = (na + TM - 1) / TM;
+    if (split >= ntile_b) return;                               // uniform per CTA
+    const int nt = min((ntile_b - split + a.S - 1) / a.S, MAXT);
+    const int h = hp * HPC + hh;
 
     if (tid == 0) {
-        mbar_init(&bars->acc_full, 1);
+        mbar_init(&bars->acc_full[0], 1);
+        mbar_init(&bars->acc_full[1], 1);
         mbar_init(&bars->pv_done, 1);
         bars->abort_flag = *reinterpret_cast<volatile int*>(status);
         fence_barrier_init();
     }
     if (warp == 0) {
-        tmem_alloc(&bars->tmem_base, 128);
+        tmem_alloc(&bars->tmem_base, 512);
         tmem_relinquish();
     }
-    // slot-embedding row of this thread's slot for its head: 64 bf16 / fp32 values, fetched before anything waits
-    float er[HD];
-    {
-        const void* src = (PASS == 1) ? a.Ek : a.Ev;
-        const size_t off = (size_t)v * D + h * HD;
+    // B operand values first (independent loads), then the slot ids and their ages (two dependent rounds of loads)
+    float4 wv[4];
 #pragma unroll
-        for (int i = 0; i < HD; i += 4) {
-            const float4 x = ld4_dyn_f32(src, a.e_dt, off + i);
-            er[i] = x.x; er[i + 1] = x.y; er[i + 2] = x.z; er[i + 3] = x.w;
+    for (int j = 0; j < 4; ++j) {
+        const int g = tid + THREADS * j, n = g >> 5, dd4 = (g & 31) * 4;
+        wv[j] = __ldg(reinterpret_cast<const float4*>(a.W + (size_t)n * D + hp * ACC_COLS + dd4));
+    }
+    int vv[MAXT * TM / THREADS];
+#pragma unroll
+    for (int j = 0; j < MAXT * TM / THREADS; ++j) {
+        const int idx = tid + THREADS * j;
+        const int k = (split + (idx >> 7) * a.S) * TM + (idx & 127);
+        vv[j] = (idx < nt * TM && k < na) ? a.active[(size_t)b * a.Kcap + k] : -1;
+    }
+#pragma unroll
+    for (int j = 0; j < MAXT * TM / THREADS; ++j) {
+        const int idx = tid + THREADS * j;
+        if (idx < nt * TM) {
+            ids_sh[idx] = vv[j];
+            dts_sh[idx] = vv[j] >= 0 ? (float)(a.t_now - a.last_t[(size_t)b * a.V + vv[j]]) : 0.f;
         }
     }
-    const float prob = (PASS == 2 && ok) ? a.scores[((size_t)b * a.H + h) * a.Kcap + k] : 0.f;
+    __syncthreads();
+
+    auto issue_state = [&](int i) {
+        if (i < nt) {
+            unsigned char* dst = S_st + (i & 1) * STAGE_BYTES;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int idx = tid + THREADS * j, r = idx >> 4, c = idx & 15;
+                const int v = ids_sh[i * TM + r];
+                if (v >= 0) cp_async16(dst + r * 256 + ((c ^ (r & 15)) << 4), a.state + ((size_t)b * a.V + v) * N + c * 4);
+            }
+        }
+        cp_commit();
+    };
+    auto issue_emb = [&](int i) {
+        if (i < nt) {
+            const __nv_bfloat16* E = (PASS == 1) ? a.Ek : a.Ev;
+            unsigned char* dst = E_st + (i & 1) * STAGE_BYTES;
+#pragma unroll
+            for (int e = 0; e < HPC; ++e)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int idx = tid + THREADS * j, r = idx >> 3, c = idx & 7;
+                    const int v = ids_sh[i * TM + r];
+                    if (v >= 0) cp_async16(dst + e * ATOM_BYTES + r * 128 + ((c ^ (r & 7)) << 4), E + (size_t)v * D + (hp * HPC + e) * HD + c * 8);
+                }
+        }
+        cp_commit();
+    };
+    issue_state(0);
+    issue_emb(0);
+    issue_state(1);
+    issue_emb(1);
     {
         const float wscale = SILU ? 0.5f : 1.0f;
-        for (int i = tid; i < N * ACC_COLS; i += THREADS) {
-            const int n = i / ACC_COLS, dd = i % ACC_COLS;
-            *reinterpret_cast<__nv_bfloat16*>(B_sh + sw128_off(dd, n)) = __float2bfloat16(a.W[(size_t)n * D + hp * ACC_COLS + dd] * wscale);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int g = tid + THREADS * j, n = g >> 5, dd4 = (g & 31) * 4;
+            *reinterpret_cast<__nv_bfloat16*>(B_sh + sw128_off(dd4 + 0, n)) = __float2bfloat16(wv[j].x * wscale);
+            *reinterpret_cast<__nv_bfloat16*>(B_sh + sw128_off(dd4 + 1, n)) = __float2bfloat16(wv[j].y * wscale);
+            *reinterpret_cast<__nv_bfloat16*>(B_sh + sw128_off(dd4 + 2, n)) = __float2bfloat16(wv[j].z * wscale);
+            *reinterpret_cast<__nv_bfloat16*>(B_sh + sw128_off(dd4 + 3, n)) = __float2bfloat16(wv[j].w * wscale);
         }
         if (PASS == 2)
             for (int i = tid; i < 1024; i += THREADS) reinterpret_cast<__nv_bfloat16*>(ones_sh)[i] = __float2bfloat16(1.0f);
         if (tid < N) l2r_sh[tid] = log2f(a.rhos[tid]);
         if (tid < ACC_COLS) q_sh[tid] = ld_dyn_f32(a.q, a.q_dt, ((size_t)b * a.H + hp * HPC) * HD + tid) * 0.125f;
     }
-    __syncthreads();
-    // decayed state tile: row = slot, this thread fills channels [32 wg, 32 wg + 32)
-    {
-        const float dt = ok ? (float)(a.t_now - a.last_t[(size_t)b * a.V + v]) : 0.f;
-        const float* srow = a.state + ((size_t)b * a.V + v) * N + 32 * wg;
+    // state stage -> decayed bf16 A tile; this thread: row `row`, channels [16 cg, 16 cg + 16)
+    auto convert = [&](int i) {
+        const unsigned char* src = S_st + (i & 1) * STAGE_BYTES + row * 256;
+        const bool ok = ids_sh[i * TM + row] >= 0;
+        const float dt = dts_sh[i * TM + row];
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
+        for (int cc = 0; cc < 2; ++cc) {
             uint4 pk = make_uint4(0u, 0u, 0u, 0u);
             if (ok) {
-                const float4 s0 = __ldg(reinterpret_cast<const float4*>(srow + cc * 8));
-                const float4 s1 = __ldg(reinterpret_cast<const float4*>(srow + cc * 8 + 4));
-                const float* lr = l2r_sh + 32 * wg + cc * 8;
-                pk.x = pack_bf16x2(s0.x * exp2f(dt * lr[0]), s0.y * exp2f(dt * lr[1]));
-                pk.y = pack_bf16x2(s0.z * exp2f(dt * lr[2]), s0.w * exp2f(dt * lr[3]));
-                pk.z = pack_bf16x2(s1.x * exp2f(dt * lr[4]), s1.y * exp2f(dt * lr[5]));
-                pk.w = pack_bf16x2(s1.z * exp2f(dt * lr[6]), s1.w * exp2f(dt * lr[7]));
+                const int c0 = 4 * cg + 2 * cc;
+                const float4 s0 = *reinterpret_cast<const float4*>(src + ((c0 ^ (row & 15)) << 4));
+                const float4 s1 = *reinterpret_cast<const float4*>(src + (((c0 + 1) ^ (row & 15)) << 4));
+                const float* lr = l2r_sh + 16 * cg + cc * 8;
+                pk.x = pack_bf16x2(s0.x * ex2_approx(dt * lr[0]), s0.y * ex2_approx(dt * lr[1]));
+                pk.y = pack_bf16x2(s0.z * ex2_approx(dt * lr[2]), s0.w * ex2_approx(dt * lr[3]));
+                pk.z = pack_bf16x2(s1.x * ex2_approx(dt * lr[4]), s1.y * ex2_approx(dt * lr[5]));
+                pk.w = pack_bf16x2(s1.z * ex2_approx(dt * lr[6]), s1.w * ex2_approx(dt * lr[7]));
             }
-            *reinterpret_cast<uint4*>(A_sh + row * 128 + (((4 * wg + cc) ^ (row & 7)) << 4)) = pk;
+            *reinterpret_cast<uint4*>(A_sh + row * 128 + (((2 * cg + cc) ^ (row & 7)) << 4)) = pk;
         }
-    }
+    };
+    const uint32_t idesc = umma_idesc_bf16(TM, ACC_COLS, 0, 0);
+    const uint64_t da = umma_desc_k_sw128(smem_u32(A_sh)), db = umma_desc_k_sw128(smem_u32(B_sh));
+    auto issue_gate = [&](uint32_t tmem_base, int i) {
+#pragma unroll
+        for (int k16 = 0; k16 < 4; ++k16)
+            umma_bf16_ss(tmem_base + (uint32_t)((i & 1) * ACC_COLS), da + (uint64_t)((k16 * 32) >> 4), db + (uint64_t)((k16 * 32) >> 4), idesc, k16 != 0 ? 1u : 0u);
+        umma_commit(&bars->acc_full[i & 1]);
+    };
+
+    cp_wait<3>();                                               // state stage of tile 0 landed (this thread's copies)
+    __syncthreads();                                            // ... everyone's; B tile, q, barriers and TMEM address too
+    tc_fence_after_sync();
+    const uint32_t tmem_base = bars->tmem_base;
+    convert(0);
     fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    const uint32_t tmem_base = bars->tmem_base;
-    if (tid == 0 && !bars->abort_flag) {
-        const uint32_t idesc = umma_idesc_bf16(TM, ACC_COLS, 0, 0);
-        const uint64_t da = umma_desc_k_sw128(smem_u32(A_sh)), db = umma_desc_k_sw128(smem_u32(B_sh));
-#pragma unroll
-        for (int k16 = 0; k16 < 4; ++k16)
-            umma_bf16_ss(tmem_base, da + (uint64_t)((k16 * 32) >> 4), db + (uint64_t)((k16 * 32) >> 4), idesc, k16 != 0 ? 1u : 0u);
-        umma_commit(&bars->acc_full);
-    }
-    if (!bars->abort_flag) mbar_wait(&bars->acc_full, 0u, abort_flag);
-    tc_fence_after_sync();
-    const uint32_t t_acc = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(wg * HD);
-    const float* qh = q_sh + wg * HD;
-    if (PASS == 1) {
-        float sp[2] = {0.f, 0.f};
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            float pre[32];
-            tmem_ld_32x32b_x32(t_acc + c * 32, pre);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-                const float h0 = pre[j], h1 = pre[j + 1];
-                const float g0 = SILU ? fmaf(h0, tanh_approx(h0), h0) : h0;
-                const float g1 = SILU ? fmaf(h1, tanh_approx(h1), h1) : h1;
-                sp[0] = fmaf(g0 * qh[c * 32 + j], er[c * 32 + j], sp[0]);
-                sp[1] = fmaf(g1 * qh[c * 32 + j + 1], er[c * 32 + j + 1], sp[1]);
-            }
-        }
-        if (ok) a.scores[((size_t)b * a.H + h) * a.Kcap + k] = sp[0] + sp[1];
-    } else {
-        unsigned char* vrow = V_sh + wg * ATOM_BYTES + row * 128;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            float pre[32];
-            tmem_ld_32x32b_x32(t_acc + c * 32, pre);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j8 = 0; j8 < 4; ++j8) {
-                uint32_t w[4];
-#pragma unroll
-                for (int pr = 0; pr < 4; ++pr) {
-                    const int j = j8 * 8 + pr * 2;
-                    const float h0 = pre[j], h1 = pre[j + 1];
-                    const float g0 = SILU ? fmaf(h0, tanh_approx(h0), h0) : h0;
-                    const float g1 = SILU ? fmaf(h1, tanh_approx(h1), h1) : h1;
-                    w[pr] = pack_bf16x2(prob * g0 * er[c * 32 + j], prob * g1 * er[c * 32 + j + 1]);
-                }
-                st_shared_v4(vrow + (((c * 4 + j8) ^ (row & 7)) << 4), w[0], w[1], w[2], w[3]);
-            }
-        }
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        __syncthreads();                    // every warp has read its accumulators and written its part of the tile
+    if (tid == 0 && !bars->abort_flag) issue_gate(tmem_base, 0);
+    issue_state(2);
+
+    for (int i = 0; i < nt; ++i) {
+        cp_wait<2>();                                           // state stage of tile i+1 and embedding stage of tile i
+        __syncthreads();
+        if (!bars->abort_flag) mbar_wait(&bars->acc_full[i & 1], (uint32_t)((i >> 1) & 1), abort_flag);   // A tile free, accumulators of tile i ready
         tc_fence_after_sync();
-        if (tid == 0 && !bars->abort_flag) {
-            const uint32_t idesc = umma_idesc_bf16(ACC_COLS, 16, 1, 0);
-            const uint64_t dv = umma_desc_mn_sw128(smem_u32(V_sh), ATOM_BYTES, 1024), d1 = umma_desc_k_sw128(smem_u32(ones_sh));
-#pragma unroll
-            for (int ks = 0; ks < TM / 16; ++ks)
-                umma_bf16_ss(tmem_base, dv + (uint64_t)(ks * (2048 >> 4)), d1, idesc, ks != 0 ? 1u : 0u);   // reuses the gate columns
-            umma_commit(&bars->pv_done);
+        if (i + 1 < nt) {
+            convert(i + 1);
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            __syncthreads();
+            tc_fence_after_sync();
+            if (tid == 0 && !bars->abort_flag) issue_gate(tmem_base, i + 1);
         }
-        if (!bars->abort_flag) mbar_wait(&bars->pv_done, 0u, abort_flag);
-        tc_fence_after_sync();
-        if (wg == 0) {                      // lane = output column d of the head pair
-            float x;
+        issue_state(i + 3);
+
+        const bool ok = ids_sh[i * TM + row] >= 0;
+        const uint32_t t_acc = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)((i & 1) * ACC_COLS + hh * HD + half * 32);
+        const unsigned char* erow = E_st + (i & 1) * STAGE_BYTES + hh * ATOM_BYTES + row * 128;
+        const float* qh = q_sh + hh * HD + half * 32;
+        const int k = (split + i * a.S) * TM + row;
+        if (PASS == 1) {
+            float sp[2] = {0.f, 0.f};
             {
-                uint32_t r;
-                asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(tmem_base + ((uint32_t)((warp & 3) * 32) << 16)) : "memory");
+                float pre[32];
+                tmem_ld_32x32b_x32(t_acc, pre);
                 tmem_wait_ld();
-                x = __uint_as_float(r);
+#pragma unroll
+                for (int j8 = 0; j8 < 4; ++j8) {
+                    const uint4 e = *reinterpret_cast<const uint4*>(erow + (((half * 4 + j8) ^ (row & 7)) << 4));
+                    const uint32_t ew[4] = {e.x, e.y, e.z, e.w};
+#pragma unroll
+                    for (int pr = 0; pr < 4; ++pr) {
+                        const int j = j8 * 8 + pr * 2;
+                        const float h0 = pre[j], h1 = pre[j + 1];
+                        const float g0 = SILU ? fmaf(h0, tanh_approx(h0), h0) : h0;
+                        const float g1 = SILU ? fmaf(h1, tanh_approx(h1), h1) : h1;
+                        sp[0] = fmaf(g0 * qh[j], bf16_lo(ew[pr]), sp[0]);
+                        sp[1] = fmaf(g1 * qh[j + 1], bf16_hi(ew[pr]), sp[1]);
+                    }
+                }
             }
-            atomicAdd(a.O + ((size_t)b * a.H + hp * HPC) * HD + row, x);
+            // the two 32-column halves of a head add into a zeroed score: two addends, so the sum is order-independent
+            if (ok) atomicAdd(a.scores + ((size_t)b * a.H + h) * a.Kcap + k, sp[0] + sp[1]);
+            tc_fence_before_sync();
+            __syncthreads();                                    // embedding stage i & 1 is free again
+        } else {
+            const float prob = ok ? a.scores[((size_t)b * a.H + h) * a.Kcap + k] : 0.f;
+            if (i > 0 && !bars->abort_flag) mbar_wait(&bars->pv_done, (uint32_t)((i - 1) & 1), abort_flag);   // V tile free
+            unsigned char* vrow = V_sh + hh * ATOM_BYTES + row * 128;
+            {
+                float pre[32];
+                tmem_ld_32x32b_x32(t_acc, pre);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j8 = 0; j8 < 4; ++j8) {
+                    const uint4 e = *reinterpret_cast<const uint4*>(erow + (((half * 4 + j8) ^ (row & 7)) << 4));
+                    const uint32_t ew[4] = {e.x, e.y, e.z, e.w};
+                    uint32_t w[4];
+#pragma unroll
+                    for (int pr = 0; pr < 4; ++pr) {
+                        const int j = j8 * 8 + pr * 2;
+                        const float h0 = pre[j], h1 = pre[j + 1];
+                        const float g0 = SILU ? fmaf(h0, tanh_approx(h0), h0) : h0;
+                        const float g1 = SILU ? fmaf(h1, tanh_approx(h1), h1) : h1;
+                        w[pr] = ok ? mul_bf16x2(pack_bf16x2(prob * g0, prob * g1), ew[pr]) : 0u;
+                    }
+                    st_shared_v4(vrow + (((half * 4 + j8) ^ (row & 7)) << 4), w[0], w[1], w[2], w[3]);
+                }
+            }
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            __syncthreads();                // accumulators and embedding stage read, V tile written, by every warp
+            tc_fence_after_sync();
+            if (tid == 0 && !bars->abort_flag) {
+                const uint32_t idesc2 = umma_idesc_bf16(ACC_COLS, 16, 1, 0);
+                const uint64_t dv = umma_desc_mn_sw128(smem_u32(V_sh), ATOM_BYTES, 1024), d1 = umma_desc_k_sw128(smem_u32(ones_sh));
+#pragma unroll
+                for (int ks = 0; ks < TM / 16; ++ks)
+                    umma_bf16_ss(tmem_base + 2 * ACC_COLS, dv + (uint64_t)(ks * (2048 >> 4)), d1, idesc2, (i != 0 || ks != 0) ? 1u : 0u);
+                umma_commit(&bars->pv_done);
+            }
+        }
+        issue_emb(i + 2);
+    }
+    cp_wait<0>();
+    if (PASS == 2) {
+        if (!bars->abort_flag) mbar_wait(&bars->pv_done, (uint32_t)((nt - 1) & 1), abort_flag);
+        tc_fence_after_sync();
+        if (cg == 0) {                      // lane = output column d of the head pair
+            uint32_t r;
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(tmem_base + 2 * ACC_COLS + ((uint32_t)((warp & 3) * 32) << 16)) : "memory");
+            tmem_wait_ld();
+            atomicAdd(a.O + ((size_t)b * a.H + hp * HPC) * HD + row, __uint_as_float(r));
         }
     }
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 0) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, 128);
+        tmem_dealloc(tmem_base, 512);
     }
     if (tid == 0 && bars->abort_flag) atomicExch(status, 1);
 }
@@ -251,17 +358,41 @@ extern "C" int mbema_decode_attend_tc(const void* q, int q_dtype, const void* E_
     if (B == 0) return MBEMA_OK;
     if (!q || !E_k || !E_v || !W_pe || !rhos || !state || !last_t || !active || !n_active || !O || !workspace) return MBEMA_ERR_NULL;
     if ((q_dtype != MBEMA_F32 && q_dtype != MBEMA_BF16) || (e_dtype != MBEMA_F32 && e_dtype != MBEMA_BF16)) return MBEMA_ERR_DTYPE;
-    if (((uintptr_t)E_k | (uintptr_t)E_v) & 15) return MBEMA_ERR_ALIGN;
+    if (e_dtype != MBEMA_BF16) return MBEMA_ERR_UNSUPPORTED;     // rows are copied as stored into the bf16 operand rings
+    if (((uintptr_t)E_k | (uintptr_t)E_v | (uintptr_t)state) & 15) return MBEMA_ERR_ALIGN;
     if (workspace_bytes < mbema_decode_attend_tc_workspace_bytes(B, H, Kcap)) return MBEMA_ERR_WORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
     int* status = reinterpret_cast<int*>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255));
-    dtc::Args a{q, q_dtype, E_k, E_v, e_dtype, W_pe, rhos, state, last_t, active, n_active,
-                reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(status) + 256), O,
-                (int)B, (int)H, (int)V, (int)Kcap, (int)t_now, (float)V_total, (flags & MBEMA_FLAG_LISTED_ONLY) ? 1 : 0};
+    // CTAs per (sequence, head pair)
+    const int ntiles = (int)((Kcap + dtc::TM - 1) / dtc::TM);
+    int sm_count = 148;
+    {
+        int dev = 0;
+        MBEMA_CUDA_TRY(cudaGetDevice(&dev));
+        MBEMA_CUDA_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+    }
+    // every CTA costs about 1.5 tile times of setup and the grid runs in waves of one CTA per SM: pick the split
+    // with the fewest (waves x (tiles per CTA + setup)), at most MAXT tiles per CTA
+    int64_t S = ntiles;
+    {
+        const int64_t groups = B * (H / 2), s_min = (ntiles + dtc::MAXT - 1) / dtc::MAXT;
+        double best = 1e30;
+        for (int64_t c = s_min; c <= ntiles; ++c) {
+            const int64_t waves = (groups * c + sm_count - 1) / sm_count, per = (ntiles + c - 1) / c;
+            const double cost = (double)waves * ((double)per + 1.5);
+            if (cost < best) { best = cost; S = c; }
+        }
+    }
+    if (S > 65535) return MBEMA_ERR_UNSUPPORTED;
+    dtc::Args a{q, q_dtype, reinterpret_cast<const __nv_bfloat16*>(E_k), reinterpret_cast<const __nv_bfloat16*>(E_v), W_pe, rhos,
+                state, last_t, active, n_active, reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(status) + 256), O,
+                (int)B, (int)H, (int)V, (int)Kcap, (int)t_now, (int)S, (float)V_total,
+                (flags & MBEMA_FLAG_LISTED_ONLY) ? 1 : 0};
     MBEMA_CUDA_TRY(cudaMemsetAsync(status, 0, 256, st));
     MBEMA_CUDA_TRY(cudaMemsetAsync(O, 0, (size_t)B * H * hd * sizeof(float), st));
-    const int smem = 4 * dtc::ATOM_BYTES + 2048 + 768 + 64 + 1024;
-    dim3 grid((unsigned)((Kcap + dtc::TM - 1) / dtc::TM), (unsigned)(H / 2), (unsigned)B);
+    MBEMA_CUDA_TRY(cudaMemsetAsync(a.scores, 0, (size_t)B * H * Kcap * sizeof(float), st));
+    const int smem = dtc::SMEM_BYTES;
+    dim3 grid((unsigned)S, (unsigned)(H / 2), (unsigned)B);
     const bool silu = (flags & MBEMA_FLAG_SILU) != 0;
 #define MBEMA_DECODE_LAUNCH(P_, S_)                                                                                    \
     do {                                                                                                              \

@@ -45,6 +45,8 @@ class DecodeState:
         if mode is None:
             mode = "tc_bf16" if (get_options()["mode"] == "tc_bf16" and tc_ok) else "fp32"
         if mode == "tc_bf16":
+            if E_k.dtype != torch.bfloat16:          # the kernel copies embedding rows as stored: keep bf16 tables to avoid this cast
+                E_k, E_v = E_k.to(torch.bfloat16), E_v.to(torch.bfloat16)
             need = lib.mbema_decode_attend_tc_workspace_bytes(B, H, self.cap)
             if self._ws is None or self._ws.numel() < need:
                 self._ws = torch.empty(need, dtype=torch.uint8, device=q.device)

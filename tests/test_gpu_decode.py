@@ -88,3 +88,34 @@ def test_decode_tensor_core_refuses_other_shapes():
     with pytest.raises(_lib.MbemaError):
         st.attend(torch.zeros(1, 2, 64).cuda(), torch.zeros(50, 128).cuda(), torch.zeros(50, 128).cuda(),
                   torch.zeros(16, 128).cuda(), 0, mode="tc_bf16")
+
+
+def test_decode_tensor_core_many_tiles_per_cta():
+    """Warm state with a different number of seen slots per sequence (up to 15 tiles of 128), enough sequences and
+    heads that one CTA walks several tiles; compared with the fp32 kernel, which the dense loop checks above."""
+    from mathbrain_b200.decode import DecodeState
+    from mathbrain_b200 import synth
+    g = torch.Generator().manual_seed(5)
+    B, V, N, H, cap = 64, 3000, 64, 8, 2048
+    D = 64 * H
+    rhos = synth.make_rhos(N, 2.0, 256.0).cuda()
+    st = DecodeState(B, V, rhos, capacity=cap)
+    for b in range(B):
+        K = int(torch.randint(1, 1900, (1,), generator=g)) if b else 1900
+        seen = torch.randperm(V, generator=g)[:K].cuda()
+        st.active[b, :K] = seen.to(torch.int32)
+        st.last_t[b, seen] = torch.randint(0, 4000, (K,), generator=g).to(torch.int32).cuda()
+        st.state[b, seen] = (torch.rand(K, N, generator=g) * 3 + 0.5).cuda()
+        st.n_active[b] = K
+    E_k = (torch.randn(V, D, generator=g) * 0.2).to(torch.bfloat16).cuda()
+    E_v = (torch.randn(V, D, generator=g) * 0.2).to(torch.bfloat16).cuda()
+    W = (torch.randn(N, D, generator=g) * 0.1).cuda()
+    q = torch.randn(B, H, 64, generator=g).cuda()
+    for silu in (True, False):
+        O_tc = st.attend(q, E_k, E_v, W, 4000, use_silu=silu, mode="tc_bf16")
+        O_32 = st.attend(q, E_k, E_v, W, 4000, use_silu=silu, mode="fp32")
+        assert rel_err(O_tc.cpu(), O_32.cpu()) < 2e-2, silu
+        assert int(st._ws[:4].view(torch.int32).item()) == 0
+        O_tc2 = st.attend(q, E_k, E_v, W, 4000, use_silu=silu, mode="tc_bf16", listed_only=True)
+        O_322 = st.attend(q, E_k, E_v, W, 4000, use_silu=silu, mode="fp32", listed_only=True)
+        assert rel_err(O_tc2.cpu(), O_322.cpu()) < 2e-2, silu
