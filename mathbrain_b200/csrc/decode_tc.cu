@@ -207,6 +207,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
     issue_state(2);
 
     for (int i = 0; i < nt; ++i) {
+        float prob = 0.f;                                       // fetched before the conversion work below, used after it
+        if (PASS == 2 && ids_sh[i * TM + row] >= 0) prob = a.scores[((size_t)b * a.H + h) * a.Kcap + (split + i * a.S) * TM + row];
         cp_wait<2>();                                           // state stage of tile i+1 and embedding stage of tile i
         __syncthreads();
         if (!bars->abort_flag) mbar_wait(&bars->acc_full[i & 1], (uint32_t)((i >> 1) & 1), abort_flag);   // A tile free, accumulators of tile i ready
@@ -252,7 +254,6 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
             tc_fence_before_sync();
             __syncthreads();                                    // embedding stage i & 1 is free again
         } else {
-            const float prob = ok ? a.scores[((size_t)b * a.H + h) * a.Kcap + k] : 0.f;
             if (i > 0 && !bars->abort_flag) mbar_wait(&bars->pv_done, (uint32_t)((i - 1) & 1), abort_flag);   // V tile free
             unsigned char* vrow = V_sh + hh * ATOM_BYTES + row * 128;
             {
