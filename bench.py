@@ -447,9 +447,9 @@ def main():
                     "d2h_bytes_per_step": 4},
             "roofline": {"bound": "tensor", "kernel": "flash-EMA backward (one layer)", "achieved": ach,
                          "peak": pk["tflops"], "unit": "TFLOP/s", "frac": ach / pk["tflops"],
-                         # DRAM bytes per launch: 23.0 B per slot-step (dram__bytes_read+write of an ncu capture of
-                         # the B=16 case, 313 MB for 13.59 M slot-steps), scaled by the slot-steps of this launch
-                         "traffic": 23.0 * hp.slot_steps, "traffic_unit": "bytes/launch (scaled from profiles/flash_bwd_tc_B16_T512_N64.md)",
+                         # DRAM bytes per launch: 22.7 B per slot-step (dram__bytes_read+write of an ncu capture of
+                         # the B=16 case, 308 MB for 13.59 M slot-steps), scaled by the slot-steps of this launch
+                         "traffic": 22.7 * hp.slot_steps, "traffic_unit": "bytes/launch (scaled from profiles/flash_bwd_tc_B16_T512_N64.md)",
                          "peak_source": pk["src"], "flops_per_launch": flops_bwd, "ms_per_launch": avg_bwd * 1000.0,
                          "forward": {"achieved": flops_fwd / avg_fwd / 1e12, "ms_per_launch": avg_fwd * 1000.0},
                          "scan_ms": sum(scan_ms) / max(1, len(scan_ms)), "gate_ms_per_step": sum(gate_ms) / args.steps},
