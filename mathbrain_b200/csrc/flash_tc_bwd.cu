@@ -45,7 +45,7 @@ static constexpr int RING_STAGE_BYTES = 256 + 2 * ACC_COLS * 4;
 static constexpr int MAX_SLOTS = 4096;
 
 struct Smem {
-    int a_off, b_off, z_off, ones_off, r_off, e_off, e2_off, ring_off, tok_off, slot_off, key_off, bar_off, total;
+    int a_off, b_off, z_off, ones_off, r_off, e2_off, ring_off, tok_off, slot_off, key_off, bar_off, total;
 };
 
 __host__ __device__ inline Smem smem_layout(int K, int NK) {
@@ -60,8 +60,7 @@ __host__ __device__ inline Smem smem_layout(int K, int NK) {
     // the recompute must build bit-identical state tiles or p = exp(s - LSE) stops summing to one);
     // NK = 2: fp32, two levels [8][128] (r / 16) and [16][128] (r % 16), product rounded once like the forward's fp32 table
     s.r_off = o; o += NK == 1 ? TM * 64 * 2 : 24 * 128 * 4;
-    s.e_off = o; o += NA * 2 * ACC_COLS * 4;      // E_k / E_v rows as fp32 ...
-    s.e2_off = o; o += NA * 2 * ACC_COLS * 2;     // ... and as bf16 (operands of the packed tile arithmetic)
+    s.e2_off = o; o += NA * 2 * ACC_COLS * 2;     // E_k / E_v rows as bf16 (operands of the packed epilogue arithmetic)
     s.ring_off = o; o += RING * RING_STAGE_BYTES;
     s.tok_off = o; o += TM * 4;
     s.slot_off = o; o += ((K * 2 + 15) / 16) * 16;
@@ -109,7 +108,6 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
     unsigned char* ones_sh = sm + L.ones_off;
     float* R_sh = reinterpret_cast<float*>(sm + L.r_off);                       // NK = 2
     __nv_bfloat16* Rb_sh = reinterpret_cast<__nv_bfloat16*>(sm + L.r_off);      // NK = 1
-    float* E_sh = reinterpret_cast<float*>(sm + L.e_off);
     __nv_bfloat16* E2_sh = reinterpret_cast<__nv_bfloat16*>(sm + L.e2_off);
     unsigned char* ring_sh = sm + L.ring_off;
     int* tok_sh = reinterpret_cast<int*>(sm + L.tok_off);
@@ -305,8 +303,6 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                     ekv = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rg + 256)[row]);
                     evv = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rg + 256 + ACC_COLS * 4)[row]);
                 }
-                E_sh[sa * 2 * ACC_COLS + row] = ekv;
-                E_sh[sa * 2 * ACC_COLS + ACC_COLS + row] = evv;
                 E2_sh[sa * 2 * ACC_COLS + row] = __float2bfloat16(ekv);
                 E2_sh[sa * 2 * ACC_COLS + ACC_COLS + row] = __float2bfloat16(evv);
             }
@@ -417,43 +413,45 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             const int sa = i % NA, sc = i % NACC;
             mbar_wait(&bars->acc_full[sc], (uint32_t)((i / NACC) & 1), abort_flag);
             tc_fence_after_sync();
-            const float* ek = E_sh + sa * 2 * ACC_COLS + wg * HD;
-            const float* ev = ek + ACC_COLS;
             const uint32_t t_acc = t_lane + (uint32_t)(sc * ACC_COLS + wg * HD);
             // ---- pass 1: gate, its derivative, score and dO.V; gate and derivative are kept as packed bf16 pairs
             uint32_t g2[HD / 2], dsl2[HD / 2];
             float sp[2] = {0.f, 0.f}, dpp[2] = {0.f, 0.f};
+            const uint32_t* ek2a = reinterpret_cast<const uint32_t*>(E2_sh + sa * 2 * ACC_COLS + wg * HD);
+            const uint32_t* ev2a = ek2a + ACC_COLS / 2;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 float pre[16];
                 tmem_ld_32x32b_x16(t_acc + c * 16, pre);
                 tmem_wait_ld();
 #pragma unroll
-                for (int pr = 0; pr < 8; ++pr) {
-                    const int j = c * 16 + pr * 2;
-                    const float2 e1 = *reinterpret_cast<const float2*>(ek + j);
-                    const float2 e2 = *reinterpret_cast<const float2*>(ev + j);
-                    const uint32_t qq = q2[j / 2], dd = do2[j / 2];
-                    const float qv[2] = {bf16_lo_pinned(qq), bf16_hi_pinned(qq)};
-                    const float dv[2] = {bf16_lo_pinned(dd), bf16_hi_pinned(dd)};
-                    const float ee1[2] = {e1.x, e1.y}, ee2[2] = {e2.x, e2.y};
-                    float g[2], dsl[2];
+                for (int j8 = 0; j8 < 2; ++j8) {
+                    uint32_t sacc = 0u, dacc = 0u;        // bf16 pair sums of 4 terms each, flushed to fp32 per 8 columns
+                    const int w0 = c * 8 + j8 * 4;
+                    const uint4 ekp = *reinterpret_cast<const uint4*>(ek2a + w0);
+                    const uint4 evp = *reinterpret_cast<const uint4*>(ev2a + w0);
+                    const uint32_t ekw[4] = {ekp.x, ekp.y, ekp.z, ekp.w}, evw[4] = {evp.x, evp.y, evp.z, evp.w};
 #pragma unroll
-                    for (int v = 0; v < 2; ++v) {
-                        const float hh = pre[pr * 2 + v];
+                    for (int pr = 0; pr < 4; ++pr) {
+                        const uint32_t h2 = pack_bf16x2(pre[j8 * 8 + pr * 2], pre[j8 * 8 + pr * 2 + 1]);
+                        uint32_t gg, dd;
                         if (SILU) {     // h = x / 2, th = tanh(h), sg = sigmoid(x) = (1 + th)/2:  SiLU = h + h*th,  SiLU' = sg + SiLU*(1 - sg)
-                            const float th = tanh_approx(hh);
-                            g[v] = fmaf(hh, th, hh);
-                            dsl[v] = fmaf(g[v], fmaf(-0.5f, th, 0.5f), fmaf(0.5f, th, 0.5f));
+                            const uint32_t th = tanh_bf16x2(h2);
+                            gg = fma_bf16x2(h2, th, h2);
+                            dd = fma_bf16x2(gg, fma_bf16x2(0xBF00BF00u, th, 0x3F003F00u), fma_bf16x2(0x3F003F00u, th, 0x3F003F00u));
                         } else {
-                            g[v] = hh;
-                            dsl[v] = 1.0f;
+                            gg = h2;
+                            dd = 0x3F803F80u;
                         }
-                        sp[v] = fmaf(g[v] * qv[v], ee1[v], sp[v]);
-                        dpp[v] = fmaf(g[v] * dv[v], ee2[v], dpp[v]);
+                        g2[w0 + pr] = gg;
+                        dsl2[w0 + pr] = dd;
+                        sacc = fma_bf16x2(gg, mul_bf16x2(q2[w0 + pr], ekw[pr]), sacc);
+                        dacc = fma_bf16x2(gg, mul_bf16x2(do2[w0 + pr], evw[pr]), dacc);
                     }
-                    g2[j / 2] = pack_bf16x2(g[0], g[1]);
-                    dsl2[j / 2] = pack_bf16x2(dsl[0], dsl[1]);
+                    sp[0] += bf16_lo(sacc);
+                    sp[1] += bf16_hi(sacc);
+                    dpp[0] += bf16_lo(dacc);
+                    dpp[1] += bf16_hi(dacc);
                 }
             }
             const float s = sp[0] + sp[1];
@@ -482,7 +480,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                     const uint4 ekp = *reinterpret_cast<const uint4*>(ek2 + w0);
                     const uint4 evp = *reinterpret_cast<const uint4*>(ev2 + w0);
                     const uint32_t ekw[4] = {ekp.x, ekp.y, ekp.z, ekp.w}, evw[4] = {evp.x, evp.y, evp.z, evp.w};
-                    uint32_t zp[4], zk[4], zv[4];
+                    uint32_t zp[4], zk[4], zv[4], ge[4];
 #pragma unroll
                     for (int pr = 0; pr < 4; ++pr) {
                         const uint32_t gg = g2[w0 + pr];
@@ -491,22 +489,18 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                         zk[pr] = mul_bf16x2(aq, gg);                                      // ds * q * g
                         zv[pr] = mul_bf16x2(bd, gg);                                      // p * dO * g
                         zp[pr] = mul_bf16x2(fma_bf16x2(bd, evw[pr], mul_bf16x2(aq, ekw[pr])), dsl2[w0 + pr]);   // dgate * SiLU'
+                        ge[pr] = mul_bf16x2(gg, ekw[pr]);                                 // K = g * E_k, for dQ
                     }
                     const int chunk = ((c * 2 + j8) ^ (row & 7)) << 4;
                     st_shared_v4(zrow + 0 * HPC * ATOM_BYTES + chunk, zp[0], zp[1], zp[2], zp[3]);
                     st_shared_v4(zrow + 1 * HPC * ATOM_BYTES + chunk, zk[0], zk[1], zk[2], zk[3]);
                     st_shared_v4(zrow + 2 * HPC * ATOM_BYTES + chunk, zv[0], zv[1], zv[2], zv[3]);
-                }
-                tmem_wait_ld();
+                    if (j8 == 0) tmem_wait_ld();
 #pragma unroll
-                for (int jj = 0; jj < 16; jj += 4) {
-                    const int j = c * 16 + jj;
-                    const float4 e1 = *reinterpret_cast<const float4*>(ek + j);
-                    const uint32_t ga = g2[j / 2], gb = g2[j / 2 + 1];
-                    dq[jj] = fmaf(dsq, e1.x * bf16_lo(ga), dq[jj]);
-                    dq[jj + 1] = fmaf(dsq, e1.y * bf16_hi(ga), dq[jj + 1]);
-                    dq[jj + 2] = fmaf(dsq, e1.z * bf16_lo(gb), dq[jj + 2]);
-                    dq[jj + 3] = fmaf(dsq, e1.w * bf16_hi(gb), dq[jj + 3]);
+                    for (int pr = 0; pr < 4; ++pr) {
+                        dq[j8 * 8 + pr * 2] = fmaf(dsq, bf16_lo(ge[pr]), dq[j8 * 8 + pr * 2]);
+                        dq[j8 * 8 + pr * 2 + 1] = fmaf(dsq, bf16_hi(ge[pr]), dq[j8 * 8 + pr * 2 + 1]);
+                    }
                 }
                 tmem_st_32x32b_x16(t_dq + c * 16, dq);
             }

@@ -213,6 +213,12 @@ __device__ __forceinline__ uint32_t fma_bf16x2(uint32_t a, uint32_t b, uint32_t 
     return d;
 }
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
+// tanh of both bf16 halves (one MUFU operation for the pair)
+__device__ __forceinline__ uint32_t tanh_bf16x2(uint32_t a) {
+    uint32_t d;
+    asm("tanh.approx.bf16x2 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
