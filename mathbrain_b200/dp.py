@@ -23,10 +23,12 @@ def slot_embedding_grad(dE_list, unique_tensor, vocab, out=None):
         out = torch.zeros(vocab, D, dtype=torch.float32, device=dE_list[0].device)
     else:
         out.zero_()
-    valid = (unique_tensor >= 0).unsqueeze(-1)
-    idx = unique_tensor.clamp_min(0).reshape(-1)
-    for g in dE_list:
-        out.index_add_(0, idx, (g.float() * valid).reshape(-1, D))
+    # every tensor scatters through the same index: sum them first (fp32), then one masked scatter-add
+    acc = dE_list[0].to(torch.float32, copy=True)
+    for g in dE_list[1:]:
+        acc = acc.add_(g)
+    acc.mul_((unique_tensor >= 0).unsqueeze(-1))
+    out.index_add_(0, unique_tensor.clamp_min(0).reshape(-1), acc.reshape(-1, D))
     return out
 
 
