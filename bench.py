@@ -188,11 +188,15 @@ def profile_case(args):
     the attention forward (and backward) of ONE layer.  Prints per-launch device times; no benchmark line."""
     import mathbrain_b200 as mb
     from mathbrain_b200 import synth
-    c = CFG
+    c = dict(CFG)
     dev = torch.device("cuda", 0)
     B = 16
+    long_case = args.profile_case == "long"      # the long-chunk stress shape: T=4096, B=8, N=128, bursty tokens
+    if long_case:
+        B = 8
+        c.update(T=4096, N=128)
     host = synth.make_chunk_batch(1000, B, c["T"], c["N"], vocab=c["V"], max_prefix=c["max_prefix"],
-                                  min_fill=c["min_fill"], min_hl=c["min_hl"], max_hl=c["max_hl"])
+                                  min_fill=c["min_fill"], min_hl=c["min_hl"], max_hl=c["max_hl"], bursty=long_case)
     K = host["K_max"]
     w = synth.make_layer_weights(1, B, K, c["D"], c["N"], c["T"], c["H"], dtype=torch.bfloat16)
     x = host["x"].to(dev)
@@ -210,7 +214,7 @@ def profile_case(args):
         tel.enabled = True
         for _ in range(3):
             O = mb.FlashEMAFunction.apply(Q, x, Ek, Ev, W, rhos, c["V"], unique, K, handle, True)
-            if args.profile_case == "bwd":
+            if args.profile_case in ("bwd", "long"):
                 O.backward(w["dO"].to(dev).float())
         torch.cuda.synchronize()
     slot_steps = float(host["pad_mask"].sum(1).double().sum() * c["T"])
@@ -356,7 +360,7 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--mode", default=os.environ.get("MBEMA_BENCH_MODE", "tc_bf16"), choices=["fp32", "tc_bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd", "decode"],
+    ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd", "long", "decode"],
                     help="run a small one-layer attention workload (for ncu captures) instead of the benchmark")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
