@@ -39,7 +39,7 @@ static constexpr int RING_STAGE_BYTES = 128 * 4 + 2 * ACC_COLS * 4;   // snapsho
 
 struct Smem {
     // offsets (bytes) into the dynamic shared memory block, base aligned to 1024
-    int a_off, b_off, r_off, e_off, ring_off, tok_off, slot_off, key_off, bar_off, total;
+    int a_off, b_off, r_off, e_off, ring_off, ts_off, tok_off, slot_off, key_off, bar_off, total;
 };
 
 __host__ __device__ inline Smem smem_layout(int N, int K) {
@@ -48,9 +48,10 @@ __host__ __device__ inline Smem smem_layout(int N, int K) {
     int o = 0;
     s.a_off = o; o += NSTAGE * NK * ATOM_BYTES;
     s.b_off = o; o += NK * ATOM_BYTES;
-    s.r_off = o; o += TM * (N + 4) * 4;
+    s.r_off = o; o += NK == 1 ? TM * 64 * 2 : TM * (N + 4) * 4;   // decay powers rho_n^r: bf16 [128][64] (N = 64) or fp32
     s.e_off = o; o += NSTAGE * 2 * HPC * HD * 4;
     s.ring_off = o; o += RING * RING_STAGE_BYTES;
+    s.ts_off = o; o += NK == 1 ? TM * 64 * 2 : 0;  // N = 64: restart values (tok_state + 1) of the tile's 128 steps, bf16
     s.tok_off = o; o += TM * 4;
     s.slot_off = o; o += ((K * 2 + 15) / 16) * 16;
     s.key_off = o; o += ((K * 4 + 15) / 16) * 16;
@@ -89,6 +90,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
     float* R_sh = reinterpret_cast<float*>(sm + L.r_off);
     float* E_sh = reinterpret_cast<float*>(sm + L.e_off);
     unsigned char* ring_sh = sm + L.ring_off;
+    __nv_bfloat16* Rb_sh = reinterpret_cast<__nv_bfloat16*>(sm + L.r_off);     // N = 64
+    uint32_t* TS2_sh = reinterpret_cast<uint32_t*>(sm + L.ts_off);             // N = 64: packed bf16 pairs
     int* tok_sh = reinterpret_cast<int*>(sm + L.tok_off);
     unsigned short* slot_sh = reinterpret_cast<unsigned short*>(sm + L.slot_off);
     int* key_sh = reinterpret_cast<int*>(sm + L.key_off);
@@ -155,11 +158,21 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
         }
         for (int i = tid; i < TM * N; i += THREADS) {   // decay powers rho_n^r, r = 0..127
             const int r = i / N, n = i % N;
-            R_sh[r * ldR + n] = exp2f((float)r * log2f(a.rhos[n]));
+            const float pw = exp2f((float)r * log2f(a.rhos[n]));
+            if (NK == 1) Rb_sh[r * N + n] = __float2bfloat16(pw); else R_sh[r * ldR + n] = pw;
         }
         for (int i = tid; i < TM; i += THREADS) {
             const int tt = t0 + i;
             tok_sh[i] = (tt < Lb) ? (int)(a.x[(size_t)b * a.T + tt] & 0x7fffffffLL) : -1;
+        }
+        if (NK == 1) {   // restart values of the tile's 128 steps: read from shared memory by the hot rows
+            for (int i = tid; i < TM * (N / 4); i += THREADS) {
+                const int r = i / (N / 4), c4 = i % (N / 4);
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (t0 + r < a.T) v = __ldg(reinterpret_cast<const float4*>(a.tok_state + ((size_t)b * a.T + t0 + r) * N) + c4);
+                TS2_sh[2 * i] = pack_bf16x2(v.x + 1.0f, v.y + 1.0f);       // "+1": the occurrence itself
+                TS2_sh[2 * i + 1] = pack_bf16x2(v.z + 1.0f, v.w + 1.0f);
+            }
         }
     }
     fence_proxy_async_smem();
@@ -168,6 +181,18 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
     tc_fence_after_sync();
     const uint32_t tmem_base = bars->tmem_base;
     const int n_slots = bars->abort_flag ? 0 : bars->n_slots;
+    // bit 31 of a slot's key: its token occurs among the tile's 128 steps (only those slots have restart rows)
+    for (int pos = tid; pos < n_slots; pos += THREADS) {
+        const int key = key_sh[pos];
+        bool hot = false;
+#pragma unroll 8
+        for (int j = 0; j < TM; j += 4) {
+            const int4 tk = *reinterpret_cast<const int4*>(tok_sh + j);
+            hot |= (tk.x == key) | (tk.y == key) | (tk.z == key) | (tk.w == key);
+        }
+        if (hot) key_sh[pos] = key | (int)0x80000000u;
+    }
+    __syncthreads();
 
     if (!is_epi) {
         // ============================================================ producer warpgroup: one thread per time step
@@ -202,7 +227,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
         uint32_t R2[NK == 1 ? 32 : 1];
         if (NK == 1) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) R2[j] = pack_bf16x2(R_sh[row * ldR + 2 * j], R_sh[row * ldR + 2 * j + 1]);
+            for (int j = 0; j < 32; ++j) R2[j] = *reinterpret_cast<const uint32_t*>(Rb_sh + row * N + 2 * j);
         }
         for (int j = 0; j < PD; ++j) prefetch(j);
         asm volatile("cp.async.wait_group %0;" ::"n"(PD - 1) : "memory");
@@ -213,7 +238,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
             asm volatile("cp.async.wait_group %0;" ::"n"(PD - 1) : "memory");   // this thread's copies for slot i+1 landed
             // stage st (A tile, E rows, accumulators) is free once the epilogue of slot i - NSTAGE has finished
             if (i >= NSTAGE) mbar_wait(&bars->acc_empty[st], (uint32_t)((u - 1) & 1), abort_flag);
-            const int key = key_sh[i];
+            const int keyf = key_sh[i];
+            const int key = keyf & 0x7fffffff;
             const unsigned char* rg = ring_sh + (i % RING) * RING_STAGE_BYTES;
             // E_k / E_v rows of the slot for the head pair, as fp32: thread p converts column p of both
             {
@@ -228,7 +254,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
             }
             // last occurrence of the slot's token strictly before this row, inside the tile
             int s = -1;
-            {
+            if (keyf < 0) {
                 unsigned w[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) w[j] = __ballot_sync(0xffffffffu, tok_sh[32 * j + lane] == key);
@@ -240,26 +266,38 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
             }
             unsigned char* Arow = A_sh + st * NK * ATOM_BYTES + row * 128;
             if (s >= 0) {   // restart from the token's own state at that occurrence (+1 for the occurrence itself)
-                const float* base = a.tok_state + ((size_t)b * a.T + t0 + s) * N;
-                const float* Rrow = R_sh + (row - s) * ldR;
-#pragma unroll 2
-                for (int cc = 0; cc < N / 8; ++cc) {
-                    const int n0 = cc * 8;
-                    const float4 b0 = __ldg(reinterpret_cast<const float4*>(base + n0));
-                    const float4 b1 = __ldg(reinterpret_cast<const float4*>(base + n0 + 4));
-                    float4 r0 = *reinterpret_cast<const float4*>(Rrow + n0);
-                    float4 r1 = *reinterpret_cast<const float4*>(Rrow + n0 + 4);
-                    if (NK == 1) {   // N = 64 multiplies by bf16-rounded powers everywhere (cold rows use packed bf16 pairs;
-                                     // the backward rebuilds the same tiles from a bf16 table)
-                        r0 = make_float4(bf16_round(r0.x), bf16_round(r0.y), bf16_round(r0.z), bf16_round(r0.w));
-                        r1 = make_float4(bf16_round(r1.x), bf16_round(r1.y), bf16_round(r1.z), bf16_round(r1.w));
+                if (NK == 1) {   // bf16 restart value x bf16 power, rounded once more by the packed multiply; the
+                                 // backward rebuilds the same tiles with the same operations
+                    const uint32_t* tsr = TS2_sh + s * (N / 2);
+                    const uint32_t* rr = reinterpret_cast<const uint32_t*>(Rb_sh + (row - s) * N);
+#pragma unroll
+                    for (int cc = 0; cc < 8; ++cc) {
+                        const uint4 tv = *reinterpret_cast<const uint4*>(tsr + 4 * cc);
+                        const uint4 rv = *reinterpret_cast<const uint4*>(rr + 4 * cc);
+                        uint4 pk;
+                        pk.x = mul_bf16x2(tv.x, rv.x);
+                        pk.y = mul_bf16x2(tv.y, rv.y);
+                        pk.z = mul_bf16x2(tv.z, rv.z);
+                        pk.w = mul_bf16x2(tv.w, rv.w);
+                        *reinterpret_cast<uint4*>(Arow + (((cc & 7) ^ (row & 7)) << 4)) = pk;
                     }
-                    uint4 pk;
-                    pk.x = pack_bf16x2(fmaf(b0.x, r0.x, r0.x), fmaf(b0.y, r0.y, r0.y));
-                    pk.y = pack_bf16x2(fmaf(b0.z, r0.z, r0.z), fmaf(b0.w, r0.w, r0.w));
-                    pk.z = pack_bf16x2(fmaf(b1.x, r1.x, r1.x), fmaf(b1.y, r1.y, r1.y));
-                    pk.w = pack_bf16x2(fmaf(b1.z, r1.z, r1.z), fmaf(b1.w, r1.w, r1.w));
-                    *reinterpret_cast<uint4*>(Arow + (cc >> 3) * ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) = pk;
+                } else {
+                    const float* base = a.tok_state + ((size_t)b * a.T + t0 + s) * N;
+                    const float* Rrow = R_sh + (row - s) * ldR;
+#pragma unroll 2
+                    for (int cc = 0; cc < N / 8; ++cc) {
+                        const int n0 = cc * 8;
+                        const float4 b0 = __ldg(reinterpret_cast<const float4*>(base + n0));
+                        const float4 b1 = __ldg(reinterpret_cast<const float4*>(base + n0 + 4));
+                        const float4 r0 = *reinterpret_cast<const float4*>(Rrow + n0);
+                        const float4 r1 = *reinterpret_cast<const float4*>(Rrow + n0 + 4);
+                        uint4 pk;
+                        pk.x = pack_bf16x2(fmaf(b0.x, r0.x, r0.x), fmaf(b0.y, r0.y, r0.y));
+                        pk.y = pack_bf16x2(fmaf(b0.z, r0.z, r0.z), fmaf(b0.w, r0.w, r0.w));
+                        pk.z = pack_bf16x2(fmaf(b1.x, r1.x, r1.x), fmaf(b1.y, r1.y, r1.y));
+                        pk.w = pack_bf16x2(fmaf(b1.z, r1.z, r1.z), fmaf(b1.w, r1.w, r1.w));
+                        *reinterpret_cast<uint4*>(Arow + (cc >> 3) * ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) = pk;
+                    }
                 }
             } else {        // plain decay of the tile-start snapshot: bf16 snapshot (prefetched, broadcast reads) times
                             // this row's decay powers; product rounded to bf16 by the packed multiply

@@ -201,6 +201,18 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
     tc_fence_after_sync();
     const uint32_t tmem_base = bars->tmem_base;
     const int n_slots = bars->abort_flag ? 0 : bars->n_slots;
+    // bit 31 of a slot's key: its token occurs among the tile's 128 steps (only those slots have restart rows)
+    for (int pos = tid; pos < n_slots; pos += THREADS) {
+        const int key = key_sh[pos];
+        bool hot = false;
+#pragma unroll 8
+        for (int j = 0; j < TM; j += 4) {
+            const int4 tk = *reinterpret_cast<const int4*>(tok_sh + j);
+            hot |= (tk.x == key) | (tk.y == key) | (tk.z == key) | (tk.w == key);
+        }
+        if (hot) key_sh[pos] = key | (int)0x80000000u;
+    }
+    __syncthreads();
 
     if (!is_epi) {
         // ============================================================ producer warpgroup
@@ -292,7 +304,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             prefetch(i + PD);
             asm volatile("cp.async.wait_group %0;" ::"n"(PD - 1) : "memory");
             if (i >= NA) mbar_wait(&a_free[sa], (uint32_t)((i / NA - 1) & 1), abort_flag);
-            const int key = key_sh[i];
+            const int keyf = key_sh[i];
+            const int key = keyf & 0x7fffffff;
             const unsigned char* rg = ring_sh + (i % RING) * RING_STAGE_BYTES;
             {
                 float ekv, evv;
@@ -307,7 +320,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                 E2_sh[sa * 2 * ACC_COLS + ACC_COLS + row] = __float2bfloat16(evv);
             }
             int s = -1;
-            {
+            if (keyf < 0) {
                 unsigned w[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) w[j] = __ballot_sync(0xffffffffu, tok_sh[32 * j + lane] == key);
@@ -324,13 +337,21 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                 for (int cc = 0; cc < N / 8; ++cc) {
                     const float4 b0 = __ldg(reinterpret_cast<const float4*>(base + cc * 8));
                     const float4 b1 = __ldg(reinterpret_cast<const float4*>(base + cc * 8 + 4));
-                    float rr[8];
-                    decay8(row - s, cc * 8, rr);
                     uint4 pk;
-                    pk.x = pack_bf16x2(fmaf(b0.x, rr[0], rr[0]), fmaf(b0.y, rr[1], rr[1]));
-                    pk.y = pack_bf16x2(fmaf(b0.z, rr[2], rr[2]), fmaf(b0.w, rr[3], rr[3]));
-                    pk.z = pack_bf16x2(fmaf(b1.x, rr[4], rr[4]), fmaf(b1.y, rr[5], rr[5]));
-                    pk.w = pack_bf16x2(fmaf(b1.z, rr[6], rr[6]), fmaf(b1.w, rr[7], rr[7]));
+                    if (NK == 1) {   // as the forward: bf16 restart value x bf16 power, packed multiply
+                        const uint4 rv = *reinterpret_cast<const uint4*>(Rb_sh + (row - s) * N + cc * 8);
+                        pk.x = mul_bf16x2(pack_bf16x2(b0.x + 1.0f, b0.y + 1.0f), rv.x);
+                        pk.y = mul_bf16x2(pack_bf16x2(b0.z + 1.0f, b0.w + 1.0f), rv.y);
+                        pk.z = mul_bf16x2(pack_bf16x2(b1.x + 1.0f, b1.y + 1.0f), rv.z);
+                        pk.w = mul_bf16x2(pack_bf16x2(b1.z + 1.0f, b1.w + 1.0f), rv.w);
+                    } else {
+                        float rr[8];
+                        decay8(row - s, cc * 8, rr);
+                        pk.x = pack_bf16x2(fmaf(b0.x, rr[0], rr[0]), fmaf(b0.y, rr[1], rr[1]));
+                        pk.y = pack_bf16x2(fmaf(b0.z, rr[2], rr[2]), fmaf(b0.w, rr[3], rr[3]));
+                        pk.z = pack_bf16x2(fmaf(b1.x, rr[4], rr[4]), fmaf(b1.y, rr[5], rr[5]));
+                        pk.w = pack_bf16x2(fmaf(b1.z, rr[6], rr[6]), fmaf(b1.w, rr[7], rr[7]));
+                    }
                     *reinterpret_cast<uint4*>(Arow + (cc >> 3) * ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) = pk;
                 }
             } else {
