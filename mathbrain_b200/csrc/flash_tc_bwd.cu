@@ -226,7 +226,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
         const int s_chunks = N / 8, e_chunks = ACC_COLS * esize / 16;
         const __nv_bfloat16* snap16 = reinterpret_cast<const __nv_bfloat16*>(a.tile_state + (size_t)a.B * a.nT * a.K * N);
         auto prefetch = [&](int j) {
-            if (j < n_slots) {
+            if (j < n_slots && row < s_chunks + 2 * e_chunks) {   // threads without a chunk to copy skip the address arithmetic too
                 const int k = slot_sh[j];
                 unsigned char* dst = ring_sh + (j % RING) * RING_STAGE_BYTES;
                 const unsigned char* srcS = reinterpret_cast<const unsigned char*>(snap16 + (((size_t)b * a.nT + tile) * a.K + k) * N);
