@@ -93,14 +93,20 @@ class ClockSampler:
 class HotPath:
     """Device-resident operands of the 6-layer hot path and the step function."""
 
-    def __init__(self, rank, dev, mode):
+    def __init__(self, rank, dev, mode, world=1):
         import mathbrain_b200 as mb
         from mathbrain_b200 import synth
         self.mb = mb
         self.dev = dev
         c = CFG
-        self.host = synth.make_chunk_batch(1000 + rank, c["B"], c["T"], c["N"], vocab=c["V"], max_prefix=c["max_prefix"],
+        # every rank draws the same global batch and keeps the shard a cost-balanced packing (cost = listed slots,
+        # all T steps are computed) assigns to it, so the slowest rank stays close to the mean
+        self.host = synth.make_chunk_batch(1000, c["B"] * world, c["T"], c["N"], vocab=c["V"], max_prefix=c["max_prefix"],
                                            min_fill=c["min_fill"], min_hl=c["min_hl"], max_hl=c["max_hl"])
+        if world > 1:
+            from mathbrain_b200 import dp
+            shards = dp.balanced_shards(self.host["pad_mask"].sum(1).tolist(), world)
+            self.host = synth.select_samples(self.host, shards[rank])
         self.K = self.host["K_max"]
         self.pinned = {k: self.host[k].pin_memory() for k in ("x", "unique_slots", "pad_mask", "c_base", "fill")}
         self.h2d_bytes = sum(t.numel() * t.element_size() for t in self.pinned.values())
@@ -392,7 +398,7 @@ def main():
         def barrier():
             return None
 
-    hp = HotPath(rank, dev, args.mode)
+    hp = HotPath(rank, dev, args.mode, world)
     hp.dist = dist_on
     tel = mb.ops.telemetry
 

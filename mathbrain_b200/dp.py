@@ -15,6 +15,27 @@ def shard_bounds(n_items, rank, world):
     return lo, lo + base + (1 if rank < rem else 0)
 
 
+def balanced_shards(costs, world):
+    """Split items with the given costs into `world` shards of equal size (len(costs) must divide evenly) whose
+    total costs are as even as a greedy longest-first packing makes them: items sorted by cost, each handed to the
+    least-loaded shard that still has room.  Deterministic; returns a list of `world` sorted index lists.
+
+    On this path a sample costs T_b * K_b (time steps times listed slots), and a step ends when the slowest rank
+    does, so the maximum shard cost is what the packing minimises."""
+    costs = [float(c) for c in costs]
+    n = len(costs)
+    if world < 1 or n % world != 0:
+        raise ValueError("balanced_shards: %d items do not split evenly over %d ranks" % (n, world))
+    per = n // world
+    load = [0.0] * world
+    out = [[] for _ in range(world)]
+    for i in sorted(range(n), key=lambda j: (-costs[j], j)):
+        r = min((r for r in range(world) if len(out[r]) < per), key=lambda r: (load[r], r))
+        out[r].append(i)
+        load[r] += costs[i]
+    return [sorted(o) for o in out]
+
+
 def slot_embedding_grad(dE_list, unique_tensor, vocab, out=None):
     """Scatter-add per-sample slot gradients [B, K, D] (one tensor per layer / per K,V) into a [vocab, D] fp32
     buffer: what the embedding table receives from the listed slots.  Entries of `unique_tensor` < 0 are skipped."""

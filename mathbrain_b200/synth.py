@@ -97,6 +97,19 @@ def make_chunk_batch(seed, B, T, N, vocab=VOCAB, max_prefix=8192, min_fill=64, b
                 fill=torch.tensor(fills, dtype=torch.int32), K_max=K, vocab=vocab)
 
 
+def select_samples(batch, idx):
+    """The sub-batch of `make_chunk_batch` output holding samples `idx`, slot lists trimmed to the subset's longest."""
+    idx = torch.as_tensor(idx, dtype=torch.long)
+    K = max(16, int(batch["pad_mask"][idx].sum(1).max()))
+    out = dict(batch)
+    for k in ("x", "fill"):
+        out[k] = batch[k][idx].contiguous()
+    for k in ("unique_slots", "pad_mask", "c_base"):
+        out[k] = batch[k][idx][:, :K].contiguous()
+    out["K_max"] = K
+    return out
+
+
 def make_layer_weights(seed, B, K, D, N, T, H, std=0.02, dtype=torch.float32):
     """Random operands of one attention layer: Q [B,H,T,hd], E_k/E_v [B,K,D], W_pe [N,D], dO like Q."""
     g = torch.Generator().manual_seed(seed)

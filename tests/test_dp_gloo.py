@@ -57,3 +57,23 @@ def test_slot_embedding_grad_skips_non_slots():
     g = torch.ones(1, 3, 4)
     out = dp.slot_embedding_grad([g], unique, vocab=5)
     assert out[2].tolist() == [2.0] * 4 and float(out.sum()) == 8.0
+
+
+def test_balanced_shards_even_counts_and_lower_peak():
+    import numpy as np
+    from mathbrain_b200 import dp, synth
+    rng = np.random.Generator(np.random.PCG64(3))
+    costs = rng.integers(300, 2600, size=64).tolist()
+    shards = dp.balanced_shards(costs, 8)
+    assert sorted(i for s in shards for i in s) == list(range(64))
+    assert all(len(s) == 8 for s in shards)
+    peak = max(sum(costs[i] for i in s) for s in shards)
+    naive = max(sum(costs[r * 8:(r + 1) * 8]) for r in range(8))
+    mean = sum(costs) / 8
+    assert peak <= naive and peak < 1.02 * mean
+    with pytest.raises(ValueError):
+        dp.balanced_shards(costs[:63], 8)
+    batch = synth.make_chunk_batch(5, 8, 64, 8, vocab=200, max_prefix=100, min_fill=8)
+    sub = synth.select_samples(batch, dp.balanced_shards(batch["pad_mask"].sum(1).tolist(), 2)[1])
+    assert sub["x"].shape[0] == 4 and sub["unique_slots"].shape[1] == sub["K_max"] == max(16, int(sub["pad_mask"].sum(1).max()))
+    assert bool((sub["unique_slots"][~sub["pad_mask"]] == 0).all())
