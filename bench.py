@@ -99,14 +99,15 @@ class HotPath:
         self.mb = mb
         self.dev = dev
         c = CFG
-        # every rank draws the same global batch and keeps the shard a cost-balanced packing (cost = listed slots,
-        # all T steps are computed) assigns to it, so the slowest rank stays close to the mean
-        self.host = synth.make_chunk_batch(1000, c["B"] * world, c["T"], c["N"], vocab=c["V"], max_prefix=c["max_prefix"],
+        # The global batch of the 8-GPU configuration (8 x B samples) is drawn identically on every rank and split into
+        # 8 cost-balanced shards (cost = listed slots; all T steps are computed).  Rank r runs shard r at every N, so
+        # the per-GPU work does not change with N and the slowest rank stays close to the mean.
+        from mathbrain_b200 import dp
+        n_shards = max(8, world)
+        self.host = synth.make_chunk_batch(1000, c["B"] * n_shards, c["T"], c["N"], vocab=c["V"], max_prefix=c["max_prefix"],
                                            min_fill=c["min_fill"], min_hl=c["min_hl"], max_hl=c["max_hl"])
-        if world > 1:
-            from mathbrain_b200 import dp
-            shards = dp.balanced_shards(self.host["pad_mask"].sum(1).tolist(), world)
-            self.host = synth.select_samples(self.host, shards[rank])
+        shards = dp.balanced_shards(self.host["pad_mask"].sum(1).tolist(), n_shards)
+        self.host = synth.select_samples(self.host, shards[rank])
         self.K = self.host["K_max"]
         self.pinned = {k: self.host[k].pin_memory() for k in ("x", "unique_slots", "pad_mask", "c_base", "fill")}
         self.h2d_bytes = sum(t.numel() * t.element_size() for t in self.pinned.values())
