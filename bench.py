@@ -230,6 +230,52 @@ def profile_case(args):
                       "bwd_ms": tel.elapsed_ms("mbema_flash_bwd"), "status": mb.device_status()}))
 
 
+def aux_case(args):
+    """The memory-bound kernels of the path at the bench's own sizes (B=56, T=512, N=64, D=512): query scan,
+    snapshots, query gate forward and backward.  Prints device time and algorithmic GB/s per call; no benchmark line."""
+    import mathbrain_b200 as mb
+    from mathbrain_b200 import synth
+    c = CFG
+    dev = torch.device("cuda", 0)
+    B, T, N, D = c["B"], c["T"], c["N"], c["D"]
+    host = synth.make_chunk_batch(1000, B, T, N, vocab=c["V"], max_prefix=c["max_prefix"], min_fill=c["min_fill"],
+                                  min_hl=c["min_hl"], max_hl=c["max_hl"])
+    K = host["K_max"]
+    x = host["x"].to(dev)
+    unique = host["unique_slots"].to(dev)
+    ut = unique.clone()
+    ut[~host["pad_mask"].to(dev)] = -1
+    rhos, c_base = host["rhos"].to(dev), host["c_base"].to(dev)
+    g = torch.Generator().manual_seed(0)
+    pe = torch.nn.Linear(N, D, bias=False).to(dev)
+    ln = torch.nn.LayerNorm(D).to(dev)
+    x_q = torch.randn(B, T, D, generator=g).to(dev).to(torch.bfloat16).requires_grad_(True)
+    dq = torch.randn(B, T, D, generator=g).to(dev).to(torch.bfloat16)
+    tel = mb.ops.telemetry
+    tel.enabled = True
+    for _ in range(5):
+        C_seq = mb.compute_query_ema_history(x, rhos, c["V"], c_base, unique)
+        mb.precompute_boundaries(x, ut, rhos, 64, c_init=c_base)
+        p_pre = pe(C_seq).to(torch.bfloat16).requires_grad_(True)
+        q_ln = mb.FusedGatingFunction.apply(x_q, p_pre, pe.weight.sum(1), ln.weight, ln.bias, True)
+        q_ln.backward(dq)
+    torch.cuda.synchronize()
+    nT = (T + 127) // 128
+    alg = {   # algorithmic bytes per call
+        "mbema_query_scan": B * T * (8 + N * 4) + B * K * (8 + N * 4),                   # tokens, C_seq out, keys + c_base rows
+        "mbema_tile_states": B * T * 8 + B * K * (8 + N * 4) + B * nT * K * N * 6 + B * T * N * 4,   # + fp32 and bf16 snapshots, tok_state
+        "mbema_qgate_fwd": B * T * D * (2 + 2 + 2),                                      # x_q, p_pre in, Q_ln out (bf16)
+        "mbema_qgate_bwd": B * T * D * (2 + 2 + 2 + 2 + 2),                              # x_q, p_pre, dQ_ln in; dx_q, dp_pre out
+    }
+    out = {"profile_case": "aux", "B": B, "T": T, "K_max": K, "hbm_peak_GBps": peaks()["hbm"]}
+    for name, nbytes in alg.items():
+        ms = sorted(tel.elapsed_ms(name))
+        if ms:
+            med = ms[len(ms) // 2]
+            out[name] = {"ms": med, "algorithmic_MB": nbytes / 1e6, "GBps": nbytes / med / 1e6}
+    print(json.dumps(out))
+
+
 def decode_case(args):
     """Streaming decode (64 sequences, V=50257, N=64, 4096 slots seen per sequence, 6 layers): device time per step
     of [6 x attend, update].  Weights and projected slot embeddings are random; no benchmark line."""
@@ -367,7 +413,7 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--mode", default=os.environ.get("MBEMA_BENCH_MODE", "tc_bf16"), choices=["fp32", "tc_bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd", "long", "decode"],
+    ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd", "long", "aux", "decode"],
                     help="run a small one-layer attention workload (for ncu captures) instead of the benchmark")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
@@ -381,6 +427,9 @@ def main():
 
     import mathbrain_b200 as mb
     mb._lib.load()                      # fails loudly if the CUDA library is missing
+    if args.profile_case == "aux":
+        aux_case(args)
+        return
     if args.profile_case == "decode":
         decode_case(args)
         return
