@@ -158,12 +158,13 @@ k_chain_scan(IndexWs w, const float* __restrict__ rhos, const float* __restrict_
     const int sd = w.seed[(size_t)b * T + j0];
 
     double l2r[4];
-    float u[4];
+    float u[4], rho[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         int n = lane + 32 * i;
         float r = (n < N) ? rhos[n] : 1.0f;
-        l2r[i] = log2((double)r);
+        rho[i] = r;
+        l2r[i] = (32 * i < N) ? log2((double)r) : 0.0;
         u[i] = 0.0f;
         if (sd != NO_SEED && n < N && c_init != nullptr) {
             u[i] = c_init[((size_t)b * K + sd) * N + n];
@@ -181,13 +182,19 @@ k_chain_scan(IndexWs w, const float* __restrict__ rhos, const float* __restrict_
             if (has && d != last_doc) keep = false;
             last_doc = d;
         }
-        const double dt = (double)(t - s_ref);
+        const int di = t - s_ref;
+        const double dt = (double)di;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            int n = lane + 32 * i;
-            float cval = keep ? u[i] * (float)exp2(dt * l2r[i]) : 0.0f;
-            if (n < N) out[((size_t)b * T + t) * N + n] = cval;
-            u[i] = cval + 1.0f;
+            if (32 * i < N) {   // channel groups beyond N do nothing
+                int n = lane + 32 * i;
+                // one step since the last occurrence (runs of a repeated token, e.g. the padding): the decay is rho
+                // itself; longer gaps take the power in double precision (its error is amplified by 1 / (1 - rho))
+                const float pw = (di == 1) ? rho[i] : (float)exp2(dt * l2r[i]);
+                float cval = keep ? u[i] * pw : 0.0f;
+                if (n < N) out[((size_t)b * T + t) * N + n] = cval;
+                u[i] = cval + 1.0f;
+            }
         }
         s_ref = t;
         has = true;
@@ -201,6 +208,10 @@ __global__ void __launch_bounds__(CHAIN_WARPS * 32)
 k_tile_states(IndexWs w, const int64_t* __restrict__ unique, const float* __restrict__ rhos,
               const float* __restrict__ c_base, float* __restrict__ tile_state, int T, int N, int K, int nT,
               int extra_decay) {
+    extern __shared__ float pw_sh[];            // [nT][N]: rho_n^(tile * 128), evaluated in double precision
+    for (int i = threadIdx.x; i < nT * N; i += blockDim.x)
+        pw_sh[i] = (float)exp2((double)((i / N) * MBEMA_TILE_T) * log2((double)rhos[i % N]));
+    __syncthreads();
     const int b = blockIdx.y;
     const int k = blockIdx.x * CHAIN_WARPS + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -233,7 +244,7 @@ k_tile_states(IndexWs w, const int64_t* __restrict__ unique, const float* __rest
     for (int i = 0; i < 4; ++i) {
         int n = lane + 32 * i;
         float rr = (n < N) ? rhos[n] : 1.0f;
-        l2r[i] = log2((double)rr);
+        l2r[i] = (32 * i < N) ? log2((double)rr) : 0.0;
         u[i] = 0.0f;
         if (c_base != nullptr && n < N) {
             u[i] = c_base[((size_t)b * K + k) * N + n];
@@ -247,7 +258,8 @@ k_tile_states(IndexWs w, const int64_t* __restrict__ unique, const float* __rest
             const int s = s_pos[j];
             const double dt = (double)(s - s_ref);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) u[i] = u[i] * (float)exp2(dt * l2r[i]) + 1.0f;
+            for (int i = 0; i < 4; ++i)
+                if (32 * i < N) u[i] = u[i] * (float)exp2(dt * l2r[i]) + 1.0f;
             s_ref = s;
             ++j;
         }
@@ -255,8 +267,10 @@ k_tile_states(IndexWs w, const int64_t* __restrict__ unique, const float* __rest
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             int n = lane + 32 * i;
-            if (n < N) {
-                const float v = u[i] * (float)exp2(dt * l2r[i]);
+            if (32 * i < N && n < N) {
+                // no occurrence yet: the power rho^t0 is the same for every slot of the CTA (table in shared memory)
+                const float pw = (s_ref == 0) ? pw_sh[tile * N + n] : (float)exp2(dt * l2r[i]);
+                const float v = u[i] * pw;
                 out[(size_t)tile * K * N + n] = v;
                 out16[(size_t)tile * K * N + n] = __float2bfloat16(v);
             }
@@ -349,7 +363,7 @@ extern "C" int mbema_tile_states(const int64_t* x, const int64_t* unique, const 
     if (rc) return rc;
     const int nT = (int)((T + MBEMA_TILE_T - 1) / MBEMA_TILE_T);
     dim3 g2((unsigned)((K + CHAIN_WARPS - 1) / CHAIN_WARPS), (unsigned)B);
-    k_tile_states<<<g2, CHAIN_WARPS * 32, 0, st>>>(w, unique, rhos, c_base, tile_state, (int)T, (int)N, (int)K, nT, extra);
+    k_tile_states<<<g2, CHAIN_WARPS * 32, (size_t)nT * N * sizeof(float), st>>>(w, unique, rhos, c_base, tile_state, (int)T, (int)N, (int)K, nT, extra);
     rc = check_launch();
     if (rc) return rc;
     k_slot_order<<<(unsigned)((B + 127) / 128), 128, 0, st>>>(w.n_valid, kcount, (int)B);

@@ -23,7 +23,7 @@ struct QGateFwdArgs {
 };
 
 template <int NV>
-__global__ void __launch_bounds__(QG_WARPS * 32) k_qgate_fwd(QGateFwdArgs a) {
+__global__ void __launch_bounds__(QG_WARPS * 32, NV <= 4 ? 4 : 2) k_qgate_fwd(QGateFwdArgs a) {
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     constexpr int nv = NV;
@@ -92,7 +92,7 @@ struct QGateBwdArgs {
 
 // dynamic smem: float red[QG_WARPS][3][D]
 template <int NV>
-__global__ void __launch_bounds__(QG_WARPS * 32) k_qgate_bwd(QGateBwdArgs a) {
+__global__ void __launch_bounds__(QG_WARPS * 32, NV <= 4 ? 2 : 1) k_qgate_bwd(QGateBwdArgs a) {
     extern __shared__ float red[];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -188,19 +188,40 @@ __global__ void __launch_bounds__(QG_WARPS * 32) k_qgate_bwd(QGateBwdArgs a) {
     }
 }
 
-// out[j][d] = sum_c part[c][j][d]
-__global__ void k_qgate_colsum(const float* __restrict__ part, int nparts, int D, float* dbias, float* dln_w, float* dln_b) {
-    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= 3 * D) return;
+// out[j][d] = sum_c part[c][j][d]: a CTA owns 32 columns, its 8 warps split the partials, fixed order -> deterministic
+__global__ void __launch_bounds__(256) k_qgate_colsum(const float* __restrict__ part, int nparts, int D, float* dbias, float* dln_w, float* dln_b) {
+    __shared__ float red[8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int idx = blockIdx.x * 32 + lane;
     float s = 0.f;
-    for (int c = 0; c < nparts; ++c) s += part[(size_t)c * 3 * D + idx];
-    const int j = idx / D, d = idx % D;
-    (j == 0 ? dbias : (j == 1 ? dln_w : dln_b))[d] = s;
+    if (idx < 3 * D)
+        for (int c = warp; c < nparts; c += 8) s += part[(size_t)c * 3 * D + idx];
+    red[warp][lane] = s;
+    __syncthreads();
+    if (warp == 0 && idx < 3 * D) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += red[w][lane];
+        const int j = idx / D, d = idx % D;
+        (j == 0 ? dbias : (j == 1 ? dln_w : dln_b))[d] = t;
+    }
 }
 
-static int qgate_grid(int64_t rows) {
-    int64_t ctas = (rows + QG_WARPS - 1) / QG_WARPS;
-    const int64_t cap = 148 * 4;  // 4 resident CTAs per SM on a 148-SM part
+static int sm_count() {
+    int dev = 0, n = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n > 0 ? n : 148;
+}
+
+// One wave of resident CTAs: SM count x the kernel's occupancy (a grid-stride loop covers the rows); a larger grid
+// would run a partial second wave.  `per_sm_cap` bounds the workspace of the backward.
+static constexpr int QG_MAX_CTAS_PER_SM = 8;
+template <typename K>
+static int qgate_grid(int64_t rows, K kernel, size_t smem) {
+    int occ = 1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, QG_WARPS * 32, smem) != cudaSuccess || occ < 1) occ = 1;
+    if (occ > QG_MAX_CTAS_PER_SM) occ = QG_MAX_CTAS_PER_SM;
+    const int64_t ctas = (rows + QG_WARPS - 1) / QG_WARPS, cap = (int64_t)sm_count() * occ;
     return (int)(ctas < cap ? (ctas < 1 ? 1 : ctas) : cap);
 }
 
@@ -228,17 +249,17 @@ extern "C" int mbema_qgate_fwd(const void* x_q, int x_dtype, const void* p_pre, 
         return MBEMA_ERR_ALIGN;
     QGateFwdArgs a{x_q, x_dtype, p_pre, p_dtype, bias, ln_w, ln_b, eps, Y, y_dtype, mu, rstd, rows, (int)D,
                    (flags & MBEMA_FLAG_SILU) ? 1 : 0};
-    const int g = qgate_grid(rows);
     cudaStream_t st = (cudaStream_t)stream;
-    if (D <= 128) k_qgate_fwd<1><<<g, QG_WARPS * 32, 0, st>>>(a);
-    else if (D <= 256) k_qgate_fwd<2><<<g, QG_WARPS * 32, 0, st>>>(a);
-    else if (D <= 512) k_qgate_fwd<4><<<g, QG_WARPS * 32, 0, st>>>(a);
-    else k_qgate_fwd<8><<<g, QG_WARPS * 32, 0, st>>>(a);
+    if (D <= 128) k_qgate_fwd<1><<<qgate_grid(rows, k_qgate_fwd<1>, 0), QG_WARPS * 32, 0, st>>>(a);
+    else if (D <= 256) k_qgate_fwd<2><<<qgate_grid(rows, k_qgate_fwd<2>, 0), QG_WARPS * 32, 0, st>>>(a);
+    else if (D <= 512) k_qgate_fwd<4><<<qgate_grid(rows, k_qgate_fwd<4>, 0), QG_WARPS * 32, 0, st>>>(a);
+    else k_qgate_fwd<8><<<qgate_grid(rows, k_qgate_fwd<8>, 0), QG_WARPS * 32, 0, st>>>(a);
     return check_launch();
 }
 
 extern "C" size_t mbema_qgate_bwd_workspace_bytes(int64_t rows, int64_t D) {
-    return (size_t)qgate_grid(rows) * 3 * (size_t)D * sizeof(float) + 256;
+    const int64_t ctas = (rows + QG_WARPS - 1) / QG_WARPS, cap = (int64_t)sm_count() * QG_MAX_CTAS_PER_SM;
+    return (size_t)(ctas < cap ? (ctas < 1 ? 1 : ctas) : cap) * 3 * (size_t)D * sizeof(float) + 256;
 }
 
 extern "C" int mbema_qgate_bwd(const void* dY, int dy_dtype, const void* x_q, int x_dtype, const void* p_pre,
@@ -262,13 +283,14 @@ extern "C" int mbema_qgate_bwd(const void* dY, int dy_dtype, const void* x_q, in
         return MBEMA_ERR_ALIGN;
     if (workspace_bytes < mbema_qgate_bwd_workspace_bytes(rows, D)) return MBEMA_ERR_WORKSPACE;
     float* part = (float*)(((uintptr_t)workspace + 255) / 256 * 256);
-    const int grid = qgate_grid(rows);
+    int grid = 1;
     QGateBwdArgs a{dY, dy_dtype, x_q, x_dtype, p_pre, p_dtype, bias, ln_w, mu, rstd, dx_q, dp_pre, part, rows, (int)D,
                    (flags & MBEMA_FLAG_SILU) ? 1 : 0};
     const size_t smem = (size_t)QG_WARPS * 3 * D * sizeof(float);
 #define MBEMA_QG_BWD(NV_)                                                                                        \
     do {                                                                                                         \
         MBEMA_CUDA_TRY(cudaFuncSetAttribute(k_qgate_bwd<NV_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        grid = qgate_grid(rows, k_qgate_bwd<NV_>, smem);                                                         \
         k_qgate_bwd<NV_><<<grid, QG_WARPS * 32, smem, st>>>(a);                                                  \
     } while (0)
     if (D <= 128) MBEMA_QG_BWD(1);
@@ -278,6 +300,6 @@ extern "C" int mbema_qgate_bwd(const void* dY, int dy_dtype, const void* x_q, in
 #undef MBEMA_QG_BWD
     rc = check_launch();
     if (rc) return rc;
-    k_qgate_colsum<<<(unsigned)((3 * D + 255) / 256), 256, 0, st>>>(part, grid, (int)D, dbias, dln_w, dln_b);
+    k_qgate_colsum<<<(unsigned)((3 * D + 31) / 32), 256, 0, st>>>(part, grid, (int)D, dbias, dln_w, dln_b);
     return check_launch();
 }
