@@ -60,7 +60,8 @@ def test_config2_full_size_layer(mb):
     # dW_pe at this size: 1.0-1.4 % norm-wise, 2-4.5 % in the max norm (seed dependent).  Slot states reach ~600 after
     # an 8192-token prefix, and the bf16 rounding of the gate product's operands (state tile and W_pe) then moves the
     # pre-activations by ~0.1; rounding those two operands alone in the fp32 backward reproduces the error, rounding
-    # the operands of the dW_pe product itself gives 0.2 %.  Exact gradients: set_options(fp32_backward=True).
+    # the operands of the dW_pe product itself gives 0.2 %.  The reference's Triton kernels round the same operands to
+    # bf16 (mathbrain/triton_flash_ema.py:188-190, 314-315).  Exact gradients: set_options(fp32_backward=True).
     assert rel_err(tc["dW_pe"], ref["dW_pe"]) < 6e-2
     # listed slots beyond a sample's count receive no gradient
     pad = ~batch["pad_mask"]
