@@ -109,7 +109,8 @@ int mbema_query_scan_static(const int64_t* x, const float* rhos, const float* c_
  * Replaces precompute_boundaries (mathbrain/triton_flash_ema.py:81-113; kernel :29-78).
  *   unique [B,K] i64 (-1 = not a slot)   c_base [B,K,N] f32 or NULL (zeros)
  *   out: tile_state [B, nT, K, N] f32 with nT = ceil(T / MBEMA_TILE_T), immediately followed in the same buffer
- *                   by the same values as bf16 [B, nT, K, N] (6 bytes per element in total)
+ *                   by the same values in 16 bits [B, nT, K, N] (6 bytes per element in total): fp16 of
+ *                   state / 64 when N == 64 (operand of the fp16 gate product), bf16 otherwise
  *        tok_state  [B, T, N]     f32  state of x[b,t]'s own slot just before step t (0 if unlisted)
  *        kcount     [2B]          i32  [0,B): number of valid (>= 0) entries of unique[b,:];
  *                                       [B,2B): sample indices by decreasing count (launch order of the attention CTAs)

@@ -10,6 +10,7 @@
 // ahead into shared-memory rings, so no thread holds a gathered row in registers while it is in flight; the state
 // tile of tile i+1 is converted and its UMMA issued before the epilogue of tile i.
 #include "common.cuh"
+#include <cuda_fp16.h>
 #include "sm100_ptx.cuh"
 
 #include <algorithm>
@@ -154,10 +155,11 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int g = tid + THREADS * j, n = g >> 5, dd4 = (g & 31) * 4;
-            *reinterpret_cast<__nv_bfloat16*>(B_sh + sw128_off(dd4 + 0, n)) = __float2bfloat16(wv[j].x * wscale);
-            *reinterpret_cast<__nv_bfloat16*>(B_sh + sw128_off(dd4 + 1, n)) = __float2bfloat16(wv[j].y * wscale);
-            *reinterpret_cast<__nv_bfloat16*>(B_sh + sw128_off(dd4 + 2, n)) = __float2bfloat16(wv[j].z * wscale);
-            *reinterpret_cast<__nv_bfloat16*>(B_sh + sw128_off(dd4 + 3, n)) = __float2bfloat16(wv[j].w * wscale);
+            // fp16 operands for the gate product (11 significant bits): state / 64 in the A tile, W * 64 here
+            *reinterpret_cast<__half*>(B_sh + sw128_off(dd4 + 0, n)) = __float2half_rn(wv[j].x * wscale * STATE_F16_UNSCALE);
+            *reinterpret_cast<__half*>(B_sh + sw128_off(dd4 + 1, n)) = __float2half_rn(wv[j].y * wscale * STATE_F16_UNSCALE);
+            *reinterpret_cast<__half*>(B_sh + sw128_off(dd4 + 2, n)) = __float2half_rn(wv[j].z * wscale * STATE_F16_UNSCALE);
+            *reinterpret_cast<__half*>(B_sh + sw128_off(dd4 + 3, n)) = __float2half_rn(wv[j].w * wscale * STATE_F16_UNSCALE);
         }
         if (PASS == 2)
             for (int i = tid; i < 1024; i += THREADS) reinterpret_cast<__nv_bfloat16*>(ones_sh)[i] = __float2bfloat16(1.0f);
@@ -177,15 +179,16 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
                 const float4 s0 = *reinterpret_cast<const float4*>(src + ((c0 ^ (row & 15)) << 4));
                 const float4 s1 = *reinterpret_cast<const float4*>(src + (((c0 + 1) ^ (row & 15)) << 4));
                 const float* lr = l2r_sh + 16 * cg + cc * 8;
-                pk.x = pack_bf16x2(s0.x * ex2_approx(dt * lr[0]), s0.y * ex2_approx(dt * lr[1]));
-                pk.y = pack_bf16x2(s0.z * ex2_approx(dt * lr[2]), s0.w * ex2_approx(dt * lr[3]));
-                pk.z = pack_bf16x2(s1.x * ex2_approx(dt * lr[4]), s1.y * ex2_approx(dt * lr[5]));
-                pk.w = pack_bf16x2(s1.z * ex2_approx(dt * lr[6]), s1.w * ex2_approx(dt * lr[7]));
+                // state / 64 (STATE_F16_SCALE) folded into the exponent: 2^(dt log2 rho - 6)
+                pk.x = pack_f16x2(s0.x * ex2_approx(fmaf(dt, lr[0], -6.0f)), s0.y * ex2_approx(fmaf(dt, lr[1], -6.0f)));
+                pk.y = pack_f16x2(s0.z * ex2_approx(fmaf(dt, lr[2], -6.0f)), s0.w * ex2_approx(fmaf(dt, lr[3], -6.0f)));
+                pk.z = pack_f16x2(s1.x * ex2_approx(fmaf(dt, lr[4], -6.0f)), s1.y * ex2_approx(fmaf(dt, lr[5], -6.0f)));
+                pk.w = pack_f16x2(s1.z * ex2_approx(fmaf(dt, lr[6], -6.0f)), s1.w * ex2_approx(fmaf(dt, lr[7], -6.0f)));
             }
             *reinterpret_cast<uint4*>(A_sh + row * 128 + (((2 * cg + cc) ^ (row & 7)) << 4)) = pk;
         }
     };
-    const uint32_t idesc = umma_idesc_bf16(TM, ACC_COLS, 0, 0);
+    const uint32_t idesc = umma_idesc_16(TM, ACC_COLS, 0, 0, 0, 0);      // fp16 state tile, fp16 W
     const uint64_t da = umma_desc_k_sw128(smem_u32(A_sh)), db = umma_desc_k_sw128(smem_u32(B_sh));
     auto issue_gate = [&](uint32_t tmem_base, int i) {
 #pragma unroll

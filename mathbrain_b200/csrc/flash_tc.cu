@@ -14,6 +14,7 @@
 // columns; the per-CTA total, 8*32*216 + 4*32*72, equals the launch allocation 384*168).  Hand-offs go through
 // mbarriers with bounded waits; nothing in here spins without a limit.
 #include "flash.cuh"
+#include <cuda_fp16.h>
 #include "sm100_ptx.cuh"
 
 namespace mbema {
@@ -154,12 +155,14 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
         for (int i = tid; i < N * HPC * HD; i += THREADS) {
             const int n = i / (HPC * HD), dd = i % (HPC * HD);
             const float w = a.W[(size_t)n * D + hp * HPC * HD + dd] * wscale;
-            *reinterpret_cast<__nv_bfloat16*>(B_sh + (n >> 6) * ATOM_BYTES + sw128_off(dd, n & 63)) = __float2bfloat16(w);
+            unsigned char* dstw = B_sh + (n >> 6) * ATOM_BYTES + sw128_off(dd, n & 63);
+            if (NK == 1) *reinterpret_cast<__half*>(dstw) = __float2half_rn(w * STATE_F16_UNSCALE);   // the state operand carries 1/64
+            else *reinterpret_cast<__nv_bfloat16*>(dstw) = __float2bfloat16(w);
         }
         for (int i = tid; i < TM * N; i += THREADS) {   // decay powers rho_n^r, r = 0..127
             const int r = i / N, n = i % N;
             const float pw = exp2f((float)r * log2f(a.rhos[n]));
-            if (NK == 1) Rb_sh[r * N + n] = __float2bfloat16(pw); else R_sh[r * ldR + n] = pw;
+            if (NK == 1) reinterpret_cast<__half*>(Rb_sh)[r * N + n] = __float2half_rn(pw); else R_sh[r * ldR + n] = pw;
         }
         for (int i = tid; i < TM; i += THREADS) {
             const int tt = t0 + i;
@@ -170,8 +173,9 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
                 const int r = i / (N / 4), c4 = i % (N / 4);
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (t0 + r < a.T) v = __ldg(reinterpret_cast<const float4*>(a.tok_state + ((size_t)b * a.T + t0 + r) * N) + c4);
-                TS2_sh[2 * i] = pack_bf16x2(v.x + 1.0f, v.y + 1.0f);       // "+1": the occurrence itself
-                TS2_sh[2 * i + 1] = pack_bf16x2(v.z + 1.0f, v.w + 1.0f);
+                const float sc = STATE_F16_SCALE;                           // "+1": the occurrence itself
+                TS2_sh[2 * i] = pack_f16x2((v.x + 1.0f) * sc, (v.y + 1.0f) * sc);
+                TS2_sh[2 * i + 1] = pack_f16x2((v.z + 1.0f) * sc, (v.w + 1.0f) * sc);
             }
         }
     }
@@ -197,7 +201,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
     if (!is_epi) {
         // ============================================================ producer warpgroup: one thread per time step
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
-        const uint32_t idesc = umma_idesc_bf16(TM, ACC_COLS, 0, 0);
+        const uint32_t idesc = umma_idesc_16(TM, ACC_COLS, 0, 0, NK == 1 ? 0 : 1, NK == 1 ? 0 : 1);   // N = 64: fp16 operands
         const uint32_t a_base = smem_u32(A_sh), b_base = smem_u32(B_sh);
         const int wi = row >> 5, bi = row & 31;
         const int esize = (a.e_dt == MBEMA_F32) ? 4 : 2;
@@ -275,10 +279,10 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
                         const uint4 tv = *reinterpret_cast<const uint4*>(tsr + 4 * cc);
                         const uint4 rv = *reinterpret_cast<const uint4*>(rr + 4 * cc);
                         uint4 pk;
-                        pk.x = mul_bf16x2(tv.x, rv.x);
-                        pk.y = mul_bf16x2(tv.y, rv.y);
-                        pk.z = mul_bf16x2(tv.z, rv.z);
-                        pk.w = mul_bf16x2(tv.w, rv.w);
+                        pk.x = mul_f16x2(tv.x, rv.x);
+                        pk.y = mul_f16x2(tv.y, rv.y);
+                        pk.z = mul_f16x2(tv.z, rv.z);
+                        pk.w = mul_f16x2(tv.w, rv.w);
                         *reinterpret_cast<uint4*>(Arow + (((cc & 7) ^ (row & 7)) << 4)) = pk;
                     }
                 } else {
@@ -306,10 +310,10 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
                     for (int cc = 0; cc < 8; ++cc) {
                         const uint4 sv = *reinterpret_cast<const uint4*>(rg + cc * 16);
                         uint4 pk;
-                        pk.x = mul_bf16x2(sv.x, R2[4 * cc]);
-                        pk.y = mul_bf16x2(sv.y, R2[4 * cc + 1]);
-                        pk.z = mul_bf16x2(sv.z, R2[4 * cc + 2]);
-                        pk.w = mul_bf16x2(sv.w, R2[4 * cc + 3]);
+                        pk.x = mul_f16x2(sv.x, R2[4 * cc]);
+                        pk.y = mul_f16x2(sv.y, R2[4 * cc + 1]);
+                        pk.z = mul_f16x2(sv.z, R2[4 * cc + 2]);
+                        pk.w = mul_f16x2(sv.w, R2[4 * cc + 3]);
                         *reinterpret_cast<uint4*>(Arow + (((cc & 7) ^ (row & 7)) << 4)) = pk;
                     }
                 } else {

@@ -11,6 +11,7 @@
 // step, which is the contraction index).  dQ is accumulated in the thread's own TMEM lane (tcgen05.ld / tcgen05.st),
 // which keeps 64 registers free; q and dO are held as packed bf16 pairs.  Every wait is bounded (see sm100_ptx.cuh).
 #include "flash.cuh"
+#include <cuda_fp16.h>
 #include "sm100_ptx.cuh"
 
 namespace mbema {
@@ -32,7 +33,7 @@ static constexpr int ACC_COLS = HPC * HD;
 //   NK = 2: gate 1 x 128 | dW^T 128 | dE_k 16 | dE_v 16 | ... | dQ 128 at column 384
 template <int NK> struct Cfg {
     static constexpr int N = 64 * NK;
-    static constexpr int NA = NK == 1 ? 3 : 2;         // A-tile / E-row stages in shared memory
+    static constexpr int NA = 2;                       // A-tile / E-row stages in shared memory (32 KB each, see STAGE_BYTES)
     static constexpr int NACC = NK == 1 ? 2 : 1;       // gate accumulator stages in TMEM
     static constexpr int COL_DW = NACC * ACC_COLS;     // dW^T [128 d x N]
     static constexpr int COL_DEK = COL_DW + N;         // dE_k column sums (16 columns, all equal)
@@ -49,10 +50,10 @@ struct Smem {
 };
 
 __host__ __device__ inline Smem smem_layout(int K, int NK) {
-    const int NA = NK == 1 ? 3 : 2;
+    const int NA = 2;
     Smem s;
     int o = 0;
-    s.a_off = o; o += NA * NK * ATOM_BYTES;
+    s.a_off = o; o += NA * 2 * ATOM_BYTES;        // N = 64: fp16 tile (gate product) + bf16 tile (dW product); N = 128: two bf16 atoms
     s.b_off = o; o += NK * ATOM_BYTES;            // W^T for the gate product (K-major over n)
     s.z_off = o; o += 3 * HPC * ATOM_BYTES;       // dpre, ds*q*g, p*dO*g tiles: [kind][head][128 t][64 d] bf16
     s.ones_off = o; o += 2048;                    // 16 x 64 bf16 ones (B operand of the column sums)
@@ -98,7 +99,7 @@ template <bool SILU, int NK>
 __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* status) {
     constexpr int N = Cfg<NK>::N, NA = Cfg<NK>::NA, NACC = Cfg<NK>::NACC;
     constexpr int COL_DW = Cfg<NK>::COL_DW, COL_DEK = Cfg<NK>::COL_DEK, COL_DEV = Cfg<NK>::COL_DEV, COL_DQ = Cfg<NK>::COL_DQ;
-    constexpr int STAGE_BYTES = NK * ATOM_BYTES;
+    constexpr int STAGE_BYTES = 2 * ATOM_BYTES;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const Smem L = smem_layout(a.K, NK);
@@ -175,12 +176,14 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
         for (int i = tid; i < N * ACC_COLS; i += THREADS) {
             const int n = i / ACC_COLS, dd = i % ACC_COLS;
             const float w = a.W[(size_t)n * D + hp * ACC_COLS + dd] * wscale;
-            *reinterpret_cast<__nv_bfloat16*>(B_sh + (n >> 6) * ATOM_BYTES + sw128_off(dd, n & 63)) = __float2bfloat16(w);
+            unsigned char* dstw = B_sh + (n >> 6) * ATOM_BYTES + sw128_off(dd, n & 63);
+            if (NK == 1) *reinterpret_cast<__half*>(dstw) = __float2half_rn(w * STATE_F16_UNSCALE);   // the state operand carries 1/64
+            else *reinterpret_cast<__nv_bfloat16*>(dstw) = __float2bfloat16(w);
         }
         if (NK == 1) {
             for (int i = tid; i < TM * N; i += THREADS) {
                 const int r = i / N, n = i % N;
-                Rb_sh[i] = __float2bfloat16(exp2f((float)r * log2f(a.rhos[n])));
+                reinterpret_cast<__half*>(Rb_sh)[i] = __float2half_rn(exp2f((float)r * log2f(a.rhos[n])));   // fp16 powers, as the forward
             }
         } else {   // rho^r = rho^(16 (r / 16)) * rho^(r % 16): rows 0..7 hold the first factor, rows 8..23 the second
             for (int i = tid; i < 24 * N; i += THREADS) {
@@ -217,8 +220,13 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
     if (!is_epi) {
         // ============================================================ producer warpgroup
         asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
-        const uint32_t idesc_gate = umma_idesc_bf16(TM, ACC_COLS, 0, 0);      // A, B K-major
-        const uint32_t idesc_dw = umma_idesc_bf16(ACC_COLS, N, 1, 1);         // A = dpre (MN-major), B = state tile (MN-major)
+        // N = 64: the gate product takes an fp16 state tile (state / 64) and fp16 W (W * 64): 11 significant bits, where
+        // bf16 operands moved the pre-activations of slots with states in the hundreds by ~0.1.  The dW product needs the
+        // tile in the format of dpre (bf16; its gradients do not fit fp16's range), so the producer stores a bf16 copy
+        // of the tile behind the fp16 one.
+        const int sfmt = NK == 1 ? 0 : 1;
+        const uint32_t idesc_gate = umma_idesc_16(TM, ACC_COLS, 0, 0, sfmt, sfmt);      // A, B K-major
+        const uint32_t idesc_dw = umma_idesc_16(ACC_COLS, N, 1, 1, 1, 1);               // A = dpre (MN-major), B = bf16 state tile (MN-major)
         const uint32_t idesc_de = umma_idesc_bf16(ACC_COLS, 16, 1, 0);        // A = Z tile (MN-major), B = ones (K-major)
         const uint32_t a_base = smem_u32(A_sh), b_base = smem_u32(B_sh), z_base = smem_u32(Z_sh), o_base = smem_u32(ones_sh);
         const int wi = row >> 5, bi = row & 31;
@@ -258,7 +266,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             mbar_wait(&bars->z_full, (uint32_t)(j & 1), abort_flag);
             tc_fence_after_sync();
             if (role == 1) {
-                const uint64_t d_at = d_a0 + (uint64_t)(((j % NA) * STAGE_BYTES) >> 4);
+                const uint64_t d_at = d_a0 + (uint64_t)(((j % NA) * STAGE_BYTES + (NK == 1 ? ATOM_BYTES : 0)) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < TM / 16; ++ks)      // contraction over the 128 time steps, 16 per instruction
                     umma_bf16_ss(tmem_base + COL_DW, d_zp + (uint64_t)(ks * (2048 >> 4)), d_at + (uint64_t)(ks * (2048 >> 4)),
@@ -340,10 +348,13 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                     uint4 pk;
                     if (NK == 1) {   // as the forward: bf16 restart value x bf16 power, packed multiply
                         const uint4 rv = *reinterpret_cast<const uint4*>(Rb_sh + (row - s) * N + cc * 8);
-                        pk.x = mul_bf16x2(pack_bf16x2(b0.x + 1.0f, b0.y + 1.0f), rv.x);
-                        pk.y = mul_bf16x2(pack_bf16x2(b0.z + 1.0f, b0.w + 1.0f), rv.y);
-                        pk.z = mul_bf16x2(pack_bf16x2(b1.x + 1.0f, b1.y + 1.0f), rv.z);
-                        pk.w = mul_bf16x2(pack_bf16x2(b1.z + 1.0f, b1.w + 1.0f), rv.w);
+                        const float sc = STATE_F16_SCALE;
+                        pk.x = mul_f16x2(pack_f16x2((b0.x + 1.0f) * sc, (b0.y + 1.0f) * sc), rv.x);
+                        pk.y = mul_f16x2(pack_f16x2((b0.z + 1.0f) * sc, (b0.w + 1.0f) * sc), rv.y);
+                        pk.z = mul_f16x2(pack_f16x2((b1.x + 1.0f) * sc, (b1.y + 1.0f) * sc), rv.z);
+                        pk.w = mul_f16x2(pack_f16x2((b1.z + 1.0f) * sc, (b1.w + 1.0f) * sc), rv.w);
+                        *reinterpret_cast<uint4*>(Arow + ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) =
+                            make_uint4(f16x2_to_bf16x2(pk.x), f16x2_to_bf16x2(pk.y), f16x2_to_bf16x2(pk.z), f16x2_to_bf16x2(pk.w));
                     } else {
                         float rr[8];
                         decay8(row - s, cc * 8, rr);
@@ -360,10 +371,12 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                     const uint4 sv = *reinterpret_cast<const uint4*>(rg + cc * 16);
                     uint4 pk;
                     if (NK == 1) {
-                        pk.x = mul_bf16x2(sv.x, R2[(4 * cc) & 31]);
-                        pk.y = mul_bf16x2(sv.y, R2[(4 * cc + 1) & 31]);
-                        pk.z = mul_bf16x2(sv.z, R2[(4 * cc + 2) & 31]);
-                        pk.w = mul_bf16x2(sv.w, R2[(4 * cc + 3) & 31]);
+                        pk.x = mul_f16x2(sv.x, R2[(4 * cc) & 31]);
+                        pk.y = mul_f16x2(sv.y, R2[(4 * cc + 1) & 31]);
+                        pk.z = mul_f16x2(sv.z, R2[(4 * cc + 2) & 31]);
+                        pk.w = mul_f16x2(sv.w, R2[(4 * cc + 3) & 31]);
+                        *reinterpret_cast<uint4*>(Arow + ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) =
+                            make_uint4(f16x2_to_bf16x2(pk.x), f16x2_to_bf16x2(pk.y), f16x2_to_bf16x2(pk.z), f16x2_to_bf16x2(pk.w));
                     } else {
                         float rr[8];
                         decay8(row, cc * 8, rr);
@@ -572,7 +585,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                     for (int j = 0; j < 32; ++j) acc[j] = 0.f;
                 }
 #pragma unroll
-                for (int j = 0; j < 32; ++j) part_out[(size_t)(c * 32 + j) * ACC_COLS + row] = acc[j];
+                for (int j = 0; j < 32; ++j) part_out[(size_t)(c * 32 + j) * ACC_COLS + row] = acc[j] * (NK == 1 ? STATE_F16_UNSCALE : 1.0f);
             }
         }
     }

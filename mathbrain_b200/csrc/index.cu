@@ -10,6 +10,7 @@
 // touched (the reference fills [B, V+1, N] floats per call, mathbrain/triton_ema_query.py:141-143).
 #include <math.h>
 
+#include <cuda_fp16.h>
 #include "common.cuh"
 
 namespace mbema {
@@ -220,14 +221,15 @@ k_tile_states(IndexWs w, const int64_t* __restrict__ unique, const float* __rest
     const int32_t* s_tok = w.s_tok + (size_t)b * T;
     const int32_t* s_pos = w.s_pos + (size_t)b * T;
     float* out = tile_state + ((size_t)b * nT * K + k) * N;  // + tile * K * N
-    // the same snapshots in bf16 follow the fp32 block (operand format of the tensor-core attention kernels)
+    // the same snapshots in 16 bits follow the fp32 block (operand format of the tensor-core attention kernels:
+    // fp16 of state / 64 when N == 64, bf16 otherwise)
     __nv_bfloat16* out16 = reinterpret_cast<__nv_bfloat16*>(tile_state + (size_t)gridDim.y * nT * K * N) +
                            ((size_t)b * nT * K + k) * N;
     if (kv < 0) {
         for (int i = 0; i < nT; ++i)
             for (int n = lane; n < N; n += 32) {
                 out[(size_t)i * K * N + n] = 0.0f;
-                out16[(size_t)i * K * N + n] = __float2bfloat16(0.0f);
+                out16[(size_t)i * K * N + n] = __float2bfloat16(0.0f);   // +0 in fp16 as well
             }
         return;
     }
@@ -272,7 +274,11 @@ k_tile_states(IndexWs w, const int64_t* __restrict__ unique, const float* __rest
                 const float pw = (s_ref == 0) ? pw_sh[tile * N + n] : (float)exp2(dt * l2r[i]);
                 const float v = u[i] * pw;
                 out[(size_t)tile * K * N + n] = v;
-                out16[(size_t)tile * K * N + n] = __float2bfloat16(v);
+                if (N == 64) {   // operand format of the N = 64 tensor-core kernels: fp16 of state / 64, saturated
+                    reinterpret_cast<__half*>(out16)[(size_t)tile * K * N + n] = __float2half_rn(fminf(v * (1.0f / 64.0f), 65504.0f));
+                } else {
+                    out16[(size_t)tile * K * N + n] = __float2bfloat16(v);
+                }
             }
         }
     }

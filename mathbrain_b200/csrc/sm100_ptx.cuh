@@ -3,6 +3,7 @@
 // Every wait is bounded: after MBEMA_SPIN_LIMIT polls it gives up, raises the CTA's abort flag and returns,
 // so a protocol error ends the kernel with an error status instead of hanging the GPU.
 #pragma once
+#include <cuda_fp16.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -219,6 +220,38 @@ __device__ __forceinline__ uint32_t tanh_bf16x2(uint32_t a) {
     asm("tanh.approx.bf16x2 %0, %1;" : "=r"(d) : "r"(a));
     return d;
 }
+// ---- fp16 pairs: the state tiles of the N = 64 kernels are fp16 (11 significant bits against bf16's 8), stored
+// scaled by STATE_F16_SCALE so that every reachable state stays below the fp16 maximum
+static constexpr float STATE_F16_SCALE = 1.0f / 64.0f;     // state / 64 <= 65504  <=>  state <= 4.19e6
+static constexpr float STATE_F16_UNSCALE = 64.0f;
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+__device__ __forceinline__ uint32_t mul_f16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+// both fp16 halves converted to bf16 (through fp32, round to nearest)
+__device__ __forceinline__ uint32_t f16x2_to_bf16x2(uint32_t v) {
+    uint32_t d;
+    asm("{\n\t.reg .b16 l, h;\n\t.reg .f32 fl, fh;\n\t"
+        "mov.b32 {l, h}, %1;\n\t"
+        "cvt.f32.f16 fl, l;\n\t"
+        "cvt.f32.f16 fh, h;\n\t"
+        "cvt.rn.bf16x2.f32 %0, fh, fl;\n\t}"
+        : "=r"(d)
+        : "r"(v));
+    return d;
+}
+// Instruction descriptor for kind::f16 with explicit operand formats (0 = fp16, 1 = bf16) and fp32 accumulation.
+__device__ __forceinline__ uint32_t umma_idesc_16(int M, int N, int a_mn_major, int b_mn_major, int a_fmt, int b_fmt) {
+    return (1u << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)a_mn_major << 15) |
+           ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 

@@ -200,7 +200,7 @@ def compute_query_ema_history(x, rhos, vocab_size, c_init=None, c_init_keys=None
 @dataclass
 class TileStates:
     """Opaque result of precompute_boundaries, consumed by FlashEMAFunction."""
-    tile_state: torch.Tensor            # [B, nT, K, N] f32 view of a buffer that also holds a bf16 copy behind it
+    tile_state: torch.Tensor            # [B, nT, K, N] f32 view of a buffer that also holds a 16-bit copy behind it
     tok_state: torch.Tensor             # [B, T, N] f32
     kcount: torch.Tensor                # [2B] i32: valid-slot counts, then the sample order (heaviest first)
     seq_lens: Optional[torch.Tensor]    # [B] i32 or None
@@ -233,7 +233,7 @@ def precompute_boundaries(x, unique_tensor, rhos, Br, c_init=None, doc_ids=None,
             raise _lib.MbemaError("c_init must be [B, K, N] matching unique_tensor [B, K]")
     nT = (L + _lib.TILE_T - 1) // _lib.TILE_T
     n_el = B * nT * K * N
-    tile_buf = torch.empty(n_el * 6 + 16, dtype=torch.uint8, device=x.device)   # fp32 block, then the bf16 copy
+    tile_buf = torch.empty(n_el * 6 + 16, dtype=torch.uint8, device=x.device)   # fp32 block, then the 16-bit copy
     tile_state = tile_buf[: n_el * 4].view(torch.float32).view(B, nT, K, N)
     tok_state = torch.empty(B, L, N, dtype=torch.float32, device=x.device)
     kcount = torch.empty(2 * B, dtype=torch.int32, device=x.device)   # counts, then samples by decreasing count

@@ -51,18 +51,12 @@ def test_config2_full_size_layer(mb):
     w["dO"] = w["dO"] * (steps < batch["fill"].view(-1, 1, 1, 1)).to(w["dO"].dtype)
     tc = _run(mb, batch, w, "tc_bf16")
     ref = _run(mb, batch, w, "fp32")
+    # slot states reach ~600 after an 8192-token prefix: the gate product runs on fp16 operands (11 significant bits);
+    # with bf16 operands dW_pe was off by 2-4.5 % here (the pre-activations moved by ~0.1)
     for k in ref:
         assert torch.isfinite(tc[k]).all(), k
-        fro = float((tc[k] - ref[k]).norm() / ref[k].norm())
-        assert fro < TOL_BF16, (k, fro)
-        if k != "dW_pe":
-            assert rel_err(tc[k], ref[k]) < TOL_BF16, (k, rel_err(tc[k], ref[k]))
-    # dW_pe at this size: 1.0-1.4 % norm-wise, 2-4.5 % in the max norm (seed dependent).  Slot states reach ~600 after
-    # an 8192-token prefix, and the bf16 rounding of the gate product's operands (state tile and W_pe) then moves the
-    # pre-activations by ~0.1; rounding those two operands alone in the fp32 backward reproduces the error, rounding
-    # the operands of the dW_pe product itself gives 0.2 %.  The reference's Triton kernels round the same operands to
-    # bf16 (mathbrain/triton_flash_ema.py:188-190, 314-315).  Exact gradients: set_options(fp32_backward=True).
-    assert rel_err(tc["dW_pe"], ref["dW_pe"]) < 6e-2
+        assert rel_err(tc[k], ref[k]) < TOL_BF16, (k, rel_err(tc[k], ref[k]))
+    assert rel_err(tc["O"], ref["O"]) < 3e-3 and rel_err(tc["dW_pe"], ref["dW_pe"]) < 1e-2
     # listed slots beyond a sample's count receive no gradient
     pad = ~batch["pad_mask"]
     assert float(tc["dE_k"][pad].abs().max()) == 0.0 and float(tc["dE_v"][pad].abs().max()) == 0.0
