@@ -3,7 +3,9 @@
 // One CTA owns (sample b, a 128-step time tile, a pair of heads) and loops over the sample's valid slots.
 // Warp-specialised, 12 warps:
 //   * producer warpgroup (warps 8-11, one thread per time step): for slot k rebuilds the 128 x N state tile
-//     A[t, :] = M_t[k, :] (bf16, 128-byte-swizzled K-major rows) in shared memory from the tile-start snapshot and
+//     A[t, :] = M_t[k, :] (16-bit, 128-byte-swizzled K-major rows: fp16 of state / 64 for N = 64, whose 11
+//     significant bits keep the pre-activations of slots with states in the hundreds accurate, bf16 for N = 128)
+//     in shared memory from the tile-start snapshot and
 //     a table of decay powers, stages the slot's E_k / E_v rows as fp32, and one of its threads issues
 //         pre[128 x 128] = A[128 x N] @ (W_pe[:, 2 heads])        tcgen05.mma, fp32 accumulators in TMEM;
 //   * two epilogue warpgroups (a warpgroup per head, a thread per time step) read their 64 accumulator columns

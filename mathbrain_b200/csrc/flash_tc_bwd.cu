@@ -5,11 +5,14 @@
 //   (1) pre[128 t x 128 d]  = A[t, n] @ W[n, d]                      recompute of the gate pre-activation
 //   (2) dW^T[128 d x N]    += dpre[t, d]^T @ A[t, n]                 accumulated in TMEM over all slots of the CTA
 //   (3) dE_k[d], dE_v[d]    = (ds*q*g)[t, d]^T @ 1,  (p*dO*g)[t, d]^T @ 1     column sums over the tile's time steps
-// The epilogue threads read the accumulators of (1) twice (two passes keep the register footprint at one 32-column
-// chunk): pass 1 forms the score and dO.V, giving p = exp(s - LSE) and ds; pass 2 recomputes the gate and writes the
-// three bf16 operand tiles of (2) and (3) to shared memory (128-byte-swizzled, "MN-major": the tile row is the time
-// step, which is the contraction index).  dQ is accumulated in the thread's own TMEM lane (tcgen05.ld / tcgen05.st),
-// which keeps 64 registers free; q and dO are held as packed bf16 pairs.  Every wait is bounded (see sm100_ptx.cuh).
+// For N = 64 product (1) takes fp16 operands (state / 64, W * 64; see flash_tc.cu) and product (2) bf16 ones, so the
+// producer stores every state tile twice (fp16, and the same values converted to bf16).
+// The epilogue threads read the accumulators of (1) once, in 16-column chunks: pass 1 forms the gate and its
+// derivative (fp32, kept as packed bf16 pairs), the score and dO.V, giving p = exp(s - LSE) and ds; pass 2 builds the
+// three bf16 operand tiles of (2) and (3) in packed bf16 arithmetic and writes them to shared memory
+// (128-byte-swizzled, "MN-major": the tile row is the time step, which is the contraction index).  dQ is
+// accumulated in the thread's own TMEM lane (tcgen05.ld / tcgen05.st), which keeps 64 registers free; q and dO are
+// held as packed bf16 pairs.  Every wait is bounded (see sm100_ptx.cuh).
 #include "flash.cuh"
 #include <cuda_fp16.h>
 #include "sm100_ptx.cuh"

@@ -57,7 +57,7 @@ def test_tc_forward_backward_config1_shape(mb):
 
 
 def test_tc_semantic_switches_and_seq_lens(mb):
-    # operand scale 0.1 (five times the model's init scale); at 0.3 the bf16 operands alone cost 2-3 % (see DESIGN.md)
+    # operand scale 0.1 (five times the model's init scale); at 0.3 the bf16 operands alone cost 2-3 %
     inp, c_base, fill = make_case(41, B=3, T=300, N=64, H=2, vocab=300, max_prefix=100, min_hl=2.0, max_hl=100.0,
                                   min_fill=20, std=0.1)
     inp["dO"] = inp["dO"].clone()
