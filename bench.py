@@ -145,7 +145,7 @@ class HotPath:
         for p in self.params:
             p.grad = None
 
-    def step(self, batch, skip_padding=False):
+    def step(self, batch, skip_padding=False, shared_rows=False):
         mb, c = self.mb, CFG
         B, T, H, D = c["B"], c["T"], c["H"], c["D"]
         x, unique_slots, pad_mask, c_base = batch["x"], batch["unique_slots"], batch["pad_mask"], batch["c_base"]
@@ -164,15 +164,25 @@ class HotPath:
                     Q_t = mb.fused_apply_symmetric_query_gating(lay["x_q"], C_seq, lay["pe"], lay["ln"], lay["qp"], True)
                     Q_mha = Q_t.view(B, T, H, D // H).transpose(1, 2).contiguous()
                     W_pe_t = lay["pe"].weight.t().contiguous()
-                    O = mb.FlashEMAFunction.apply(Q_mha, x, lay["E_k"], lay["E_v"], W_pe_t, self.rhos, c["V"],
-                                                  unique_tensor, self.K, handle, True)
+                    if shared_rows:     # extension: one E row per token listed anywhere in the batch
+                        O = mb.FlashEMARowsFunction.apply(Q_mha, x, lay["E_k_rows"], lay["E_v_rows"], self.row_index,
+                                                          W_pe_t, self.rhos, c["V"], unique_tensor, self.K, handle, True)
+                    else:
+                        O = mb.FlashEMAFunction.apply(Q_mha, x, lay["E_k"], lay["E_v"], W_pe_t, self.rhos, c["V"],
+                                                      unique_tensor, self.K, handle, True)
                 O.backward(lay["dO"])
                 s = O.detach().float().sum()
                 acc = s if acc is None else acc + s
             if self.dist:
                 from mathbrain_b200 import dp
-                grads = [lay[k].grad for lay in self.layers for k in ("E_k", "E_v")]
-                self.dE_vocab = dp.slot_embedding_grad(grads, unique_tensor, c["V"], out=self.dE_vocab)
+                if shared_rows:      # row r belongs to token self.row_tokens[r]
+                    rg = sum(lay[k].grad.float() for lay in self.layers for k in ("E_k_rows", "E_v_rows"))
+                    if self.dE_vocab is None:
+                        self.dE_vocab = torch.zeros(c["V"], D, dtype=torch.float32, device=self.dev)
+                    self.dE_vocab.zero_().index_add_(0, self.row_tokens, rg)
+                else:
+                    grads = [lay[k].grad for lay in self.layers for k in ("E_k", "E_v")]
+                    self.dE_vocab = dp.slot_embedding_grad(grads, unique_tensor, c["V"], out=self.dE_vocab)
                 dp.allreduce_gradients(self.params, extra=[self.dE_vocab])
             self.result.copy_(acc.reshape(1))
 
@@ -181,6 +191,20 @@ class HotPath:
 
     def step_resident_skip(self):
         self.step(self.resident, skip_padding=True)
+
+    def step_resident_rows(self):
+        if not hasattr(self, "row_index"):
+            ut = self.resident["unique_slots"].clone()
+            ut[~self.resident["pad_mask"]] = -1
+            self.row_tokens, self.row_index = self.mb.shared_slot_rows(ut)
+            self.n_rows = int(self.row_tokens.numel())
+            g = torch.Generator().manual_seed(77)
+            for lay in self.layers:
+                for k in ("E_k_rows", "E_v_rows"):
+                    lay[k] = (torch.randn(self.n_rows, CFG["D"], generator=g) * 0.02).to(torch.bfloat16).to(self.dev).requires_grad_(True)
+        for lay in self.layers:
+            lay["E_k_rows"].grad = lay["E_v_rows"].grad = None
+        self.step(self.resident, shared_rows=True)
 
     def step_e2e(self):
         batch = {k: v.to(self.dev, non_blocking=True) for k, v in self.pinned.items()}
@@ -470,6 +494,8 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     # same workload with the padded steps skipped (reported as an extra key, not as the headline)
     secs_skip = timed(hp.step_resident_skip, args.steps, 1, barrier)
+    # same workload with slot-embedding rows shared between the samples of the batch (extension, extra key)
+    secs_rows = timed(hp.step_resident_rows, args.steps, 1, barrier)
     # end-to-end measurement: batch copied from pinned host memory each step, result scalar read back
     secs_e2e = timed(hp.step_e2e, args.steps, 1, barrier)
 
@@ -502,6 +528,9 @@ def main():
             "skip_padding": {"value": tokens * args.steps / secs_skip, "unit": "tokens/s (B*T per step, padded steps skipped)",
                              "ms_per_step": secs_skip / args.steps * 1000.0,
                              "valid_tokens_per_s": float(hp.host["fill"].sum()) * world * args.steps / secs_skip},
+            "shared_rows": {"value": tokens * args.steps / secs_rows, "unit": "tokens/s (E_k/E_v rows shared between samples)",
+                            "ms_per_step": secs_rows / args.steps * 1000.0, "rows": hp.n_rows,
+                            "per_sample_rows": c["B"] * hp.K},
             "clocks": clocks,
             "e2e": {"value": tokens * args.steps / secs_e2e, "unit": "tokens/s", "h2d_bytes_per_step": hp.h2d_bytes,
                     "d2h_bytes_per_step": 4},

@@ -172,6 +172,28 @@ int mbema_flash_bwd(const void* Q, int q_dtype, const int64_t* x, const void* E_
                     int64_t V_total, int flags, int mode, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * The same attention with slot-embedding rows SHARED between samples: E_k, E_v are [e_rows, H*hd] tables and
+ * e_row_index [B,K] i32 names the row slot (b, k) reads (for instance one row per token that is listed anywhere in
+ * the batch, so that a token's projection is computed once per layer instead of once per sample); dE_k, dE_v are
+ * [e_rows, H*hd] f32 and receive the sum over all slots that share a row.  Everything else as mbema_flash_fwd / _bwd.
+ * The reference always materialises [B,K,H*hd] (mathbrain/model.py:63-68): this is an extension, the first "next"
+ * step around the path.  Entries of e_row_index at padded slots (unique < 0) are not read.
+ * ---------------------------------------------------------------------------------------------- */
+int mbema_flash_fwd_rows(const void* Q, int q_dtype, const int64_t* x, const void* E_k, const void* E_v, int e_dtype,
+                         const int32_t* e_row_index, int64_t e_rows, const float* W_pe, const float* rhos,
+                         const int64_t* unique, const float* tile_state, const float* tok_state,
+                         const int32_t* kcount, const int32_t* seq_lens, float* O, float* LSE, int64_t B, int64_t H,
+                         int64_t T, int64_t hd, int64_t N, int64_t K, int64_t V_total, int flags, int mode,
+                         void* workspace, size_t workspace_bytes, void* stream);
+int mbema_flash_bwd_rows(const void* Q, int q_dtype, const int64_t* x, const void* E_k, const void* E_v, int e_dtype,
+                         const int32_t* e_row_index, int64_t e_rows, const float* W_pe, const float* rhos,
+                         const int64_t* unique, const float* tile_state, const float* tok_state,
+                         const int32_t* kcount, const int32_t* seq_lens, const float* O, const float* LSE,
+                         const void* dO, int do_dtype, float* dQ, float* dE_k, float* dE_v, float* dW_pe, int64_t B,
+                         int64_t H, int64_t T, int64_t hd, int64_t N, int64_t K, int64_t V_total, int flags, int mode,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Streaming decode with resident per-sequence slot state.  The reference has no decode loop; one step is one
  * iteration of the loop body of mathbrain/flash_ema_attention.py:46-82 (attention over the slots, then the
  * "+1" of the current token) plus the query-side read of mathbrain/triton_ema_query.py:36-64.

@@ -35,6 +35,11 @@ SIGNATURES = {
     "mbema_flash_bwd_workspace_bytes": (_sz, [_i64] * 6 + [_i32]),
     "mbema_flash_bwd": (_i32, [_vp, _i32, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32,
                                _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _vp, _sz, _vp]),
+    "mbema_flash_fwd_rows": (_i32, [_vp, _i32, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                    _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _vp, _sz, _vp]),
+    "mbema_flash_bwd_rows": (_i32, [_vp, _i32, _vp, _vp, _vp, _i32, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                    _vp, _i32, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32,
+                                    _vp, _sz, _vp]),
     "mbema_decode_attend": (_i32, [_vp, _i32, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                    _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "mbema_decode_attend_tc_workspace_bytes": (_sz, [_i64] * 3),

@@ -13,6 +13,8 @@ struct FlashArgs {
     const float* tile_state; const float* tok_state;
     const int* kcount; const int* seq_lens;
     const int* order;   // [B] sample processed by blockIdx.z (heaviest first), or null
+    const int* erow;    // [B, K] row of E_k / E_v / dE_k / dE_v that slot (b, k) uses, or null: row b * K + k
+    long long e_rows;   // number of rows of E_k / E_v (B * K without erow)
     float* O; float* LSE;
     // backward only
     const void* dO; int do_dt;
@@ -21,6 +23,11 @@ struct FlashArgs {
     float v_total;
     int silu, listed_only;
 };
+
+// row of the slot-embedding tables (and of their gradients) that slot (b, k) reads
+__device__ __forceinline__ size_t e_row(const FlashArgs& a, int b, int k) {
+    return a.erow ? (size_t)a.erow[(size_t)b * a.K + k] : (size_t)b * a.K + k;
+}
 
 int flash_fwd_simt(const FlashArgs& a, cudaStream_t st);
 size_t flash_bwd_simt_ws(int64_t B, int64_t H, int64_t T, int64_t N);

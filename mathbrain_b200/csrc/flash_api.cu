@@ -27,6 +27,8 @@ static FlashArgs pack(const void* Q, int q_dtype, const int64_t* x, const void* 
     a.v_total = (float)V_total;
     a.silu = (flags & MBEMA_FLAG_SILU) ? 1 : 0;
     a.listed_only = (flags & MBEMA_FLAG_LISTED_ONLY) ? 1 : 0;
+    a.erow = nullptr;
+    a.e_rows = (long long)B * K;
     return a;
 }
 
@@ -34,14 +36,15 @@ extern "C" size_t mbema_flash_fwd_workspace_bytes(int64_t, int64_t, int64_t, int
     return 256;
 }
 
-extern "C" int mbema_flash_fwd(const void* Q, int q_dtype, const int64_t* x, const void* E_k, const void* E_v,
-                               int e_dtype, const float* W_pe, const float* rhos, const int64_t* unique,
-                               const float* tile_state, const float* tok_state, const int32_t* kcount,
-                               const int32_t* seq_lens, float* O, float* LSE, int64_t B, int64_t H, int64_t T,
-                               int64_t hd, int64_t N, int64_t K, int64_t V_total, int flags, int mode,
-                               void* workspace, size_t workspace_bytes, void* stream) {
+static int flash_fwd_impl(const void* Q, int q_dtype, const int64_t* x, const void* E_k, const void* E_v,
+                          int e_dtype, const int32_t* e_row_index, int64_t e_rows, const float* W_pe, const float* rhos,
+                          const int64_t* unique, const float* tile_state, const float* tok_state, const int32_t* kcount,
+                          const int32_t* seq_lens, float* O, float* LSE, int64_t B, int64_t H, int64_t T,
+                          int64_t hd, int64_t N, int64_t K, int64_t V_total, int flags, int mode,
+                          void* workspace, size_t workspace_bytes, void* stream) {
     int rc = flash_check(B, H, T, hd, N, K, mode);
     if (rc) return rc;
+    if (e_row_index && e_rows < 1) return MBEMA_ERR_SHAPE;
     if (B == 0) return MBEMA_OK;
     if (!Q || !x || !E_k || !E_v || !W_pe || !rhos || !unique || !tile_state || !tok_state || !kcount || !O || !LSE)
         return MBEMA_ERR_NULL;
@@ -50,12 +53,36 @@ extern "C" int mbema_flash_fwd(const void* Q, int q_dtype, const int64_t* x, con
     FlashArgs a = pack(Q, q_dtype, x, E_k, E_v, e_dtype, W_pe, rhos, unique, tile_state, tok_state, kcount, seq_lens,
                        B, H, T, N, K, V_total, flags);
     a.O = O; a.LSE = LSE;
+    if (e_row_index) { a.erow = e_row_index; a.e_rows = e_rows; }
     if (mode == MBEMA_MODE_TC_BF16) {
         if (!workspace) return MBEMA_ERR_NULL;
         if (workspace_bytes < flash_fwd_tc_ws()) return MBEMA_ERR_WORKSPACE;
         return flash_fwd_tc(a, workspace, (cudaStream_t)stream);
     }
     return flash_fwd_simt(a, (cudaStream_t)stream);
+}
+
+extern "C" int mbema_flash_fwd(const void* Q, int q_dtype, const int64_t* x, const void* E_k, const void* E_v,
+                               int e_dtype, const float* W_pe, const float* rhos, const int64_t* unique,
+                               const float* tile_state, const float* tok_state, const int32_t* kcount,
+                               const int32_t* seq_lens, float* O, float* LSE, int64_t B, int64_t H, int64_t T,
+                               int64_t hd, int64_t N, int64_t K, int64_t V_total, int flags, int mode,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+    return flash_fwd_impl(Q, q_dtype, x, E_k, E_v, e_dtype, nullptr, 0, W_pe, rhos, unique, tile_state, tok_state, kcount,
+                          seq_lens, O, LSE, B, H, T, hd, N, K, V_total, flags, mode, workspace, workspace_bytes, stream);
+}
+
+extern "C" int mbema_flash_fwd_rows(const void* Q, int q_dtype, const int64_t* x, const void* E_k, const void* E_v,
+                                    int e_dtype, const int32_t* e_row_index, int64_t e_rows, const float* W_pe,
+                                    const float* rhos, const int64_t* unique, const float* tile_state,
+                                    const float* tok_state, const int32_t* kcount, const int32_t* seq_lens, float* O,
+                                    float* LSE, int64_t B, int64_t H, int64_t T, int64_t hd, int64_t N, int64_t K,
+                                    int64_t V_total, int flags, int mode, void* workspace, size_t workspace_bytes,
+                                    void* stream) {
+    if (!e_row_index) return MBEMA_ERR_NULL;
+    return flash_fwd_impl(Q, q_dtype, x, E_k, E_v, e_dtype, e_row_index, e_rows, W_pe, rhos, unique, tile_state, tok_state,
+                          kcount, seq_lens, O, LSE, B, H, T, hd, N, K, V_total, flags, mode, workspace, workspace_bytes,
+                          stream);
 }
 
 extern "C" size_t mbema_flash_bwd_workspace_bytes(int64_t B, int64_t H, int64_t T, int64_t hd, int64_t N, int64_t K,
@@ -70,15 +97,16 @@ extern "C" size_t mbema_flash_bwd_workspace_bytes(int64_t B, int64_t H, int64_t 
     return need;
 }
 
-extern "C" int mbema_flash_bwd(const void* Q, int q_dtype, const int64_t* x, const void* E_k, const void* E_v,
-                               int e_dtype, const float* W_pe, const float* rhos, const int64_t* unique,
-                               const float* tile_state, const float* tok_state, const int32_t* kcount,
-                               const int32_t* seq_lens, const float* O, const float* LSE, const void* dO,
-                               int do_dtype, float* dQ, float* dE_k, float* dE_v, float* dW_pe, int64_t B, int64_t H,
-                               int64_t T, int64_t hd, int64_t N, int64_t K, int64_t V_total, int flags, int mode,
-                               void* workspace, size_t workspace_bytes, void* stream) {
+static int flash_bwd_impl(const void* Q, int q_dtype, const int64_t* x, const void* E_k, const void* E_v,
+                          int e_dtype, const int32_t* e_row_index, int64_t e_rows, const float* W_pe, const float* rhos,
+                          const int64_t* unique, const float* tile_state, const float* tok_state, const int32_t* kcount,
+                          const int32_t* seq_lens, const float* O, const float* LSE, const void* dO,
+                          int do_dtype, float* dQ, float* dE_k, float* dE_v, float* dW_pe, int64_t B, int64_t H,
+                          int64_t T, int64_t hd, int64_t N, int64_t K, int64_t V_total, int flags, int mode,
+                          void* workspace, size_t workspace_bytes, void* stream) {
     int rc = flash_check(B, H, T, hd, N, K, mode);
     if (rc) return rc;
+    if (e_row_index && e_rows < 1) return MBEMA_ERR_SHAPE;
     if (!dW_pe) return MBEMA_ERR_NULL;
     cudaStream_t st = (cudaStream_t)stream;
     if (B == 0) {
@@ -96,6 +124,7 @@ extern "C" int mbema_flash_bwd(const void* Q, int q_dtype, const int64_t* x, con
                        B, H, T, N, K, V_total, flags);
     a.O = const_cast<float*>(O); a.LSE = const_cast<float*>(LSE);
     a.dO = dO; a.do_dt = do_dtype; a.dQ = dQ; a.dEk = dE_k; a.dEv = dE_v;
+    if (e_row_index) { a.erow = e_row_index; a.e_rows = e_rows; }
     // tensor-core backward where the shape fits its shared-memory budget (N == 64); otherwise the fp32 kernels
     if (mode == MBEMA_MODE_TC_BF16) {
         if (!(flags & MBEMA_FLAG_FP32_BACKWARD) && flash_bwd_tc_supported((int)H, (int)N, (int)K))
@@ -104,4 +133,30 @@ extern "C" int mbema_flash_bwd(const void* Q, int q_dtype, const int64_t* x, con
         return flash_bwd_simt(a, dW_pe, static_cast<unsigned char*>(workspace) + 512, st);
     }
     return flash_bwd_simt(a, dW_pe, workspace, st);
+}
+
+extern "C" int mbema_flash_bwd(const void* Q, int q_dtype, const int64_t* x, const void* E_k, const void* E_v,
+                               int e_dtype, const float* W_pe, const float* rhos, const int64_t* unique,
+                               const float* tile_state, const float* tok_state, const int32_t* kcount,
+                               const int32_t* seq_lens, const float* O, const float* LSE, const void* dO,
+                               int do_dtype, float* dQ, float* dE_k, float* dE_v, float* dW_pe, int64_t B, int64_t H,
+                               int64_t T, int64_t hd, int64_t N, int64_t K, int64_t V_total, int flags, int mode,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+    return flash_bwd_impl(Q, q_dtype, x, E_k, E_v, e_dtype, nullptr, 0, W_pe, rhos, unique, tile_state, tok_state, kcount,
+                          seq_lens, O, LSE, dO, do_dtype, dQ, dE_k, dE_v, dW_pe, B, H, T, hd, N, K, V_total, flags, mode,
+                          workspace, workspace_bytes, stream);
+}
+
+extern "C" int mbema_flash_bwd_rows(const void* Q, int q_dtype, const int64_t* x, const void* E_k, const void* E_v,
+                                    int e_dtype, const int32_t* e_row_index, int64_t e_rows, const float* W_pe,
+                                    const float* rhos, const int64_t* unique, const float* tile_state,
+                                    const float* tok_state, const int32_t* kcount, const int32_t* seq_lens,
+                                    const float* O, const float* LSE, const void* dO, int do_dtype, float* dQ,
+                                    float* dE_k, float* dE_v, float* dW_pe, int64_t B, int64_t H, int64_t T, int64_t hd,
+                                    int64_t N, int64_t K, int64_t V_total, int flags, int mode, void* workspace,
+                                    size_t workspace_bytes, void* stream) {
+    if (!e_row_index) return MBEMA_ERR_NULL;
+    return flash_bwd_impl(Q, q_dtype, x, E_k, E_v, e_dtype, e_row_index, e_rows, W_pe, rhos, unique, tile_state, tok_state,
+                          kcount, seq_lens, O, LSE, dO, do_dtype, dQ, dE_k, dE_v, dW_pe, B, H, T, hd, N, K, V_total, flags,
+                          mode, workspace, workspace_bytes, stream);
 }

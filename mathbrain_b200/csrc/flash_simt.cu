@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(FS_THREADS) k_flash_fwd_simt(FlashArgs a) {
         if (kv < 0) continue;  // uniform across the CTA
         const int key = (int)(kv & 0x7fffffffLL);
         build_state_rows(a, b, tile, k, key, r_tile, tr, dg, lane, tok_sh, l2r_sh, A_sh, ldA);
-        const size_t eoff = ((size_t)b * a.K + k) * D + h * FS_HD + dg * 16;
+        const size_t eoff = e_row(a, b, k) * D + h * FS_HD + dg * 16;
         float ek[16], ev[16];
 #pragma unroll
         for (int i = 0; i < 16; i += 4) {
@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(FS_THREADS) k_flash_bwd_simt(FlashArgs a) {
         if (kv < 0) continue;
         const int key = (int)(kv & 0x7fffffffLL);
         build_state_rows(a, b, tile, k, key, r_tile, tr, dg, lane, tok_sh, l2r_sh, A_sh, ldA);
-        const size_t eoff = ((size_t)b * a.K + k) * D + h * FS_HD + dg * 16;
+        const size_t eoff = e_row(a, b, k) * D + h * FS_HD + dg * 16;
         float ek[16], ev[16];
 #pragma unroll
         for (int i = 0; i < 16; i += 4) {
@@ -346,7 +346,7 @@ __global__ void __launch_bounds__(FS_THREADS) k_flash_bwd_simt(FlashArgs a) {
             float s = 0.f;
 #pragma unroll 8
             for (int r = 0; r < FS_ROWS; ++r) s += Z[r * FS_ZLD + cc];
-            float* dst = ((tid < FS_HD) ? a.dEk : a.dEv) + ((size_t)b * a.K + k) * D + h * FS_HD + c;
+            float* dst = ((tid < FS_HD) ? a.dEk : a.dEv) + e_row(a, b, k) * D + h * FS_HD + c;
             atomicAdd(dst, s);
         }
         // the next iteration's first __syncthreads orders these reads before A_sh / Z are rewritten:
@@ -396,8 +396,8 @@ size_t flash_bwd_simt_ws(int64_t B, int64_t H, int64_t T, int64_t N) {
 int flash_bwd_simt(FlashArgs a, float* dW, void* ws, cudaStream_t st) {
     const int D = a.H * FS_HD;
     a.dW_part = (float*)(((uintptr_t)ws + 255) / 256 * 256);
-    MBEMA_CUDA_TRY(cudaMemsetAsync(a.dEk, 0, (size_t)a.B * a.K * D * sizeof(float), st));
-    MBEMA_CUDA_TRY(cudaMemsetAsync(a.dEv, 0, (size_t)a.B * a.K * D * sizeof(float), st));
+    MBEMA_CUDA_TRY(cudaMemsetAsync(a.dEk, 0, (size_t)a.e_rows * D * sizeof(float), st));
+    MBEMA_CUDA_TRY(cudaMemsetAsync(a.dEv, 0, (size_t)a.e_rows * D * sizeof(float), st));
     const size_t smem = fs_smem_bwd(a.N);
     MBEMA_CUDA_TRY(cudaFuncSetAttribute(k_flash_bwd_simt, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid(2 * a.nT, a.H, a.B);

@@ -82,7 +82,8 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 
 // SILU is a compile-time switch: a run-time test inside the unrolled epilogue would put a branch between every
 // pair of gate elements and stop the scheduler from overlapping their MUFU and FMA latencies.
-template <bool SILU, int NK>
+// ROWS: slot-embedding rows are looked up through FlashArgs::erow (tables shared between samples)
+template <bool SILU, int NK, bool ROWS>
 __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* status) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -210,12 +211,16 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
         const int s_chunks = N / 8, e_chunks = ACC_COLS * esize / 16;     // 16-byte chunks per row (bf16 snapshot; raw E)
         const __nv_bfloat16* snap16 = reinterpret_cast<const __nv_bfloat16*>(a.tile_state + (size_t)a.B * a.nT * a.K * N);
         // Asynchronous prefetch of slot j's snapshot row and raw E_k / E_v rows into ring stage j % RING.
+        // E row of the next slot to prefetch (tables shared between samples: one index load per slot, a slot ahead)
+        size_t erow_next = (ROWS && n_slots > 0) ? (size_t)a.erow[(size_t)b * a.K + slot_sh[0]] : 0;
         auto prefetch = [&](int j) {
             if (j < n_slots && row < s_chunks + 2 * e_chunks) {   // threads without a chunk to copy skip the address arithmetic too
                 const int k = slot_sh[j];
+                const size_t er = ROWS ? erow_next : (size_t)b * a.K + k;
+                if (ROWS && j + 1 < n_slots) erow_next = (size_t)a.erow[(size_t)b * a.K + slot_sh[j + 1]];
                 unsigned char* dst = ring_sh + (j % RING) * RING_STAGE_BYTES;
                 const unsigned char* srcS = reinterpret_cast<const unsigned char*>(snap16 + (((size_t)b * a.nT + tile) * a.K + k) * N);
-                const size_t eoff = (((size_t)b * a.K + k) * D + hp * ACC_COLS) * esize;
+                const size_t eoff = (er * D + hp * ACC_COLS) * esize;
                 const unsigned char* srcK = reinterpret_cast<const unsigned char*>(a.Ek) + eoff;
                 const unsigned char* srcV = reinterpret_cast<const unsigned char*>(a.Ev) + eoff;
                 for (int c = row; c < s_chunks + 2 * e_chunks; c += PROD_THREADS) {
@@ -448,13 +453,19 @@ int flash_fwd_tc(const FlashArgs& a, void* ws, cudaStream_t st) {
     const tc::Smem L = tc::smem_layout(a.N, a.K);
     if (L.total > 227 * 1024) return MBEMA_ERR_UNSUPPORTED;
     dim3 grid(a.nT, a.H / tc::HPC, a.B);
-#define MBEMA_LAUNCH_FWD(S_, NK_)                                                                                     \
+#define MBEMA_LAUNCH_FWD(S_, NK_, R_)                                                                                     \
     do {                                                                                                             \
-        MBEMA_CUDA_TRY(cudaFuncSetAttribute(tc::k_flash_fwd_tc<S_, NK_>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total)); \
-        tc::k_flash_fwd_tc<S_, NK_><<<grid, tc::THREADS, L.total, st>>>(a, status);                                 \
+        MBEMA_CUDA_TRY(cudaFuncSetAttribute(tc::k_flash_fwd_tc<S_, NK_, R_>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total)); \
+        tc::k_flash_fwd_tc<S_, NK_, R_><<<grid, tc::THREADS, L.total, st>>>(a, status);                                 \
     } while (0)
-    if (a.N == 64) { if (a.silu) MBEMA_LAUNCH_FWD(true, 1); else MBEMA_LAUNCH_FWD(false, 1); }
-    else { if (a.silu) MBEMA_LAUNCH_FWD(true, 2); else MBEMA_LAUNCH_FWD(false, 2); }
+    const bool rows = a.erow != nullptr;
+#define MBEMA_PICK(R_)                                                                     \
+    do {                                                                                   \
+        if (a.N == 64) { if (a.silu) MBEMA_LAUNCH_FWD(true, 1, R_); else MBEMA_LAUNCH_FWD(false, 1, R_); }             \
+        else { if (a.silu) MBEMA_LAUNCH_FWD(true, 2, R_); else MBEMA_LAUNCH_FWD(false, 2, R_); }                       \
+    } while (0)
+    if (rows) MBEMA_PICK(true); else MBEMA_PICK(false);
+#undef MBEMA_PICK
 #undef MBEMA_LAUNCH_FWD
     return check_launch();
 }

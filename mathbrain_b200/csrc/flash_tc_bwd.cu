@@ -98,7 +98,8 @@ __device__ __forceinline__ float tmem_ld_1(uint32_t taddr) {
     return __uint_as_float(r);
 }
 
-template <bool SILU, int NK>
+// ROWS: slot-embedding rows are looked up through FlashArgs::erow (tables shared between samples)
+template <bool SILU, int NK, bool ROWS>
 __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* status) {
     constexpr int N = Cfg<NK>::N, NA = Cfg<NK>::NA, NACC = Cfg<NK>::NACC;
     constexpr int COL_DW = Cfg<NK>::COL_DW, COL_DEK = Cfg<NK>::COL_DEK, COL_DEV = Cfg<NK>::COL_DEV, COL_DQ = Cfg<NK>::COL_DQ;
@@ -236,12 +237,16 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
         const int esize = (a.e_dt == MBEMA_F32) ? 4 : 2;
         const int s_chunks = N / 8, e_chunks = ACC_COLS * esize / 16;
         const __nv_bfloat16* snap16 = reinterpret_cast<const __nv_bfloat16*>(a.tile_state + (size_t)a.B * a.nT * a.K * N);
+        // E row of the next slot to prefetch (tables shared between samples: one index load per slot, a slot ahead)
+        size_t erow_next = (ROWS && n_slots > 0) ? (size_t)a.erow[(size_t)b * a.K + slot_sh[0]] : 0;
         auto prefetch = [&](int j) {
             if (j < n_slots && row < s_chunks + 2 * e_chunks) {   // threads without a chunk to copy skip the address arithmetic too
                 const int k = slot_sh[j];
+                const size_t er = ROWS ? erow_next : (size_t)b * a.K + k;
+                if (ROWS && j + 1 < n_slots) erow_next = (size_t)a.erow[(size_t)b * a.K + slot_sh[j + 1]];
                 unsigned char* dst = ring_sh + (j % RING) * RING_STAGE_BYTES;
                 const unsigned char* srcS = reinterpret_cast<const unsigned char*>(snap16 + (((size_t)b * a.nT + tile) * a.K + k) * N);
-                const size_t eoff = (((size_t)b * a.K + k) * D + hp * ACC_COLS) * esize;
+                const size_t eoff = (er * D + hp * ACC_COLS) * esize;
                 const unsigned char* srcK = reinterpret_cast<const unsigned char*>(a.Ek) + eoff;
                 const unsigned char* srcV = reinterpret_cast<const unsigned char*>(a.Ev) + eoff;
                 for (int c = row; c < s_chunks + 2 * e_chunks; c += PROD_THREADS) {
@@ -443,11 +448,14 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             tmem_wait_st();
         }
         unsigned char* zrow = Z_sh + wg * ATOM_BYTES + row * 128;     // + kind * HPC * ATOM_BYTES + swizzled chunk
-        float* dE_out = (wg == 0 ? a.dEk : a.dEv) + (size_t)b * a.K * D + hp * ACC_COLS + row;   // + slot * D
+        float* dE_out = (wg == 0 ? a.dEk : a.dEv) + hp * ACC_COLS + row;   // + E row of the slot * D
+        size_t de_row_prev = 0;                                          // E row of slot i - 1
         const uint32_t t_de = t_lane + (wg == 0 ? COL_DEK : COL_DEV);
 
         for (int i = 0; i < n_slots; ++i) {
             const int sa = i % NA, sc = i % NACC;
+            size_t de_row_cur = 0;                                      // used one iteration later: the load has a whole slot to land
+            if (ROWS) de_row_cur = (size_t)a.erow[(size_t)b * a.K + slot_sh[i]];
             mbar_wait(&bars->acc_full[sc], (uint32_t)((i / NACC) & 1), abort_flag);
             tc_fence_after_sync();
             const uint32_t t_acc = t_lane + (uint32_t)(sc * ACC_COLS + wg * HD);
@@ -510,7 +518,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                 tc_fence_after_sync();
                 const float v = tmem_ld_1(t_de);
                 tmem_wait_ld();
-                atomicAdd(dE_out + (size_t)slot_sh[i - 1] * D, v);
+                atomicAdd(dE_out + (ROWS ? de_row_prev : (size_t)b * a.K + slot_sh[i - 1]) * D, v);
             }
             // ---- pass 2: operand tiles of the dW / dE products in packed bf16 arithmetic, dQ in fp32 (TMEM)
             const uint32_t* ek2 = reinterpret_cast<const uint32_t*>(E2_sh + sa * 2 * ACC_COLS + wg * HD);
@@ -557,13 +565,14 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                 mbar_arrive(&bars->z_full);
                 mbar_arrive(&bars->acc_empty[sc]);
             }
+            if (ROWS) de_row_prev = de_row_cur;
         }
         if (n_slots > 0) {
             mbar_wait(&bars->z_done, (uint32_t)((n_slots - 1) & 1), abort_flag);
             tc_fence_after_sync();
             const float v = tmem_ld_1(t_de);
             tmem_wait_ld();
-            atomicAdd(dE_out + (size_t)slot_sh[n_slots - 1] * D, v);
+            atomicAdd(dE_out + (ROWS ? de_row_prev : (size_t)b * a.K + slot_sh[n_slots - 1]) * D, v);
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -630,17 +639,23 @@ int flash_bwd_tc(FlashArgs a, float* dW, void* ws, cudaStream_t st) {
     int* status = reinterpret_cast<int*>((reinterpret_cast<uintptr_t>(ws) + 255) & ~uintptr_t(255));
     a.dW_part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(status) + 256);
     MBEMA_CUDA_TRY(cudaMemsetAsync(status, 0, 256, st));
-    MBEMA_CUDA_TRY(cudaMemsetAsync(a.dEk, 0, (size_t)a.B * a.K * D * sizeof(float), st));
-    MBEMA_CUDA_TRY(cudaMemsetAsync(a.dEv, 0, (size_t)a.B * a.K * D * sizeof(float), st));
+    MBEMA_CUDA_TRY(cudaMemsetAsync(a.dEk, 0, (size_t)a.e_rows * D * sizeof(float), st));
+    MBEMA_CUDA_TRY(cudaMemsetAsync(a.dEv, 0, (size_t)a.e_rows * D * sizeof(float), st));
     const tcb::Smem L = tcb::smem_layout(a.K, a.N / 64);
     dim3 grid(a.nT, a.H / tcb::HPC, a.B);
-#define MBEMA_LAUNCH_BWD(S_, NK_)                                                                                     \
+#define MBEMA_LAUNCH_BWD(S_, NK_, R_)                                                                                     \
     do {                                                                                                             \
-        MBEMA_CUDA_TRY(cudaFuncSetAttribute(tcb::k_flash_bwd_tc<S_, NK_>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total)); \
-        tcb::k_flash_bwd_tc<S_, NK_><<<grid, tcb::THREADS, L.total, st>>>(a, status);                               \
+        MBEMA_CUDA_TRY(cudaFuncSetAttribute(tcb::k_flash_bwd_tc<S_, NK_, R_>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total)); \
+        tcb::k_flash_bwd_tc<S_, NK_, R_><<<grid, tcb::THREADS, L.total, st>>>(a, status);                               \
     } while (0)
-    if (a.N == 64) { if (a.silu) MBEMA_LAUNCH_BWD(true, 1); else MBEMA_LAUNCH_BWD(false, 1); }
-    else { if (a.silu) MBEMA_LAUNCH_BWD(true, 2); else MBEMA_LAUNCH_BWD(false, 2); }
+    const bool rows = a.erow != nullptr;
+#define MBEMA_PICK(R_)                                                                     \
+    do {                                                                                   \
+        if (a.N == 64) { if (a.silu) MBEMA_LAUNCH_BWD(true, 1, R_); else MBEMA_LAUNCH_BWD(false, 1, R_); }             \
+        else { if (a.silu) MBEMA_LAUNCH_BWD(true, 2, R_); else MBEMA_LAUNCH_BWD(false, 2, R_); }                       \
+    } while (0)
+    if (rows) MBEMA_PICK(true); else MBEMA_PICK(false);
+#undef MBEMA_PICK
 #undef MBEMA_LAUNCH_BWD
     int rc = check_launch();
     if (rc) return rc;

@@ -364,6 +364,105 @@ class FlashEMAFunction(torch.autograd.Function):
         return (dQ.to(qd), None, dEk.to(kd), dEv.to(vd), dW.to(wd), None, None, None, None, None, None, None)
 
 
+def shared_slot_rows(unique_tensor):
+    """Rows for slot-embedding tables shared between samples: returns (tokens[U] int64, row_index[B,K] int32) with
+    tokens the sorted distinct tokens listed anywhere in `unique_tensor` (entries < 0 are padding) and
+    tokens[row_index[b,k]] == unique_tensor[b,k] at every listed slot (0 at padded ones, never read)."""
+    _require_cuda(unique_tensor)
+    valid = unique_tensor >= 0
+    tokens, inverse = torch.unique(unique_tensor[valid], return_inverse=True)
+    row_index = torch.zeros(unique_tensor.shape, dtype=torch.int32, device=unique_tensor.device)
+    row_index[valid] = inverse.to(torch.int32)
+    return tokens, row_index
+
+
+class FlashEMARowsFunction(torch.autograd.Function):
+    """FlashEMAFunction with slot-embedding rows shared between samples (an extension: the reference always
+    materialises per-sample [B,K_max,D] tensors, mathbrain/model.py:63-68).
+
+    forward(Q[B,H,L,hd], x[B,L], E_k_rows[U,D], E_v_rows[U,D], row_index[B,K_max] int32, W_pe[N,D], rhos[N], V_total,
+            unique_tensor[B,K_max], K_max, C_bounds, use_silu)
+    Slot (b,k) reads row row_index[b,k] (see shared_slot_rows); the gradients of E_k_rows / E_v_rows are the sums over
+    all slots sharing a row.  backward returns (dQ, None, dE_k_rows, dE_v_rows, None, dW_pe, None x 6)."""
+
+    @staticmethod
+    def forward(ctx, Q, x, E_k_rows, E_v_rows, row_index, W_pe, rhos, V_total, unique_tensor, K_max, C_bounds,
+                use_silu=True):
+        _require_cuda(Q, x, E_k_rows, E_v_rows, row_index, W_pe, rhos, unique_tensor)
+        if not isinstance(C_bounds, TileStates):
+            raise _lib.MbemaError("C_bounds must come from mathbrain_b200.precompute_boundaries")
+        lib = _lib.load()
+        B, H, L, hd = Q.shape
+        D = H * hd
+        N = rhos.shape[0]
+        K = int(K_max)
+        if C_bounds.shape != (B, L, K, N):
+            raise _lib.MbemaError("C_bounds was built for (B,L,K,N)=%s, operator called with %s"
+                                  % (C_bounds.shape, (B, L, K, N)))
+        Qc = _f32_or_bf16(Q).contiguous()
+        Ek = _f32_or_bf16(E_k_rows).contiguous()
+        Ev = _f32_or_bf16(E_v_rows).to(Ek.dtype).contiguous()
+        U = Ek.shape[0]
+        if Ek.dim() != 2 or Ek.shape[1] != D or Ev.shape != Ek.shape or U < 1:
+            raise _lib.MbemaError("E_k_rows / E_v_rows must be [U, D] with U >= 1")
+        if tuple(row_index.shape) != (B, K):
+            raise _lib.MbemaError("row_index must be [B, K_max]")
+        ri = row_index.to(torch.int32).contiguous()
+        W = W_pe.float().contiguous()
+        if W.shape != (N, D):
+            raise _lib.MbemaError("W_pe must be [N, D]")
+        rh = rhos.float().contiguous()
+        xx = x.long().contiguous()
+        O = torch.empty(B, H, L, hd, dtype=torch.float32, device=Q.device)
+        LSE = torch.empty(B, H, L, dtype=torch.float32, device=Q.device)
+        mode = _MODES[_OPTIONS["mode"]]
+        flags = _flash_flags(use_silu)
+        ws = _workspace(lib.mbema_flash_fwd_workspace_bytes(B, H, L, hd, N, K, mode), Q.device)
+        _ev = telemetry.begin("mbema_flash_fwd")
+        rc = lib.mbema_flash_fwd_rows(_ptr(Qc), _dt(Qc), _ptr(xx), _ptr(Ek), _ptr(Ev), _dt(Ek), _ptr(ri), U, _ptr(W),
+                                      _ptr(rh), _ptr(C_bounds.unique), _ptr(C_bounds.tile_state),
+                                      _ptr(C_bounds.tok_state), _ptr(C_bounds.kcount), _ptr(C_bounds.seq_lens),
+                                      _ptr(O), _ptr(LSE), B, H, L, hd, N, K, int(V_total), flags, mode, _ptr(ws),
+                                      ws.numel(), _stream())
+        telemetry.end("mbema_flash_fwd", _ev)
+        _lib.check(rc, "mbema_flash_fwd_rows")
+        if mode == _lib.MODE_TC_BF16:
+            global _last_tc_workspace
+            _last_tc_workspace = ws
+        ctx.save_for_backward(Qc, xx, Ek, Ev, ri, W, rh, O, LSE)
+        ctx.handle = C_bounds
+        ctx.meta = (B, H, L, hd, N, K, U, int(V_total), flags, mode)
+        ctx.in_dtypes = (Q.dtype, E_k_rows.dtype, E_v_rows.dtype, W_pe.dtype)
+        return O
+
+    @staticmethod
+    def backward(ctx, dO):
+        lib = _lib.load()
+        Qc, xx, Ek, Ev, ri, W, rh, O, LSE = ctx.saved_tensors
+        h = ctx.handle
+        B, H, L, hd, N, K, U, V_total, flags, mode = ctx.meta
+        D = H * hd
+        dOc = _f32_or_bf16(dO).contiguous()
+        dQ = torch.empty(B, H, L, hd, dtype=torch.float32, device=dO.device)
+        dEk = torch.empty(U, D, dtype=torch.float32, device=dO.device)
+        dEv = torch.empty(U, D, dtype=torch.float32, device=dO.device)
+        dW = torch.empty(N, D, dtype=torch.float32, device=dO.device)
+        ws = _workspace(lib.mbema_flash_bwd_workspace_bytes(B, H, L, hd, N, K, mode), dO.device)
+        _ev = telemetry.begin("mbema_flash_bwd")
+        rc = lib.mbema_flash_bwd_rows(_ptr(Qc), _dt(Qc), _ptr(xx), _ptr(Ek), _ptr(Ev), _dt(Ek), _ptr(ri), U, _ptr(W),
+                                      _ptr(rh), _ptr(h.unique), _ptr(h.tile_state), _ptr(h.tok_state), _ptr(h.kcount),
+                                      _ptr(h.seq_lens), _ptr(O), _ptr(LSE), _ptr(dOc), _dt(dOc), _ptr(dQ), _ptr(dEk),
+                                      _ptr(dEv), _ptr(dW), B, H, L, hd, N, K, V_total, flags, mode, _ptr(ws),
+                                      ws.numel(), _stream())
+        telemetry.end("mbema_flash_bwd", _ev)
+        _lib.check(rc, "mbema_flash_bwd_rows")
+        if mode == _lib.MODE_TC_BF16:
+            global _last_tc_workspace
+            _last_tc_workspace = ws
+        qd, kd, vd, wd = ctx.in_dtypes
+        return (dQ.to(qd), None, dEk.to(kd), dEv.to(vd), None, dW.to(wd), None, None, None, None, None, None)
+
+
 # ---------------------------------------------------------------------------------------------
 # query gate + LayerNorm
 # ---------------------------------------------------------------------------------------------

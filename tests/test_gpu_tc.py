@@ -109,3 +109,45 @@ def test_tc_unsupported_shape_is_refused(mb):
     inp, c_base, _ = make_case(5, B=1, T=64, N=16, H=2, vocab=100, max_prefix=10, min_hl=2.0, max_hl=30.0)
     with pytest.raises(mb._lib.MbemaError):
         run_tc(mb, inp, c_base, with_grad=False)
+
+
+@pytest.mark.parametrize("mode", ["tc_bf16", "fp32"])
+def test_shared_embedding_rows_match_per_sample_tensors(mb, mode):
+    """Slot-embedding rows shared between samples (one row per token listed anywhere in the batch): same output as the
+    per-sample [B,K,D] tensors gathered from those rows, and row gradients equal to the scatter-sum of the per-sample ones."""
+    inp, c_base, _ = make_case(23, B=4, T=260, N=64, H=2, vocab=150, max_prefix=120, min_hl=4.0, max_hl=300.0, std=0.1)
+    dev = "cuda"
+    unique = inp["unique"].to(dev)
+    tokens, row_index = mb.shared_slot_rows(unique)
+    U, D = tokens.numel(), inp["E_k"].shape[-1]
+    g = torch.Generator().manual_seed(3)
+    dt = torch.bfloat16 if mode == "tc_bf16" else torch.float32
+    Ek_rows = (torch.randn(U, D, generator=g) * 0.1).to(dt).to(dev)
+    Ev_rows = (torch.randn(U, D, generator=g) * 0.1).to(dt).to(dev)
+    valid = (unique >= 0).unsqueeze(-1)
+    Ek_b = (Ek_rows[row_index.long()] * valid).detach().clone().requires_grad_(True)
+    Ev_b = (Ev_rows[row_index.long()] * valid).detach().clone().requires_grad_(True)
+    Ek_r, Ev_r = Ek_rows.clone().requires_grad_(True), Ev_rows.clone().requires_grad_(True)
+    x, rhos = inp["x"].to(dev), inp["rhos"].to(dev)
+    K = unique.shape[1]
+    dO = inp["dO"].to(dev).float()
+    outs = []
+    with mb.options(mode=mode):
+        h = mb.precompute_boundaries(x, unique, rhos, 64, c_init=c_base.to(dev))
+        for shared in (False, True):
+            Q = inp["Q"].to(dev).to(dt).requires_grad_(True)
+            W = inp["W_pe"].to(dev).requires_grad_(True)
+            if shared:
+                O = mb.FlashEMARowsFunction.apply(Q, x, Ek_r, Ev_r, row_index, W, rhos, inp["V"], unique, K, h, True)
+            else:
+                O = mb.FlashEMAFunction.apply(Q, x, Ek_b, Ev_b, W, rhos, inp["V"], unique, K, h, True)
+            O.backward(dO)
+            outs.append((O.detach().float().cpu(), Q.grad.float().cpu(), W.grad.float().cpu()))
+    assert mb.device_status() == 0
+    assert float((outs[0][0] - outs[1][0]).abs().max()) == 0.0                 # forward: the same rows, bit for bit
+    assert rel_err(outs[1][1], outs[0][1]) < 1e-6                              # dQ
+    assert rel_err(outs[1][2], outs[0][2]) < 1e-5                              # dW_pe (per-CTA partials, same order)
+    for rows_grad, per_sample in ((Ek_r.grad, Ek_b.grad), (Ev_r.grad, Ev_b.grad)):
+        ref = torch.zeros(U, D, device=dev)
+        ref.index_add_(0, row_index.long().reshape(-1), (per_sample.float() * valid).reshape(-1, D))
+        assert rel_err(rows_grad.float().cpu(), ref.cpu()) < (2e-2 if mode == "tc_bf16" else 1e-5)   # atomics: order differs
