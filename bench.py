@@ -90,6 +90,22 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------------------------- native arm
+WORKLOAD = "46M-config hot path: scan + snapshots + 6 x (query gate, flash-EMA fwd, bwd of both)"
+
+
+def make_rank_batch(rank, world):
+    """The global batch of the 8-GPU configuration (8 x B samples) is drawn identically on every rank and split into
+    8 cost-balanced shards (cost = listed slots; all T steps are computed).  Rank r runs shard r at every N, so the
+    per-GPU work does not change with N and the slowest rank stays close to the mean."""
+    from mathbrain_b200 import dp, synth
+    c = CFG
+    n_shards = max(8, world)
+    host = synth.make_chunk_batch(1000, c["B"] * n_shards, c["T"], c["N"], vocab=c["V"], max_prefix=c["max_prefix"],
+                                  min_fill=c["min_fill"], min_hl=c["min_hl"], max_hl=c["max_hl"])
+    shards = dp.balanced_shards(host["pad_mask"].sum(1).tolist(), n_shards)
+    return synth.select_samples(host, shards[rank])
+
+
 class HotPath:
     """Device-resident operands of the 6-layer hot path and the step function."""
 
@@ -99,15 +115,7 @@ class HotPath:
         self.mb = mb
         self.dev = dev
         c = CFG
-        # The global batch of the 8-GPU configuration (8 x B samples) is drawn identically on every rank and split into
-        # 8 cost-balanced shards (cost = listed slots; all T steps are computed).  Rank r runs shard r at every N, so
-        # the per-GPU work does not change with N and the slowest rank stays close to the mean.
-        from mathbrain_b200 import dp
-        n_shards = max(8, world)
-        self.host = synth.make_chunk_batch(1000, c["B"] * n_shards, c["T"], c["N"], vocab=c["V"], max_prefix=c["max_prefix"],
-                                           min_fill=c["min_fill"], min_hl=c["min_hl"], max_hl=c["max_hl"])
-        shards = dp.balanced_shards(self.host["pad_mask"].sum(1).tolist(), n_shards)
-        self.host = synth.select_samples(self.host, shards[rank])
+        self.host = make_rank_batch(rank, world)
         self.K = self.host["K_max"]
         self.pinned = {k: self.host[k].pin_memory() for k in ("x", "unique_slots", "pad_mask", "c_base", "fill")}
         self.h2d_bytes = sum(t.numel() * t.element_size() for t in self.pinned.values())
@@ -406,8 +414,7 @@ def run_reference(args, rank):
     from mathbrain_b200 import synth
     c = CFG
     threads = os.cpu_count() or 1
-    host = synth.make_chunk_batch(1000, c["B"], c["T"], c["N"], vocab=c["V"], max_prefix=c["max_prefix"],
-                                  min_fill=c["min_fill"], min_hl=c["min_hl"], max_hl=c["max_hl"])
+    host = make_rank_batch(0, 1)           # the batch of the native arm's rank 0
     steps_t = 256
     for _ in range(max(1, args.warmup)):
         cpu_baseline_sample(host, threads, steps_t=8)
@@ -423,7 +430,11 @@ def run_reference(args, rank):
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1000.0,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "46M-config hot path (B=56,T=512,d=512,H=8,N=64,6 layers,V=50257), CPU sample"},
+            "config": {"workload": WORKLOAD, "B_per_gpu": c["B"], "T": c["T"], "d_model": c["D"], "heads": c["H"], "N": c["N"],
+                       "layers": c["L"], "vocab": c["V"], "K_max": host["K_max"],
+                       "mean_slots": float(host["pad_mask"].sum(1).double().mean()), "mode": "cpu_fp32",
+                       "padding": "all T steps computed, as the reference does",
+                       "note": "bounded CPU sample of this workload, see cpu_baseline.sample", "parallelism": "cpu"},
             "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
@@ -518,7 +529,7 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / args.steps * 1000.0,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32" if args.mode == "fp32" else "bf16", "data": "synthetic",
-            "config": {"workload": "46M-config hot path: scan + snapshots + 6 x (query gate, flash-EMA fwd, bwd of both)",
+            "config": {"workload": WORKLOAD,
                        "B_per_gpu": c["B"], "T": c["T"], "d_model": c["D"], "heads": c["H"], "N": c["N"],
                        "layers": c["L"], "vocab": c["V"], "K_max": hp.K, "mean_slots": hp.slot_steps / (c["B"] * c["T"]),
                        "mode": args.mode, "padding": "all T steps computed, as the reference does",
