@@ -147,7 +147,8 @@ int mbema_qgate_bwd(const void* dY, int dy_dtype, const void* x_q, int x_dtype, 
  *   rhos [N] f32   unique [B,K] i64   tile_state, tok_state, kcount from mbema_tile_states
  *   seq_lens [B] i32 or NULL: steps >= seq_lens[b] are skipped (their outputs are left untouched)
  *   out: O [B,H,T,hd] f32, LSE [B,H,T] f32 (log of the softmax normaliser, saved for the backward)
- *   limits: hd == 64, N in {16, 32, 64, 128} for MBEMA_MODE_TC_BF16; hd == 64, N <= 128 for FP32.
+ *   limits: hd == 64; MBEMA_MODE_TC_BF16 needs N in {64, 128}, an even H and a slot list that fits shared memory
+ *   (otherwise MBEMA_ERR_UNSUPPORTED; the backward falls back to the fp32 kernels by itself); FP32: N <= 128.
  * ---------------------------------------------------------------------------------------------- */
 size_t mbema_flash_fwd_workspace_bytes(int64_t B, int64_t H, int64_t T, int64_t hd, int64_t N, int64_t K, int mode);
 int mbema_flash_fwd(const void* Q, int q_dtype, const int64_t* x, const void* E_k, const void* E_v, int e_dtype,
