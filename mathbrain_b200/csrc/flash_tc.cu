@@ -32,9 +32,11 @@ static constexpr int EPI_THREADS = 32 * EPI_WARPS;
 static constexpr int PROD_THREADS = 128;
 static constexpr int THREADS = EPI_THREADS + PROD_THREADS;
 static constexpr int ATOM_BYTES = TM * 128;        // one 128-row x 64-column bf16 swizzle atom
-static constexpr int NSTAGE = 3;                   // A-tile / accumulator / E-row pipeline depth
+static constexpr int NSTAGE_MAX = 4;               // A-tile / accumulator / E-row pipeline depth: 4 stages for N = 64 (all
+                                                   // 512 TMEM columns), 3 for N = 128 (shared memory)
+__host__ __device__ constexpr int nstage(int NK) { return NK == 1 ? 4 : 3; }
 static constexpr int ACC_COLS = HPC * HD;          // fp32 accumulator columns per stage
-static constexpr int TMEM_COLS = 512;              // power of two >= NSTAGE * ACC_COLS
+static constexpr int TMEM_COLS = 512;              // power of two >= stages * ACC_COLS
 static constexpr int MAX_SLOTS = 8192;
 static constexpr int PD = 3;                       // prefetch distance (slots) of the snapshot / E-row ring
 static constexpr int RING = PD + 1;
@@ -49,6 +51,7 @@ __host__ __device__ inline Smem smem_layout(int N, int K) {
     const int NK = N / 64;
     Smem s;
     int o = 0;
+    const int NSTAGE = nstage(NK);
     s.a_off = o; o += NSTAGE * NK * ATOM_BYTES;
     s.b_off = o; o += NK * ATOM_BYTES;
     s.r_off = o; o += NK == 1 ? TM * 64 * 2 : TM * (N + 4) * 4;   // decay powers rho_n^r: bf16 [128][64] (N = 64) or fp32
@@ -69,8 +72,8 @@ __device__ __forceinline__ int sw128_off(int row, int col) {
 }
 
 struct Bars {
-    uint64_t acc_full[NSTAGE];    // UMMAs of the stage done + E rows staged   (2 arrivals: commit, issuer)
-    uint64_t acc_empty[NSTAGE];   // every epilogue warp has read the stage's accumulators (EPI_WARPS arrivals)
+    uint64_t acc_full[NSTAGE_MAX];    // UMMAs of the stage done + E rows staged   (2 arrivals: commit, issuer)
+    uint64_t acc_empty[NSTAGE_MAX];   // every epilogue warp has read the stage's accumulators (EPI_WARPS arrivals)
     uint32_t tmem_base;
     int abort_flag;
     int n_slots;
@@ -87,7 +90,7 @@ template <bool SILU, int NK, bool ROWS>
 __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* status) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    constexpr int N = NK * 64, ldR = N + 4;
+    constexpr int N = NK * 64, ldR = N + 4, NSTAGE = nstage(NK);
     const Smem L = smem_layout(N, a.K);
     unsigned char* A_sh = sm + L.a_off;
     unsigned char* B_sh = sm + L.b_off;
