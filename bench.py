@@ -352,8 +352,23 @@ def decode_case(args):
         times.append(e0.elapsed_time(e1))
     st.check_overflow()
     ms = sorted(times[8:])[len(times[8:]) // 2]
+    # the same step replayed from a CUDA graph (step number in device memory, static q / token tensors)
+    st.use_device_step(8192 + 40)
+    tok_static = toks[0].clone()
+    graph, _, _ = st.capture_step([q] * L, E_k, E_v, W, tok_static, mode=mode)
+    gtimes = []
+    for step in range(24):
+        tok_static.copy_(toks[step])
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        gtimes.append(e0.elapsed_time(e1))
+    st.check_overflow()
+    ms_graph = sorted(gtimes[4:])[len(gtimes[4:]) // 2]
     bytes_step = B * L * K * (N * 4 + 4 + 2 * D * 2)            # state rows + last_t + E_k/E_v rows per active slot
-    print(json.dumps({"profile_case": "decode", "mode": mode, "rel_diff_vs_fp32_kernel": diff, "sequences": B, "active_slots": K, "layers": L, "ms_per_step": ms,
+    print(json.dumps({"profile_case": "decode", "mode": mode, "rel_diff_vs_fp32_kernel": diff, "sequences": B, "active_slots": K, "layers": L, "ms_per_step": ms, "ms_per_step_cuda_graph": ms_graph,
                       "tokens_per_s": B / ms * 1000.0, "algorithmic_GB_per_step": bytes_step / 1e9,
                       "achieved_GBps": bytes_step / ms / 1e6, "hbm_peak_GBps": peaks()["hbm"]}))
 

@@ -210,7 +210,8 @@ int mbema_flash_bwd_rows(const void* Q, int q_dtype, const int64_t* x, const voi
 int mbema_decode_attend(const void* q, int q_dtype, const void* E_k, const void* E_v, int e_dtype, const float* W_pe,
                         const float* rhos, const float* state, const int32_t* last_t, const int32_t* active,
                         const int32_t* n_active, float* O, int64_t B, int64_t H, int64_t hd, int64_t V, int64_t N,
-                        int64_t Kcap, int64_t t_now, int64_t V_total, int flags, void* stream);
+                        int64_t Kcap, int64_t t_now, int64_t V_total, int flags, const int32_t* t_now_dev,
+                        void* stream);
 /* Tensor-core variant of mbema_decode_attend (bf16 operands, fp32 accumulation; N = 64, hd = 64, H even, E_k/E_v
  * stored as bf16): two
  * tcgen05 passes over 128-slot tiles with a softmax over all V_total slots between them.  Same arguments plus a
@@ -221,10 +222,14 @@ int mbema_decode_attend_tc(const void* q, int q_dtype, const void* E_k, const vo
                            const float* W_pe, const float* rhos, const float* state, const int32_t* last_t,
                            const int32_t* active, const int32_t* n_active, float* O, int64_t B, int64_t H, int64_t hd,
                            int64_t V, int64_t N, int64_t Kcap, int64_t t_now, int64_t V_total, int flags,
-                           void* workspace, size_t workspace_bytes, void* stream);
+                           const int32_t* t_now_dev, void* workspace, size_t workspace_bytes, void* stream);
 int mbema_decode_update(const int64_t* tok, const float* rhos, float* state, int32_t* last_t, int32_t* active,
                         int32_t* n_active, float* C_q, int32_t* overflow, int64_t B, int64_t V, int64_t N,
-                        int64_t Kcap, int64_t t_now, void* stream);
+                        int64_t Kcap, int64_t t_now, const int32_t* t_now_dev, void* stream);
+/* t_now_dev (all three calls above): NULL, or a device int32 holding the step number, which then replaces t_now;
+ * with it a whole step (attends, update, mbema_decode_advance) can be captured in a CUDA graph and replayed.
+ * mbema_decode_advance adds one to it, ordered on the stream. */
+int mbema_decode_advance(int32_t* t_now_dev, void* stream);
 
 #ifdef __cplusplus
 }

@@ -41,11 +41,12 @@ SIGNATURES = {
                                     _vp, _i32, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32,
                                     _vp, _sz, _vp]),
     "mbema_decode_attend": (_i32, [_vp, _i32, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
-                                   _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
+                                   _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _vp]),
     "mbema_decode_attend_tc_workspace_bytes": (_sz, [_i64] * 3),
     "mbema_decode_attend_tc": (_i32, [_vp, _i32, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
-                                      _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
-    "mbema_decode_update": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
+                                      _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _sz, _vp]),
+    "mbema_decode_update": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp]),
+    "mbema_decode_advance": (_i32, [_vp, _vp]),
 }
 
 _lib = None

@@ -23,6 +23,7 @@ struct DecodeArgs {
     const int* active; const int* n_active;     // [B, Kcap], [B]
     float* O;                             // [B, H, 64]
     int B, H, V, N, Kcap, t_now;
+    const int* t_dev;              // when not null: the step number is read from device memory (graph replays)
     float v_total;
     int silu, listed_only;
 };
@@ -56,7 +57,7 @@ __global__ void __launch_bounds__(DC_THREADS) k_decode_attend(DecodeArgs a) {
         const bool ok = k < na;
         const int v = ok ? a.active[(size_t)b * a.Kcap + k] : 0;
         {   // decayed state row of this thread's slot (columns dg, dg+4, ...)
-            const float dt = ok ? (float)(a.t_now - a.last_t[(size_t)b * a.V + v]) : 0.f;
+            const float dt = ok ? (float)((a.t_dev ? *a.t_dev : a.t_now) - a.last_t[(size_t)b * a.V + v]) : 0.f;
             const float* srow = a.state + ((size_t)b * a.V + v) * N;
             for (int n = dg; n < N; n += 4) A_sh[sr * ldA + n] = ok ? srow[n] * exp2f(dt * l2r_sh[n]) : 0.f;
         }
@@ -140,7 +141,9 @@ __global__ void __launch_bounds__(DC_THREADS) k_decode_attend(DecodeArgs a) {
 // one warp per sequence: query-side state of the new token, then the slot update
 __global__ void k_decode_update(const long long* __restrict__ tok, const float* __restrict__ rhos, float* __restrict__ state,
                                 int* __restrict__ last_t, int* __restrict__ active, int* __restrict__ n_active,
-                                float* __restrict__ C_q, int* __restrict__ overflow, int B, int V, int N, int Kcap, int t_now) {
+                                float* __restrict__ C_q, int* __restrict__ overflow, int B, int V, int N, int Kcap, int t_host,
+                                const int* __restrict__ t_dev) {
+    const int t_now = t_dev ? *t_dev : t_host;
     const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (b >= B) return;
@@ -165,6 +168,8 @@ __global__ void k_decode_update(const long long* __restrict__ tok, const float* 
     }
 }
 
+__global__ void k_decode_advance(int* t_dev) { *t_dev += 1; }
+
 }  // namespace mbema
 
 using namespace mbema;
@@ -173,7 +178,7 @@ extern "C" int mbema_decode_attend(const void* q, int q_dtype, const void* E_k, 
                                    const float* W_pe, const float* rhos, const float* state, const int32_t* last_t,
                                    const int32_t* active, const int32_t* n_active, float* O, int64_t B, int64_t H,
                                    int64_t hd, int64_t V, int64_t N, int64_t Kcap, int64_t t_now, int64_t V_total,
-                                   int flags, void* stream) {
+                                   int flags, const int32_t* t_now_dev, void* stream) {
     if (B < 0 || H < 1 || V < 1 || N < 1 || Kcap < 1) return MBEMA_ERR_SHAPE;
     if (hd != 64 || N > 128 || B > 65535 || H > 65535) return MBEMA_ERR_UNSUPPORTED;
     if (B == 0) return MBEMA_OK;
@@ -181,7 +186,7 @@ extern "C" int mbema_decode_attend(const void* q, int q_dtype, const void* E_k, 
     if ((q_dtype != MBEMA_F32 && q_dtype != MBEMA_BF16) || (e_dtype != MBEMA_F32 && e_dtype != MBEMA_BF16)) return MBEMA_ERR_DTYPE;
     if (((uintptr_t)q | (uintptr_t)E_k | (uintptr_t)E_v) & 15) return MBEMA_ERR_ALIGN;
     DecodeArgs a{q, q_dtype, E_k, E_v, e_dtype, W_pe, rhos, state, last_t, active, n_active, O,
-                 (int)B, (int)H, (int)V, (int)N, (int)Kcap, (int)t_now, (float)V_total,
+                 (int)B, (int)H, (int)V, (int)N, (int)Kcap, (int)t_now, t_now_dev, (float)V_total,
                  (flags & MBEMA_FLAG_SILU) ? 1 : 0, (flags & MBEMA_FLAG_LISTED_ONLY) ? 1 : 0};
     const size_t smem = ((size_t)N * DC_HD + ((DC_SLOTS * (N + 1) + 3) & ~3) + ((N + 3) & ~3) + DC_THREADS * 18) * 4;
     MBEMA_CUDA_TRY(cudaFuncSetAttribute(k_decode_attend, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -192,13 +197,19 @@ extern "C" int mbema_decode_attend(const void* q, int q_dtype, const void* E_k, 
 
 extern "C" int mbema_decode_update(const int64_t* tok, const float* rhos, float* state, int32_t* last_t, int32_t* active,
                                    int32_t* n_active, float* C_q, int32_t* overflow, int64_t B, int64_t V, int64_t N,
-                                   int64_t Kcap, int64_t t_now, void* stream) {
+                                   int64_t Kcap, int64_t t_now, const int32_t* t_now_dev, void* stream) {
     if (B < 0 || V < 1 || N < 1 || Kcap < 1) return MBEMA_ERR_SHAPE;
     if (N > 128) return MBEMA_ERR_UNSUPPORTED;
     if (B == 0) return MBEMA_OK;
     if (!tok || !rhos || !state || !last_t || !active || !n_active || !C_q || !overflow) return MBEMA_ERR_NULL;
     k_decode_update<<<(unsigned)((B + 3) / 4), 128, 0, (cudaStream_t)stream>>>((const long long*)tok, rhos, state, last_t, active,
                                                                            n_active, C_q, overflow, (int)B, (int)V, (int)N,
-                                                                           (int)Kcap, (int)t_now);
+                                                                           (int)Kcap, (int)t_now, t_now_dev);
+    return check_launch();
+}
+
+extern "C" int mbema_decode_advance(int32_t* t_now_dev, void* stream) {
+    if (!t_now_dev) return MBEMA_ERR_NULL;
+    k_decode_advance<<<1, 1, 0, (cudaStream_t)stream>>>(t_now_dev);
     return check_launch();
 }

@@ -35,6 +35,7 @@ struct Args {
     float* scores;                 // [B, H, Kcap]: scores after pass 1, probabilities after the softmax
     float* O;                      // [B, H, 64]
     int B, H, V, Kcap, t_now, S;   // S: CTAs per (sequence, head pair); CTA s takes tiles s, s + S, ...
+    const int* t_dev;              // when not null: the step number is read from device memory (graph replays)
     float v_total;
     int listed_only;
 };
@@ -102,6 +103,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
         const int g = tid + THREADS * j, n = g >> 5, dd4 = (g & 31) * 4;
         wv[j] = __ldg(reinterpret_cast<const float4*>(a.W + (size_t)n * D + hp * ACC_COLS + dd4));
     }
+    const int t_now = a.t_dev ? *a.t_dev : a.t_now;
     int vv[MAXT * TM / THREADS];
 #pragma unroll
     for (int j = 0; j < MAXT * TM / THREADS; ++j) {
@@ -114,7 +116,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
         const int idx = tid + THREADS * j;
         if (idx < nt * TM) {
             ids_sh[idx] = vv[j];
-            dts_sh[idx] = vv[j] >= 0 ? (float)(a.t_now - a.last_t[(size_t)b * a.V + vv[j]]) : 0.f;
+            dts_sh[idx] = vv[j] >= 0 ? (float)(t_now - a.last_t[(size_t)b * a.V + vv[j]]) : 0.f;
         }
     }
     __syncthreads();
@@ -356,7 +358,8 @@ extern "C" int mbema_decode_attend_tc(const void* q, int q_dtype, const void* E_
                                       const float* W_pe, const float* rhos, const float* state, const int32_t* last_t,
                                       const int32_t* active, const int32_t* n_active, float* O, int64_t B, int64_t H,
                                       int64_t hd, int64_t V, int64_t N, int64_t Kcap, int64_t t_now, int64_t V_total,
-                                      int flags, void* workspace, size_t workspace_bytes, void* stream) {
+                                      int flags, const int32_t* t_now_dev, void* workspace, size_t workspace_bytes,
+                                      void* stream) {
     if (B < 0 || H < 1 || V < 1 || N < 1 || Kcap < 1) return MBEMA_ERR_SHAPE;
     if (hd != 64 || N != 64 || (H % 2) != 0 || B > 65535 || H > 65535) return MBEMA_ERR_UNSUPPORTED;
     if (B == 0) return MBEMA_OK;
@@ -390,7 +393,7 @@ extern "C" int mbema_decode_attend_tc(const void* q, int q_dtype, const void* E_
     if (S > 65535) return MBEMA_ERR_UNSUPPORTED;
     dtc::Args a{q, q_dtype, reinterpret_cast<const __nv_bfloat16*>(E_k), reinterpret_cast<const __nv_bfloat16*>(E_v), W_pe, rhos,
                 state, last_t, active, n_active, reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(status) + 256), O,
-                (int)B, (int)H, (int)V, (int)Kcap, (int)t_now, (int)S, (float)V_total,
+                (int)B, (int)H, (int)V, (int)Kcap, (int)t_now, (int)S, t_now_dev, (float)V_total,
                 (flags & MBEMA_FLAG_LISTED_ONLY) ? 1 : 0};
     MBEMA_CUDA_TRY(cudaMemsetAsync(status, 0, 256, st));
     MBEMA_CUDA_TRY(cudaMemsetAsync(O, 0, (size_t)B * H * hd * sizeof(float), st));

@@ -26,6 +26,47 @@ class DecodeState:
         self.n_active = torch.zeros(self.B, dtype=torch.int32, device=dev)
         self.overflow = torch.zeros(1, dtype=torch.int32, device=dev)
         self._ws = None
+        self.t_dev = None        # device int32 step number (use_device_step): replaces the t_now arguments
+
+    def use_device_step(self, t0=0):
+        """Keep the step number in device memory from now on: attend / update ignore their t_now argument and
+        advance() adds one, stream-ordered.  Nothing in a step then depends on a host value, so a whole step can be
+        captured in a CUDA graph (torch.cuda.graph) and replayed; see capture_step."""
+        self.t_dev = torch.tensor([int(t0)], dtype=torch.int32, device=self.state.device)
+        return self.t_dev
+
+    def advance(self):
+        _lib.check(_lib.load().mbema_decode_advance(_ptr(self.t_dev), _stream()), "mbema_decode_advance")
+
+    def capture_step(self, qs, E_ks, E_vs, W_pes, tok, use_silu=True, mode=None):
+        """Capture one decode step (an attend per layer over the static tensors qs[l], E_ks[l], E_vs[l], W_pes[l],
+        then the update with the static token tensor `tok`, then advance) in a CUDA graph.  Returns
+        (graph, outputs, C_q): fill qs / tok in place, call graph.replay(), read outputs[l] and C_q.  Layers whose
+        query depends on the previous layer's output need their own capture around this state's calls instead."""
+        if self.t_dev is None:
+            self.use_device_step(0)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):          # warm-up outside the capture: workspaces, kernel attributes
+            rows = torch.arange(self.B, device=tok.device)
+            tk = tok.long().clamp(0, self.V - 1)
+            keep = (self.state[rows, tk].clone(), self.last_t[rows, tk].clone(), self.active.clone(),
+                    self.n_active.clone(), self.t_dev.clone(), self.overflow.clone())
+            for l in range(len(qs)):
+                self.attend(qs[l], E_ks[l], E_vs[l], W_pes[l], 0, use_silu=use_silu, mode=mode)
+            self.update(tok, 0)
+            self.advance()
+            self.state[rows, tk] = keep[0]            # undo the warm-up step: only the tokens' own rows were touched
+            self.last_t[rows, tk] = keep[1]
+            for dst, src in zip((self.active, self.n_active, self.t_dev, self.overflow), keep[2:]):
+                dst.copy_(src)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            outs = [self.attend(qs[l], E_ks[l], E_vs[l], W_pes[l], 0, use_silu=use_silu, mode=mode) for l in range(len(qs))]
+            C_q = self.update(tok, 0)
+            self.advance()
+        return graph, outs, C_q
 
     def attend(self, q, E_k, E_v, W_pe, t_now, V_total=None, use_silu=True, listed_only=False, mode=None):
         """O [B, H, 64] float32.  q [B, H, 64]; E_k, E_v [V, H*64] projected slot embeddings; W_pe [N, H*64].
@@ -54,7 +95,7 @@ class DecodeState:
                                             _ptr(self.state), _ptr(self.last_t), _ptr(self.active),
                                             _ptr(self.n_active), _ptr(O), B, H, hd, self.V, self.N, self.cap,
                                             int(t_now), int(self.V if V_total is None else V_total), flags,
-                                            _ptr(self._ws), self._ws.numel(), _stream())
+                                            _ptr(self.t_dev), _ptr(self._ws), self._ws.numel(), _stream())
             _lib.check(rc, "mbema_decode_attend_tc")
             return O
         if mode != "fp32":
@@ -62,7 +103,7 @@ class DecodeState:
         rc = lib.mbema_decode_attend(_ptr(q), _dt(q), _ptr(E_k), _ptr(E_v), _dt(E_k), _ptr(W), _ptr(self.rhos),
                                      _ptr(self.state), _ptr(self.last_t), _ptr(self.active), _ptr(self.n_active),
                                      _ptr(O), B, H, hd, self.V, self.N, self.cap, int(t_now),
-                                     int(self.V if V_total is None else V_total), flags, _stream())
+                                     int(self.V if V_total is None else V_total), flags, _ptr(self.t_dev), _stream())
         _lib.check(rc, "mbema_decode_attend")
         return O
 
@@ -74,7 +115,7 @@ class DecodeState:
         C_q = torch.empty(self.B, self.N, dtype=torch.float32, device=tok.device)
         rc = lib.mbema_decode_update(_ptr(tok), _ptr(self.rhos), _ptr(self.state), _ptr(self.last_t), _ptr(self.active),
                                      _ptr(self.n_active), _ptr(C_q), _ptr(self.overflow), self.B, self.V, self.N,
-                                     self.cap, int(t_now), _stream())
+                                     self.cap, int(t_now), _ptr(self.t_dev), _stream())
         _lib.check(rc, "mbema_decode_update")
         return C_q
 

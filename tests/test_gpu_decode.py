@@ -119,3 +119,39 @@ def test_decode_tensor_core_many_tiles_per_cta():
         O_tc2 = st.attend(q, E_k, E_v, W, 4000, use_silu=silu, mode="tc_bf16", listed_only=True)
         O_322 = st.attend(q, E_k, E_v, W, 4000, use_silu=silu, mode="fp32", listed_only=True)
         assert rel_err(O_tc2.cpu(), O_322.cpu()) < 2e-2, silu
+
+
+def test_decode_step_replayed_from_a_cuda_graph():
+    """A whole step (two layers of attend, update, advance) captured once and replayed, with the step number in device
+    memory, against the same steps run eagerly on a second state."""
+    from mathbrain_b200.decode import DecodeState
+    from mathbrain_b200 import synth
+    g = torch.Generator().manual_seed(11)
+    B, V, N, H, L, steps = 5, 400, 64, 2, 2, 12
+    D = 64 * H
+    rhos = synth.make_rhos(N, 2.0, 64.0).cuda()
+    E_k = [(torch.randn(V, D, generator=g) * 0.2).to(torch.bfloat16).cuda() for _ in range(L)]
+    E_v = [(torch.randn(V, D, generator=g) * 0.2).to(torch.bfloat16).cuda() for _ in range(L)]
+    W = [(torch.randn(N, D, generator=g) * 0.1).cuda() for _ in range(L)]
+    toks = torch.randint(0, V, (steps + 3, B), generator=g).cuda()
+    Q = torch.randn(steps + 3, L, B, H, 64, generator=g).cuda()
+    st, ref = DecodeState(B, V, rhos, capacity=128), DecodeState(B, V, rhos, capacity=128)
+    for t in range(3):                       # a few eager steps first, so that the captured step starts from a used state
+        for s_ in (st, ref):
+            s_.update(toks[t], t)
+    st.use_device_step(3)
+    q_static = [Q[3, l].clone() for l in range(L)]
+    tok_static = toks[3].clone()
+    graph, outs, C_q = st.capture_step(q_static, E_k, E_v, W, tok_static, mode="tc_bf16")
+    for t in range(3, steps + 3):
+        for l in range(L):
+            q_static[l].copy_(Q[t, l])
+        tok_static.copy_(toks[t])
+        graph.replay()
+        for l in range(L):
+            O_ref = ref.attend(Q[t, l], E_k[l], E_v[l], W[l], t, mode="tc_bf16")
+            assert rel_err(outs[l].cpu(), O_ref.cpu()) < 1e-5, (t, l)      # fp32 atomics: the order of the tile sums differs
+        assert torch.equal(C_q, ref.update(toks[t], t)), t
+    assert int(st.t_dev.item()) == steps + 3
+    assert torch.equal(st.state, ref.state) and torch.equal(st.last_t, ref.last_t) and torch.equal(st.n_active, ref.n_active)
+    st.check_overflow()
