@@ -175,30 +175,39 @@ k_chain_scan(IndexWs w, const float* __restrict__ rhos, const float* __restrict_
     bool has = (sd != NO_SEED);
     int s_ref = 0;
     int last_doc = (doc_ids != nullptr) ? doc_ids[(size_t)b * T] : 0;
-    for (int j = j0; j < j1; ++j) {
-        const int t = s_pos[j];
-        bool keep = has;
-        if (doc_ids != nullptr) {
-            int d = doc_ids[(size_t)b * T + t];
-            if (has && d != last_doc) keep = false;
-            last_doc = d;
-        }
-        const int di = t - s_ref;
-        const double dt = (double)di;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            if (32 * i < N) {   // channel groups beyond N do nothing
-                int n = lane + 32 * i;
-                // one step since the last occurrence (runs of a repeated token, e.g. the padding): the decay is rho
-                // itself; longer gaps take the power in double precision (its error is amplified by 1 / (1 - rho))
-                const float pw = (di == 1) ? rho[i] : (float)exp2(dt * l2r[i]);
-                float cval = keep ? u[i] * pw : 0.0f;
-                if (n < N) out[((size_t)b * T + t) * N + n] = cval;
-                u[i] = cval + 1.0f;
+    // The chain is walked 32 occurrences at a time: every lane fetches one position (and document id), the steps then
+    // take them from registers with shuffles, so a long chain pays the load latency once per 32 steps, not per step.
+    for (int jb = j0; jb < j1; jb += 32) {
+        const int jj = jb + lane;
+        const int t_l = (jj < j1) ? s_pos[jj] : 0;
+        const int d_l = (doc_ids != nullptr && jj < j1) ? doc_ids[(size_t)b * T + t_l] : 0;
+        const int cnt = min(32, j1 - jb);
+        for (int q = 0; q < cnt; ++q) {
+            const int t = __shfl_sync(0xffffffffu, t_l, q);
+            bool keep = has;
+            if (doc_ids != nullptr) {
+                const int d = __shfl_sync(0xffffffffu, d_l, q);
+                if (has && d != last_doc) keep = false;
+                last_doc = d;
             }
+            const int di = t - s_ref;
+            const double dt = (double)di;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (32 * i < N) {   // channel groups beyond N do nothing
+                    int n = lane + 32 * i;
+                    // one step since the last occurrence (runs of a repeated token, e.g. the padding): the decay is
+                    // rho itself; longer gaps take the power in double precision (its error is amplified by
+                    // 1 / (1 - rho))
+                    const float pw = (di == 1) ? rho[i] : (float)exp2(dt * l2r[i]);
+                    float cval = keep ? u[i] * pw : 0.0f;
+                    if (n < N) out[((size_t)b * T + t) * N + n] = cval;
+                    u[i] = cval + 1.0f;
+                }
+            }
+            s_ref = t;
+            has = true;
         }
-        s_ref = t;
-        has = true;
     }
 }
 
@@ -254,10 +263,20 @@ k_tile_states(IndexWs w, const int64_t* __restrict__ unique, const float* __rest
         }
     }
     int s_ref = 0;
+    // occurrences are read 32 at a time (one per lane) and handed out with shuffles: `blk` is the first index of the
+    // block in registers; positions of other tokens or beyond T read as "no more occurrences"
+    int blk = -64, pos_l = 0x7fffffff;
+    auto occurrence = [&](int jx) -> int {       // step of the jx-th sorted entry if it is an occurrence of `key`, else INT_MAX
+        if (jx - blk >= 32) {
+            blk = jx;
+            const int jj = jx + lane;
+            pos_l = (jj < T && s_tok[jj] == key) ? s_pos[jj] : 0x7fffffff;
+        }
+        return __shfl_sync(0xffffffffu, pos_l, jx - blk);
+    };
     for (int tile = 0; tile < nT; ++tile) {
         const int t0 = tile * MBEMA_TILE_T;
-        while (j < T && s_tok[j] == key && s_pos[j] < t0) {
-            const int s = s_pos[j];
+        for (int s = occurrence(j); s < t0; s = occurrence(j)) {
             const double dt = (double)(s - s_ref);
 #pragma unroll
             for (int i = 0; i < 4; ++i)
