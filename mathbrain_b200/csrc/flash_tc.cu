@@ -2,19 +2,27 @@
 //
 // One CTA owns (sample b, a 128-step time tile, a pair of heads) and loops over the sample's valid slots.
 // Warp-specialised, 12 warps:
-//   * producer warpgroup (warps 8-11, one thread per time step): for slot k rebuilds the 128 x N state tile
-//     A[t, :] = M_t[k, :] (16-bit, 128-byte-swizzled K-major rows: fp16 of state / 64 for N = 64, whose 11
-//     significant bits keep the pre-activations of slots with states in the hundreds accurate, bf16 for N = 128)
-//     in shared memory from the tile-start snapshot and
-//     a table of decay powers, stages the slot's E_k / E_v rows as fp32, and one of its threads issues
-//         pre[128 x 128] = A[128 x N] @ (W_pe[:, 2 heads])        tcgen05.mma, fp32 accumulators in TMEM;
-//   * two epilogue warpgroups (a warpgroup per head, a thread per time step) read their 64 accumulator columns
-//     with tcgen05.ld and fuse SiLU, K = E_k*gate, V = E_v*gate, the score, the online softmax and the P.V update,
-//     all thread-local.
-// A tiles and TMEM accumulators are multi-buffered, so state generation and the tensor core run ahead of the
-// epilogue.  Registers are rebalanced with setmaxnreg (epilogue threads hold q, the output row and 64 accumulator
-// columns; the per-CTA total, 8*32*216 + 4*32*72, equals the launch allocation 384*168).  Hand-offs go through
-// mbarriers with bounded waits; nothing in here spins without a limit.
+//   * four producer warps, each working on its own slots and its own pipeline stage (slot i belongs to producer warp
+//     i % 4 and to stage i % 4), with no barrier between them.  For its slot the warp rebuilds the 128 x N state tile
+//     A[t, :] = M_t[k, :] in shared memory (fp16 of state / 64, 128-byte-swizzled K-major rows; 11 significant bits
+//     keep the pre-activations of slots with states in the hundreds accurate) as the packed product of the tile-start
+//     snapshot and a table of decay powers, converts the slot's E_k / E_v rows to fp16, and one of its lanes issues
+//         pre[128 x 128] = A[128 x N] @ (W_pe[:, 2 heads])        tcgen05.mma, fp32 accumulators in TMEM.
+//     A warp's per-slot work is a chain of latencies (copy wait, barrier poll, shared-memory loads, proxy fence, UMMA
+//     issue); four independent chains keep four slots in flight.  Because a producer warp owns its stage, it never
+//     runs more than one barrier phase ahead of the epilogue (a parity wait cannot tell phases two apart).
+//   * eight epilogue warps (a warpgroup per head): a thread owns one time step (its TMEM lane) and the head's 64
+//     accumulator columns, reads them with tcgen05.ld and fuses SiLU, K = E_k*gate, V = E_v*gate, the score, the
+//     online softmax and the P.V update, all thread-local.  One tanh per gate element is what the SM's
+//     special-function pipe allows (16 per clock per SM, packed or not); the gate is formed in fp32 and packed to
+//     fp16 pairs, the products with E_k, E_v and q are packed fp16 operations, score terms are summed 16 at a time in
+//     fp16 and then in fp32, and the P.V terms go into the fp32 output row with the mixed-precision FMA.  The P.V
+//     update of slot i - 1 shares the pass over the columns with the gate of slot i, and the softmax bookkeeping of
+//     slot i - 1 runs under the TMEM load of slot i.
+// A tiles and TMEM accumulators are four deep (all 512 TMEM columns) for N = 64.  Registers are rebalanced with
+// setmaxnreg: 8*32*216 (epilogue) + 4*32*72 (producers) equals the launch allocation 384*168 (asking for more would
+// block forever).  Hand-offs go through mbarriers with bounded waits; nothing in here spins without a limit, and a
+// wait that gives up ends the CTA's loops, drains the tensor pipe and frees TMEM before the CTA leaves.
 #include "flash.cuh"
 #include <cuda_fp16.h>
 #include "sm100_ptx.cuh"
@@ -27,37 +35,37 @@ using namespace ptx;
 static constexpr int TM = MBEMA_TILE_T;        // rows (time steps) per CTA
 static constexpr int HPC = 2;                  // heads per CTA
 static constexpr int HD = 64;
-static constexpr int EPI_WARPS = 4 * HPC;
+static constexpr int EPI_WARPS = 4 * HPC;            // 4 TMEM lane quarters x 2 heads
 static constexpr int EPI_THREADS = 32 * EPI_WARPS;
-static constexpr int PROD_THREADS = 128;
-static constexpr int THREADS = EPI_THREADS + PROD_THREADS;
-static constexpr int ATOM_BYTES = TM * 128;        // one 128-row x 64-column bf16 swizzle atom
-static constexpr int NSTAGE_MAX = 4;               // A-tile / accumulator / E-row pipeline depth: 4 stages for N = 64 (all
-                                                   // 512 TMEM columns), 3 for N = 128 (shared memory)
-__host__ __device__ constexpr int nstage(int NK) { return NK == 1 ? 4 : 3; }
+static constexpr int PROD_WARPS = 4;
+static constexpr int THREADS = EPI_THREADS + 32 * PROD_WARPS;
+static constexpr int ATOM_BYTES = TM * 128;        // one 128-row x 64-column 16-bit swizzle atom
+static constexpr int NSTAGE = PROD_WARPS;          // A-tile / accumulator stages: one per producer warp
+static constexpr int NE = NSTAGE + 1;              // E-row stages: a slot's E_v row is read one slot later than its accumulators
 static constexpr int ACC_COLS = HPC * HD;          // fp32 accumulator columns per stage
-static constexpr int TMEM_COLS = 512;              // power of two >= stages * ACC_COLS
+static constexpr int TMEM_COLS = 512;              // NSTAGE * ACC_COLS
 static constexpr int MAX_SLOTS = 8192;
-static constexpr int PD = 3;                       // prefetch distance (slots) of the snapshot / E-row ring
-static constexpr int RING = PD + 1;
-static constexpr int RING_STAGE_BYTES = 128 * 4 + 2 * ACC_COLS * 4;   // snapshot row (N <= 128 fp32) + raw E_k, E_v rows
+static constexpr float LAZY_MAX = 2.0f;            // the softmax reference maximum follows a score only beyond this margin
+static constexpr int PDW = 2;                      // a producer warp prefetches this many of its own slots ahead
+static constexpr int RW = PDW + 1;                 // ring stages per producer warp
+static constexpr int RING_STAGE_BYTES = 256 + 2 * ACC_COLS * 4;   // fp16 snapshot row (N <= 128) + raw E_k, E_v rows
+__host__ __device__ constexpr int r_stride(int N) { return N * 2; }
 
 struct Smem {
     // offsets (bytes) into the dynamic shared memory block, base aligned to 1024
-    int a_off, b_off, r_off, e_off, ring_off, ts_off, tok_off, slot_off, key_off, bar_off, total;
+    int a_off, b_off, r_off, ts_off, e_off, ring_off, tok_off, slot_off, key_off, bar_off, total;
 };
 
 __host__ __device__ inline Smem smem_layout(int N, int K) {
     const int NK = N / 64;
     Smem s;
     int o = 0;
-    const int NSTAGE = nstage(NK);
     s.a_off = o; o += NSTAGE * NK * ATOM_BYTES;
     s.b_off = o; o += NK * ATOM_BYTES;
-    s.r_off = o; o += NK == 1 ? TM * 64 * 2 : TM * (N + 4) * 4;   // decay powers rho_n^r: bf16 [128][64] (N = 64) or fp32
-    s.e_off = o; o += NSTAGE * 2 * HPC * HD * 4;
-    s.ring_off = o; o += RING * RING_STAGE_BYTES;
-    s.ts_off = o; o += NK == 1 ? TM * 64 * 2 : 0;  // N = 64: restart values (tok_state + 1) of the tile's 128 steps, bf16
+    s.r_off = o; o += TM * r_stride(N);               // decay powers rho_n^r, fp16 [128][N]
+    s.ts_off = o; o += NK == 1 ? TM * N * 2 : 0;      // N = 64: restart values (tok_state + 1) / 64 of the tile's steps, fp16
+    s.e_off = o; o += NE * 2 * ACC_COLS * 2;          // E_k / E_v rows, fp16
+    s.ring_off = o; o += PROD_WARPS * RW * RING_STAGE_BYTES;
     s.tok_off = o; o += TM * 4;
     s.slot_off = o; o += ((K * 2 + 15) / 16) * 16;
     s.key_off = o; o += ((K * 4 + 15) / 16) * 16;
@@ -66,21 +74,23 @@ __host__ __device__ inline Smem smem_layout(int N, int K) {
     return s;
 }
 
-// byte offset of element (row, col) inside one swizzled 128-row x 64-col bf16 atom
+// byte offset of element (row, col) inside one swizzled 128-row x 64-col 16-bit atom
 __device__ __forceinline__ int sw128_off(int row, int col) {
     return row * 128 + ((((col >> 3) ^ (row & 7)) << 4) | ((col & 7) << 1));
 }
 
 struct Bars {
-    uint64_t acc_full[NSTAGE_MAX];    // UMMAs of the stage done + E rows staged   (2 arrivals: commit, issuer)
-    uint64_t acc_empty[NSTAGE_MAX];   // every epilogue warp has read the stage's accumulators (EPI_WARPS arrivals)
+    uint64_t acc_full[NSTAGE];        // UMMAs of the stage done + E rows staged   (2 arrivals: commit, issuer)
+    uint64_t acc_empty[NSTAGE];       // every epilogue warp has read the stage's accumulators (EPI_WARPS arrivals)
+    uint64_t drain;                   // every issuing lane's UMMAs have completed (PROD_WARPS arrivals, teardown)
     uint32_t tmem_base;
     int abort_flag;
     int n_slots;
+    int drain_flag;                   // give-up flag of the teardown wait (kept apart from abort_flag: that wait must not be cut short)
 };
 
-__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+__device__ __forceinline__ uint4 mul4_f16x2(uint4 a, uint4 b) {
+    return make_uint4(mul_f16x2(a.x, b.x), mul_f16x2(a.y, b.y), mul_f16x2(a.z, b.z), mul_f16x2(a.w, b.w));
 }
 
 // SILU is a compile-time switch: a run-time test inside the unrolled epilogue would put a branch between every
@@ -89,16 +99,17 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 template <bool SILU, int NK, bool ROWS>
 __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* status) {
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    constexpr int N = NK * 64, ldR = N + 4, NSTAGE = nstage(NK);
+    // 1024-byte alignment for the swizzled operand tiles; the offset is added to the __shared__ array itself so that the
+    // compiler keeps addressing shared memory directly (a pointer rebuilt from an integer would turn every access generic)
+    unsigned char* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    constexpr int N = NK * 64, RS = r_stride(N);
     const Smem L = smem_layout(N, a.K);
     unsigned char* A_sh = sm + L.a_off;
     unsigned char* B_sh = sm + L.b_off;
-    float* R_sh = reinterpret_cast<float*>(sm + L.r_off);
-    float* E_sh = reinterpret_cast<float*>(sm + L.e_off);
+    unsigned char* R_sh = sm + L.r_off;                                        // fp16 [128][N]
+    unsigned char* TS_sh = sm + L.ts_off;                                      // fp16 [128][64] (N = 64)
+    __half* E2_sh = reinterpret_cast<__half*>(sm + L.e_off);                   // [stage][E_k | E_v][128 columns of the head pair]
     unsigned char* ring_sh = sm + L.ring_off;
-    __nv_bfloat16* Rb_sh = reinterpret_cast<__nv_bfloat16*>(sm + L.r_off);     // N = 64
-    uint32_t* TS2_sh = reinterpret_cast<uint32_t*>(sm + L.ts_off);             // N = 64: packed bf16 pairs
     int* tok_sh = reinterpret_cast<int*>(sm + L.tok_off);
     unsigned short* slot_sh = reinterpret_cast<unsigned short*>(sm + L.slot_off);
     int* key_sh = reinterpret_cast<int*>(sm + L.key_off);
@@ -131,7 +142,9 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
             mbar_init(&bars->acc_full[i], 2);
             mbar_init(&bars->acc_empty[i], EPI_WARPS);
         }
+        mbar_init(&bars->drain, PROD_WARPS);
         bars->abort_flag = *reinterpret_cast<volatile int*>(status);   // an earlier CTA already gave up: do nothing
+        bars->drain_flag = 0;
         fence_barrier_init();
     }
     if (warp == EPI_WARPS) {
@@ -155,35 +168,37 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
         if (lane == 0) bars->n_slots = n;
     }
     {
-        // B operand: rows = the pair's 128 output columns, K-major over n; 0.5 * W when the gate is SiLU (the
-        // epilogue evaluates SiLU(x) = h + h * tanh(h) with h = x / 2)
-        const float wscale = SILU ? 0.5f : 1.0f;
-        for (int i = tid; i < N * HPC * HD; i += THREADS) {
-            const int n = i / (HPC * HD), dd = i % (HPC * HD);
-            const float w = a.W[(size_t)n * D + hp * HPC * HD + dd] * wscale;
-            unsigned char* dstw = B_sh + (n >> 6) * ATOM_BYTES + sw128_off(dd, n & 63);
-            if (NK == 1) *reinterpret_cast<__half*>(dstw) = __float2half_rn(w * STATE_F16_UNSCALE);   // the state operand carries 1/64
-            else *reinterpret_cast<__nv_bfloat16*>(dstw) = __float2bfloat16(w);
+        // B operand: rows = the pair's 128 output columns, K-major over n, fp16 of 64 * W (the state operand carries
+        // 1/64); 0.5 * W when the gate is SiLU (the epilogue evaluates SiLU(x) = h + h * tanh(h) with h = x / 2)
+        const float wscale = (SILU ? 0.5f : 1.0f) * STATE_F16_UNSCALE;
+        for (int i = tid; i < N * ACC_COLS; i += THREADS) {
+            const int n = i / ACC_COLS, dd = i % ACC_COLS;
+            const float w = a.W[(size_t)n * D + hp * ACC_COLS + dd] * wscale;
+            *reinterpret_cast<__half*>(B_sh + (n >> 6) * ATOM_BYTES + sw128_off(dd, n & 63)) = __float2half_rn(w);
         }
         for (int i = tid; i < TM * N; i += THREADS) {   // decay powers rho_n^r, r = 0..127
             const int r = i / N, n = i % N;
-            const float pw = exp2f((float)r * log2f(a.rhos[n]));
-            if (NK == 1) reinterpret_cast<__half*>(Rb_sh)[r * N + n] = __float2half_rn(pw); else R_sh[r * ldR + n] = pw;
+            // N = 128: the backward kernel has no room for this table and forms rho^r as rho^(16 (r / 16)) * rho^(r % 16);
+            // the same product here keeps the two kernels' state tiles identical
+            const float l2 = log2f(a.rhos[n]);
+            const float pw = NK == 1 ? exp2f((float)r * l2) : exp2f(16.0f * (float)(r >> 4) * l2) * exp2f((float)(r & 15) * l2);
+            *reinterpret_cast<__half*>(R_sh + r * RS + n * 2) = __float2half_rn(pw);
         }
         for (int i = tid; i < TM; i += THREADS) {
             const int tt = t0 + i;
             tok_sh[i] = (tt < Lb) ? (int)(a.x[(size_t)b * a.T + tt] & 0x7fffffffLL) : -1;
         }
-        if (NK == 1) {   // restart values of the tile's 128 steps: read from shared memory by the hot rows
+        if (NK == 1) {   // restart values of the tile's 128 steps: read from shared memory by the rows after an occurrence
             for (int i = tid; i < TM * (N / 4); i += THREADS) {
                 const int r = i / (N / 4), c4 = i % (N / 4);
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (t0 + r < a.T) v = __ldg(reinterpret_cast<const float4*>(a.tok_state + ((size_t)b * a.T + t0 + r) * N) + c4);
                 const float sc = STATE_F16_SCALE;                           // "+1": the occurrence itself
-                TS2_sh[2 * i] = pack_f16x2((v.x + 1.0f) * sc, (v.y + 1.0f) * sc);
-                TS2_sh[2 * i + 1] = pack_f16x2((v.z + 1.0f) * sc, (v.w + 1.0f) * sc);
+                reinterpret_cast<uint32_t*>(TS_sh)[2 * i] = pack_f16x2((v.x + 1.0f) * sc, (v.y + 1.0f) * sc);
+                reinterpret_cast<uint32_t*>(TS_sh)[2 * i + 1] = pack_f16x2((v.z + 1.0f) * sc, (v.w + 1.0f) * sc);
             }
         }
+        for (int i = tid; i < NE * 2 * ACC_COLS / 2; i += THREADS) reinterpret_cast<uint32_t*>(E2_sh)[i] = 0u;
     }
     fence_proxy_async_smem();
     tc_fence_before_sync();
@@ -205,160 +220,143 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
     __syncthreads();
 
     if (!is_epi) {
-        // ============================================================ producer warpgroup: one thread per time step
+        // ============================================================ producer warps: slot i belongs to warp i % 4
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
-        const uint32_t idesc = umma_idesc_16(TM, ACC_COLS, 0, 0, NK == 1 ? 0 : 1, NK == 1 ? 0 : 1);   // N = 64: fp16 operands
-        const uint32_t a_base = smem_u32(A_sh), b_base = smem_u32(B_sh);
-        const int wi = row >> 5, bi = row & 31;
+        const int pw = warp - EPI_WARPS;
+        const uint32_t idesc = umma_idesc_16(TM, ACC_COLS, 0, 0, 0, 0);          // fp16 operands, fp32 accumulation
+        const uint32_t a_base = smem_u32(A_sh) + pw * NK * ATOM_BYTES, b_base = smem_u32(B_sh);
+        constexpr int CH = N / 8;                   // 16-byte chunks per tile row
+        constexpr int RPP = 32 / CH;                // tile rows the warp writes per pass
+        constexpr int RB = 8;                       // passes whose loads are issued together
+        const int cc = lane % CH, r0 = lane / CH;   // this lane's chunk column and first row
         const int esize = (a.e_dt == MBEMA_F32) ? 4 : 2;
-        const int s_chunks = N / 8, e_chunks = ACC_COLS * esize / 16;     // 16-byte chunks per row (bf16 snapshot; raw E)
-        const __nv_bfloat16* snap16 = reinterpret_cast<const __nv_bfloat16*>(a.tile_state + (size_t)a.B * a.nT * a.K * N);
-        // Asynchronous prefetch of slot j's snapshot row and raw E_k / E_v rows into ring stage j % RING.
-        // E row of the next slot to prefetch (tables shared between samples: one index load per slot, a slot ahead)
-        size_t erow_next = (ROWS && n_slots > 0) ? (size_t)a.erow[(size_t)b * a.K + slot_sh[0]] : 0;
-        auto prefetch = [&](int j) {
-            if (j < n_slots && row < s_chunks + 2 * e_chunks) {   // threads without a chunk to copy skip the address arithmetic too
-                const int k = slot_sh[j];
+        const int s_chunks = N / 8, e_chunks = ACC_COLS * esize / 16;     // 16-byte chunks per row (fp16 snapshot; raw E)
+        const __half* snap16 = reinterpret_cast<const __half*>(a.tile_state + (size_t)a.B * a.nT * a.K * N);
+        unsigned char* ring_w = ring_sh + pw * RW * RING_STAGE_BYTES;
+        unsigned char* At = A_sh + pw * NK * ATOM_BYTES + (cc >> 3) * ATOM_BYTES;     // this warp's stage, this lane's atom
+        const int c8 = cc & 7;
+        const unsigned char* Rc = R_sh + cc * 16;
+        // Asynchronous prefetch of slot i's snapshot row and raw E_k / E_v rows into this warp's ring stage `rs`.
+        // E row of the next slot to prefetch (tables shared between samples): loaded one iteration ahead
+        size_t erow_next = (ROWS && pw < n_slots) ? (size_t)a.erow[(size_t)b * a.K + slot_sh[pw]] : 0;
+        auto prefetch = [&](int i, int rs) {
+            if (i < n_slots) {
+                const int k = slot_sh[i];
                 const size_t er = ROWS ? erow_next : (size_t)b * a.K + k;
-                if (ROWS && j + 1 < n_slots) erow_next = (size_t)a.erow[(size_t)b * a.K + slot_sh[j + 1]];
-                unsigned char* dst = ring_sh + (j % RING) * RING_STAGE_BYTES;
+                if (ROWS && i + PROD_WARPS < n_slots) erow_next = (size_t)a.erow[(size_t)b * a.K + slot_sh[i + PROD_WARPS]];
+                unsigned char* dst = ring_w + rs * RING_STAGE_BYTES;
                 const unsigned char* srcS = reinterpret_cast<const unsigned char*>(snap16 + (((size_t)b * a.nT + tile) * a.K + k) * N);
                 const size_t eoff = (er * D + hp * ACC_COLS) * esize;
                 const unsigned char* srcK = reinterpret_cast<const unsigned char*>(a.Ek) + eoff;
                 const unsigned char* srcV = reinterpret_cast<const unsigned char*>(a.Ev) + eoff;
-                for (int c = row; c < s_chunks + 2 * e_chunks; c += PROD_THREADS) {
+                for (int c = lane; c < s_chunks + 2 * e_chunks; c += 32) {
                     const unsigned char* src;
                     unsigned char* d;
                     if (c < s_chunks) { src = srcS + c * 16; d = dst + c * 16; }
-                    else if (c < s_chunks + e_chunks) { src = srcK + (c - s_chunks) * 16; d = dst + 512 + (c - s_chunks) * 16; }
-                    else { src = srcV + (c - s_chunks - e_chunks) * 16; d = dst + 512 + ACC_COLS * 4 + (c - s_chunks - e_chunks) * 16; }
+                    else if (c < s_chunks + e_chunks) { src = srcK + (c - s_chunks) * 16; d = dst + 256 + (c - s_chunks) * 16; }
+                    else { src = srcV + (c - s_chunks - e_chunks) * 16; d = dst + 256 + ACC_COLS * 4 + (c - s_chunks - e_chunks) * 16; }
                     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(d)), "l"(src) : "memory");
                 }
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        // this row's decay powers as packed bf16 pairs (register-resident when N == 64)
-        uint32_t R2[NK == 1 ? 32 : 1];
-        if (NK == 1) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) R2[j] = *reinterpret_cast<const uint32_t*>(Rb_sh + row * N + 2 * j);
-        }
-        for (int j = 0; j < PD; ++j) prefetch(j);
-        asm volatile("cp.async.wait_group %0;" ::"n"(PD - 1) : "memory");
-        named_bar_sync(1, PROD_THREADS);                // slot 0's rows are visible to the whole warpgroup
-        for (int i = 0; i < n_slots; ++i) {
-            const int st = i % NSTAGE, u = i / NSTAGE;
-            prefetch(i + PD);
-            asm volatile("cp.async.wait_group %0;" ::"n"(PD - 1) : "memory");   // this thread's copies for slot i+1 landed
-            // stage st (A tile, E rows, accumulators) is free once the epilogue of slot i - NSTAGE has finished
-            if (i >= NSTAGE) mbar_wait(&bars->acc_empty[st], (uint32_t)((u - 1) & 1), abort_flag);
+        for (int j = 0; j < PDW; ++j) prefetch(pw + PROD_WARPS * j, j);
+        for (int i = pw, it = 0; i < n_slots; i += PROD_WARPS, ++it) {
+            prefetch(i + PROD_WARPS * PDW, (it + PDW) % RW);
+            asm volatile("cp.async.wait_group %0;" ::"n"(PDW) : "memory");   // this lane's copies for slot i have landed
+            __syncwarp();                                                       // ... and so have the other lanes'
+            // this warp's stage (A tile, accumulators) is free once the epilogue has read slot i - NSTAGE; by then the
+            // epilogue is also done with the E rows of slot i - NE, whose stage the rows of slot i take
+            if (it >= 1 && !mbar_wait(&bars->acc_empty[pw], (uint32_t)((it - 1) & 1), abort_flag, 1)) break;
             const int keyf = key_sh[i];
-            const int key = keyf & 0x7fffffff;
-            const unsigned char* rg = ring_sh + (i % RING) * RING_STAGE_BYTES;
-            // E_k / E_v rows of the slot for the head pair, as fp32: thread p converts column p of both
+            const unsigned char* rg = ring_w + (it % RW) * RING_STAGE_BYTES;
+            // E_k / E_v rows of the slot for the head pair, as fp16 (saturated): lane l converts columns 4l .. 4l+3 of both
             {
-                float* dst = E_sh + st * 2 * ACC_COLS + row;
+                uint2* dst = reinterpret_cast<uint2*>(E2_sh + (i % NE) * 2 * ACC_COLS) + lane;
+                float4 fk, fv;
                 if (esize == 4) {
-                    dst[0] = reinterpret_cast<const float*>(rg + 512)[row];
-                    dst[ACC_COLS] = reinterpret_cast<const float*>(rg + 512 + ACC_COLS * 4)[row];
+                    fk = reinterpret_cast<const float4*>(rg + 256)[lane];
+                    fv = reinterpret_cast<const float4*>(rg + 256 + ACC_COLS * 4)[lane];
                 } else {
-                    dst[0] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rg + 512)[row]);
-                    dst[ACC_COLS] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rg + 512 + ACC_COLS * 4)[row]);
+                    const uint2 rk = reinterpret_cast<const uint2*>(rg + 256)[lane];
+                    const uint2 rv = reinterpret_cast<const uint2*>(rg + 256 + ACC_COLS * 4)[lane];
+                    fk = make_float4(bf16_lo(rk.x), bf16_hi(rk.x), bf16_lo(rk.y), bf16_hi(rk.y));
+                    fv = make_float4(bf16_lo(rv.x), bf16_hi(rv.x), bf16_lo(rv.y), bf16_hi(rv.y));
                 }
+                dst[0] = make_uint2(pack_f16x2_sat(fk.x, fk.y), pack_f16x2_sat(fk.z, fk.w));
+                dst[ACC_COLS / 4] = make_uint2(pack_f16x2_sat(fv.x, fv.y), pack_f16x2_sat(fv.z, fv.w));
             }
-            // last occurrence of the slot's token strictly before this row, inside the tile
-            int s = -1;
-            if (keyf < 0) {
-                unsigned w[4];
+            // The state tile: lane (cc, r0) writes chunk cc of rows r0, r0 + RPP, ...  The loads of RB passes are issued
+            // together: the compiler cannot move a shared-memory load above an earlier shared-memory store (it cannot tell
+            // the buffers apart), so a load-multiply-store loop would run as one load latency per pass.
+            const uint4 sv = *reinterpret_cast<const uint4*>(rg + cc * 16);
+            if (keyf >= 0) {
+                // no occurrence of the slot's token in the tile: snapshot times decay power, one packed product per pair
+                for (int rb = r0; rb < TM; rb += RPP * RB) {
+                    uint4 rv[RB];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) w[j] = __ballot_sync(0xffffffffu, tok_sh[32 * j + lane] == key);
+                    for (int j = 0; j < RB; ++j) rv[j] = *reinterpret_cast<const uint4*>(Rc + (rb + j * RPP) * RS);
 #pragma unroll
-                for (int j = 3; j >= 0; --j) {
-                    unsigned mm = (j > wi) ? 0u : (j == wi ? (w[j] & ((1u << bi) - 1u)) : w[j]);
-                    if (s < 0 && mm) s = j * 32 + 31 - __clz(mm);
-                }
-            }
-            unsigned char* Arow = A_sh + st * NK * ATOM_BYTES + row * 128;
-            if (s >= 0) {   // restart from the token's own state at that occurrence (+1 for the occurrence itself)
-                if (NK == 1) {   // bf16 restart value x bf16 power, rounded once more by the packed multiply; the
-                                 // backward rebuilds the same tiles with the same operations
-                    const uint32_t* tsr = TS2_sh + s * (N / 2);
-                    const uint32_t* rr = reinterpret_cast<const uint32_t*>(Rb_sh + (row - s) * N);
-#pragma unroll
-                    for (int cc = 0; cc < 8; ++cc) {
-                        const uint4 tv = *reinterpret_cast<const uint4*>(tsr + 4 * cc);
-                        const uint4 rv = *reinterpret_cast<const uint4*>(rr + 4 * cc);
-                        uint4 pk;
-                        pk.x = mul_f16x2(tv.x, rv.x);
-                        pk.y = mul_f16x2(tv.y, rv.y);
-                        pk.z = mul_f16x2(tv.z, rv.z);
-                        pk.w = mul_f16x2(tv.w, rv.w);
-                        *reinterpret_cast<uint4*>(Arow + (((cc & 7) ^ (row & 7)) << 4)) = pk;
-                    }
-                } else {
-                    const float* base = a.tok_state + ((size_t)b * a.T + t0 + s) * N;
-                    const float* Rrow = R_sh + (row - s) * ldR;
-#pragma unroll 2
-                    for (int cc = 0; cc < N / 8; ++cc) {
-                        const int n0 = cc * 8;
-                        const float4 b0 = __ldg(reinterpret_cast<const float4*>(base + n0));
-                        const float4 b1 = __ldg(reinterpret_cast<const float4*>(base + n0 + 4));
-                        const float4 r0 = *reinterpret_cast<const float4*>(Rrow + n0);
-                        const float4 r1 = *reinterpret_cast<const float4*>(Rrow + n0 + 4);
-                        uint4 pk;
-                        pk.x = pack_bf16x2(fmaf(b0.x, r0.x, r0.x), fmaf(b0.y, r0.y, r0.y));
-                        pk.y = pack_bf16x2(fmaf(b0.z, r0.z, r0.z), fmaf(b0.w, r0.w, r0.w));
-                        pk.z = pack_bf16x2(fmaf(b1.x, r1.x, r1.x), fmaf(b1.y, r1.y, r1.y));
-                        pk.w = pack_bf16x2(fmaf(b1.z, r1.z, r1.z), fmaf(b1.w, r1.w, r1.w));
-                        *reinterpret_cast<uint4*>(Arow + (cc >> 3) * ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) = pk;
+                    for (int j = 0; j < RB; ++j) {
+                        const int r = rb + j * RPP;
+                        *reinterpret_cast<uint4*>(At + r * 128 + ((c8 ^ (r & 7)) << 4)) = mul4_f16x2(sv, rv[j]);
                     }
                 }
-            } else {        // plain decay of the tile-start snapshot: bf16 snapshot (prefetched, broadcast reads) times
-                            // this row's decay powers; product rounded to bf16 by the packed multiply
-                if (NK == 1) {
+            } else {
+                // rows after an occurrence at step s restart from (tok_state[s] + 1) * rho^(r - s)
+                const int key = keyf & 0x7fffffff;
+                unsigned occ[4];
 #pragma unroll
-                    for (int cc = 0; cc < 8; ++cc) {
-                        const uint4 sv = *reinterpret_cast<const uint4*>(rg + cc * 16);
-                        uint4 pk;
-                        pk.x = mul_f16x2(sv.x, R2[4 * cc]);
-                        pk.y = mul_f16x2(sv.y, R2[4 * cc + 1]);
-                        pk.z = mul_f16x2(sv.z, R2[4 * cc + 2]);
-                        pk.w = mul_f16x2(sv.w, R2[4 * cc + 3]);
-                        *reinterpret_cast<uint4*>(Arow + (((cc & 7) ^ (row & 7)) << 4)) = pk;
+                for (int j = 0; j < 4; ++j) occ[j] = __ballot_sync(0xffffffffu, tok_sh[32 * j + lane] == key);
+                int s_have = -1;
+                uint4 tv = make_uint4(0u, 0u, 0u, 0u);
+                for (int r = r0; r < TM; r += RPP) {
+                    const int wi = r >> 5, bi = r & 31;
+                    int s = -1;
+#pragma unroll
+                    for (int j = 3; j >= 0; --j) {
+                        const unsigned mm = (j > wi) ? 0u : (j == wi ? (occ[j] & ((1u << bi) - 1u)) : occ[j]);
+                        if (s < 0 && mm) s = j * 32 + 31 - __clz(mm);
                     }
-                } else {
-                    const float* Rrow = R_sh + row * ldR;
-#pragma unroll 2
-                    for (int cc = 0; cc < N / 8; ++cc) {
-                        const int n0 = cc * 8;
-                        const uint4 sv = *reinterpret_cast<const uint4*>(rg + cc * 16);
-                        const float4 r0 = *reinterpret_cast<const float4*>(Rrow + n0);
-                        const float4 r1 = *reinterpret_cast<const float4*>(Rrow + n0 + 4);
-                        uint4 pk;
-                        pk.x = pack_bf16x2(bf16_lo(sv.x) * r0.x, bf16_hi(sv.x) * r0.y);
-                        pk.y = pack_bf16x2(bf16_lo(sv.y) * r0.z, bf16_hi(sv.y) * r0.w);
-                        pk.z = pack_bf16x2(bf16_lo(sv.z) * r1.x, bf16_hi(sv.z) * r1.y);
-                        pk.w = pack_bf16x2(bf16_lo(sv.w) * r1.z, bf16_hi(sv.w) * r1.w);
-                        *reinterpret_cast<uint4*>(Arow + (cc >> 3) * ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) = pk;
+                    uint4 base = sv;
+                    int rr = r;
+                    if (s >= 0) {
+                        if (s != s_have) {
+                            if (NK == 1) {
+                                tv = *reinterpret_cast<const uint4*>(TS_sh + s * 128 + cc * 16);
+                            } else {
+                                const float* src = a.tok_state + ((size_t)b * a.T + t0 + s) * N + cc * 8;
+                                const float4 b0 = __ldg(reinterpret_cast<const float4*>(src));
+                                const float4 b1 = __ldg(reinterpret_cast<const float4*>(src + 4));
+                                const float sc = STATE_F16_SCALE;
+                                tv = make_uint4(pack_f16x2((b0.x + 1.0f) * sc, (b0.y + 1.0f) * sc), pack_f16x2((b0.z + 1.0f) * sc, (b0.w + 1.0f) * sc),
+                                                pack_f16x2((b1.x + 1.0f) * sc, (b1.y + 1.0f) * sc), pack_f16x2((b1.z + 1.0f) * sc, (b1.w + 1.0f) * sc));
+                            }
+                            s_have = s;
+                        }
+                        base = tv;
+                        rr = r - s;
                     }
+                    const uint4 rv = *reinterpret_cast<const uint4*>(Rc + rr * RS);
+                    *reinterpret_cast<uint4*>(At + r * 128 + ((c8 ^ (r & 7)) << 4)) = mul4_f16x2(base, rv);
                 }
             }
             fence_proxy_async_smem();
-            named_bar_sync(1, PROD_THREADS);          // the whole tile and both E rows are in shared memory
-            if (warp == EPI_WARPS + (i & 3) && lane == 0) {   // one thread issues the UMMAs of this slot (the role rotates)
+            __syncwarp();          // the whole tile and both E rows are in shared memory
+            if (lane == 0) {
                 tc_fence_after_sync();
-                for (int atom = 0; atom < NK; ++atom) {
 #pragma unroll
-                    for (int k16 = 0; k16 < 4; ++k16) {
-                        const uint64_t adesc = umma_desc_k_sw128(a_base + (st * NK + atom) * ATOM_BYTES + k16 * 32);
-                        const uint64_t bdesc = umma_desc_k_sw128(b_base + atom * ATOM_BYTES + k16 * 32);
-                        umma_bf16_ss(tmem_base + (uint32_t)(st * ACC_COLS), adesc, bdesc, idesc, (atom | k16) != 0 ? 1u : 0u);
-                    }
+                for (int k16 = 0; k16 < 4 * NK; ++k16) {     // contraction over n, 16 per instruction, 64 per swizzle atom
+                    const int off = (k16 >> 2) * ATOM_BYTES + (k16 & 3) * 32;
+                    umma_bf16_ss(tmem_base + (uint32_t)(pw * ACC_COLS), umma_desc_k_sw128(a_base + off), umma_desc_k_sw128(b_base + off),
+                                 idesc, k16 != 0 ? 1u : 0u);
                 }
-                umma_commit(&bars->acc_full[st]);   // first arrival: the UMMAs above have completed
-                mbar_arrive(&bars->acc_full[st]);   // second arrival: releases the staged E rows
+                umma_commit(&bars->acc_full[pw]);   // first arrival: the UMMAs above have completed
+                mbar_arrive(&bars->acc_full[pw]);   // second arrival: releases the staged E rows
             }
         }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (lane == 0) umma_commit(&bars->drain);   // arrives once every UMMA this lane issued has completed
     } else {
         // ============================================================ epilogue warpgroups: a thread per time step, a head per warpgroup
         asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
@@ -366,67 +364,102 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
         const int h = hp * HPC + wg;
         const size_t qoff = (((size_t)b * a.H + h) * a.T + t) * HD;
         const bool row_ok = t < Lb;
-        float q[HD], o[HD];
+        // q / sqrt(hd) and the gate of the previous slot as packed fp16 pairs; the output row in fp32
+        uint32_t q2[HD / 2], g_old[HD / 2];
+        float o[HD];
 #pragma unroll
         for (int i = 0; i < HD; i += 4) {
             float4 v = row_ok ? ld4_dyn_f32(a.Q, a.q_dt, qoff + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-            q[i] = v.x * 0.125f; q[i + 1] = v.y * 0.125f; q[i + 2] = v.z * 0.125f; q[i + 3] = v.w * 0.125f;
+            q2[i / 2] = pack_f16x2_sat(v.x * 0.125f, v.y * 0.125f);
+            q2[i / 2 + 1] = pack_f16x2_sat(v.z * 0.125f, v.w * 0.125f);
+            g_old[i / 2] = g_old[i / 2 + 1] = 0u;
             o[i] = o[i + 1] = o[i + 2] = o[i + 3] = 0.f;
         }
         const float rest = a.v_total - (float)a.kcount[b];
         float m, l;
         if (!a.listed_only && rest > 0.f) { m = 0.f; l = rest; } else { m = -INFINITY; l = 0.f; }
         const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(wg * HD);
-
-        for (int i = 0; i < n_slots; ++i) {
-            const int st = i % NSTAGE, u = i / NSTAGE;
-            mbar_wait(&bars->acc_full[st], (uint32_t)(u & 1), abort_flag);
-            tc_fence_after_sync();
-            float pre[HD];
-            tmem_ld_32x32b_x32(t_lane + st * ACC_COLS, pre);
-            tmem_ld_32x32b_x32(t_lane + st * ACC_COLS + 32, pre + 32);
-            tmem_wait_ld();
-
-            const float* ek = E_sh + st * 2 * ACC_COLS + wg * HD;
-            const float* ev = ek + ACC_COLS;
-            float sp[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int j = 0; j < HD; j += 4) {
-                const float4 e = *reinterpret_cast<const float4*>(ek + j);
-                const float ee[4] = {e.x, e.y, e.z, e.w};
-#pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                    const float hh = pre[j + v];
-                    const float g = SILU ? fmaf(hh, tanh_approx(hh), hh) : hh;
-                    pre[j + v] = g;
-                    sp[v] = fmaf(g * q[j + v], ee[v], sp[v]);
-                }
-            }
-            const float s = (sp[0] + sp[1]) + (sp[2] + sp[3]);
-            const float m_new = fmaxf(m, s);
-            if (m_new > m) {
-                const float alpha = __expf(m - m_new);
+        // In iteration i a thread
+        //   (1) starts the TMEM load of slot i's accumulators,
+        //   (2) under that load, finishes slot i - 1: updates the lazy softmax reference with score(i-1), gets p(i-1),
+        //   (3) walks its 64 columns once, doing per pair of columns
+        //         O += p(i-1) * (E_v(i-1) * gate(i-1))                                    P.V, one slot behind
+        //         gate(i) = SiLU(pre) = h + h * tanh(h), h = pre (W_pe carries the 1/2)    overwrites gate(i-1)
+        //         score(i) += gate(i) * (q * E_k(i))                                       16 columns in fp16, then fp32
+        // The reference maximum only moves when a score exceeds it by more than LAZY_MAX (the probabilities stay below
+        // e^LAZY_MAX, well inside fp16), so rescaling the output row is rare.
+        float s_prev = 0.f;                     // score(i-1)
+        bool alive = true;
+        // (2): softmax bookkeeping of a finished slot with score s; returns its probability in both fp16 halves
+        auto finish_slot = [&](float s) -> uint32_t {
+            if (s > m + LAZY_MAX) {
+                const float alpha = __expf(m - s);     // m = -inf at the start: alpha = 0
                 l *= alpha;
 #pragma unroll
                 for (int j = 0; j < HD; ++j) o[j] *= alpha;
-                m = m_new;
+                m = s;
             }
             const float p = __expf(s - m);
             l += p;
+            return pack_f16x2(p, p);
+        };
+        for (int i = 0; i < n_slots; ++i) {
+            const int st = i % NSTAGE, u = i / NSTAGE;
+            alive = mbar_wait(&bars->acc_full[st], (uint32_t)(u & 1), abort_flag, 2);
+            if (!alive) break;
+            tc_fence_after_sync();
+            const uint32_t t_acc = t_lane + st * ACC_COLS;
+            float pre[2][16];
+            tmem_ld_32x32b_x16(t_acc, pre[0]);
+            const uint32_t p2 = (i >= 1) ? finish_slot(s_prev) : 0u;
+            // (3)
+            const uint32_t* ek2 = reinterpret_cast<const uint32_t*>(E2_sh + (i % NE) * 2 * ACC_COLS + wg * HD);
+            const uint32_t* ev2 = reinterpret_cast<const uint32_t*>(E2_sh + ((i + NE - 1) % NE) * 2 * ACC_COLS + ACC_COLS + wg * HD);
+            float sp0 = 0.f, sp1 = 0.f;
 #pragma unroll
-            for (int j = 0; j < HD; j += 4) {
-                const float4 e = *reinterpret_cast<const float4*>(ev + j);
-                o[j] = fmaf(p * pre[j], e.x, o[j]);
-                o[j + 1] = fmaf(p * pre[j + 1], e.y, o[j + 1]);
-                o[j + 2] = fmaf(p * pre[j + 2], e.z, o[j + 2]);
-                o[j + 3] = fmaf(p * pre[j + 3], e.w, o[j + 3]);
+            for (int c = 0; c < HD / 16; ++c) {      // 16 accumulator columns (8 pairs) per TMEM load, the next load in flight
+                tmem_wait_ld();
+                if (c + 1 < HD / 16) tmem_ld_32x32b_x16(t_acc + (c + 1) * 16, pre[(c + 1) & 1]);
+                const uint4 ekA = *reinterpret_cast<const uint4*>(ek2 + c * 8), ekB = *reinterpret_cast<const uint4*>(ek2 + c * 8 + 4);
+                const uint4 evA = *reinterpret_cast<const uint4*>(ev2 + c * 8), evB = *reinterpret_cast<const uint4*>(ev2 + c * 8 + 4);
+                const uint32_t ekw[8] = {ekA.x, ekA.y, ekA.z, ekA.w, ekB.x, ekB.y, ekB.z, ekB.w};
+                const uint32_t evw[8] = {evA.x, evA.y, evA.z, evA.w, evB.x, evB.y, evB.z, evB.w};
+                uint32_t sa0 = 0u, sa1 = 0u;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int w = c * 8 + j;
+                    fma_f32_f16x2(o[2 * w], o[2 * w + 1], mul_f16x2(g_old[w], evw[j]), p2);
+                    const float h0 = pre[c & 1][2 * j], h1 = pre[c & 1][2 * j + 1];
+                    const float g0 = SILU ? fmaf(h0, tanh_approx(h0), h0) : h0;
+                    const float g1 = SILU ? fmaf(h1, tanh_approx(h1), h1) : h1;
+                    const uint32_t gg = pack_f16x2(g0, g1);
+                    g_old[w] = gg;
+                    const uint32_t qe = mul_f16x2(q2[w], ekw[j]);
+                    if (j & 1) sa1 = fma_f16x2(gg, qe, sa1); else sa0 = fma_f16x2(gg, qe, sa0);
+                }
+                const float2 f0 = unpack_f16x2(sa0), f1 = unpack_f16x2(sa1);
+                sp0 += f0.x + f0.y;
+                sp1 += f1.x + f1.y;
             }
-            // accumulators and E rows of this stage are consumed
+            // the stage's accumulators are consumed (its E rows live in their own, deeper ring)
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->acc_empty[st]);
+            s_prev = sp0 + sp1;
         }
-        if (t < a.T) {
+        if (alive && n_slots > 0) {
+            // the last slot: its softmax bookkeeping and P.V update
+            const uint32_t p2 = finish_slot(s_prev);
+            const uint32_t* ev2 = reinterpret_cast<const uint32_t*>(E2_sh + ((n_slots - 1) % NE) * 2 * ACC_COLS + ACC_COLS + wg * HD);
+#pragma unroll
+            for (int w4 = 0; w4 < HD / 2; w4 += 4) {
+                const uint4 evp = *reinterpret_cast<const uint4*>(ev2 + w4);
+                const uint32_t evw[4] = {evp.x, evp.y, evp.z, evp.w};
+#pragma unroll
+                for (int pr = 0; pr < 4; ++pr) fma_f32_f16x2(o[2 * (w4 + pr)], o[2 * (w4 + pr) + 1], mul_f16x2(g_old[w4 + pr], evw[pr]), p2);
+            }
+        }
+        if (alive && t < a.T) {
             const float inv = (row_ok && l > 0.f) ? 1.0f / l : 0.f;
 #pragma unroll
             for (int i = 0; i < HD; i += 4)
@@ -438,15 +471,18 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
     tc_fence_before_sync();
     __syncthreads();
     if (warp == EPI_WARPS) {
+        mbar_wait<100>(&bars->drain, 0u, &bars->drain_flag, 3);   // bounded: no UMMA of this CTA is in flight when TMEM is released
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, TMEM_COLS);
     }
-    if (tid == 0 && bars->abort_flag) atomicExch(status, 1);   // sticky: later CTAs of this launch skip their work
+    if (tid == 0 && (bars->abort_flag | bars->drain_flag)) atomicOr(status, bars->abort_flag | bars->drain_flag);   // sticky: later CTAs of this launch skip their work
 }
 
 }  // namespace tc
 
-bool flash_tc_supported(int H, int N, int K) { return (H % tc::HPC) == 0 && (N == 64 || N == 128) && K <= tc::MAX_SLOTS; }
+bool flash_tc_supported(int H, int N, int K) {
+    return (H % tc::HPC) == 0 && (N == 64 || N == 128) && K <= tc::MAX_SLOTS && tc::smem_layout(N, K).total <= 227 * 1024;
+}
 
 size_t flash_fwd_tc_ws() { return 256; }
 
@@ -454,7 +490,6 @@ int flash_fwd_tc(const FlashArgs& a, void* ws, cudaStream_t st) {
     int* status = reinterpret_cast<int*>((reinterpret_cast<uintptr_t>(ws) + 15) & ~uintptr_t(15));
     MBEMA_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), st));
     const tc::Smem L = tc::smem_layout(a.N, a.K);
-    if (L.total > 227 * 1024) return MBEMA_ERR_UNSUPPORTED;
     dim3 grid(a.nT, a.H / tc::HPC, a.B);
 #define MBEMA_LAUNCH_FWD(S_, NK_, R_)                                                                                     \
     do {                                                                                                             \

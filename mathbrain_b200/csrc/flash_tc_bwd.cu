@@ -105,7 +105,9 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
     constexpr int COL_DW = Cfg<NK>::COL_DW, COL_DEK = Cfg<NK>::COL_DEK, COL_DEV = Cfg<NK>::COL_DEV, COL_DQ = Cfg<NK>::COL_DQ;
     constexpr int STAGE_BYTES = 2 * ATOM_BYTES;
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // 1024-byte alignment for the swizzled operand tiles; the offset is added to the __shared__ array itself so that the
+    // compiler keeps addressing shared memory directly (a pointer rebuilt from an integer would turn every access generic)
+    unsigned char* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const Smem L = smem_layout(a.K, NK);
     unsigned char* A_sh = sm + L.a_off;
     unsigned char* B_sh = sm + L.b_off;
@@ -181,8 +183,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             const int n = i / ACC_COLS, dd = i % ACC_COLS;
             const float w = a.W[(size_t)n * D + hp * ACC_COLS + dd] * wscale;
             unsigned char* dstw = B_sh + (n >> 6) * ATOM_BYTES + sw128_off(dd, n & 63);
-            if (NK == 1) *reinterpret_cast<__half*>(dstw) = __float2half_rn(w * STATE_F16_UNSCALE);   // the state operand carries 1/64
-            else *reinterpret_cast<__nv_bfloat16*>(dstw) = __float2bfloat16(w);
+            *reinterpret_cast<__half*>(dstw) = __float2half_rn(w * STATE_F16_UNSCALE);   // the state operand carries 1/64
         }
         if (NK == 1) {
             for (int i = tid; i < TM * N; i += THREADS) {
@@ -228,8 +229,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
         // bf16 operands moved the pre-activations of slots with states in the hundreds by ~0.1.  The dW product needs the
         // tile in the format of dpre (bf16; its gradients do not fit fp16's range), so the producer stores a bf16 copy
         // of the tile behind the fp16 one.
-        const int sfmt = NK == 1 ? 0 : 1;
-        const uint32_t idesc_gate = umma_idesc_16(TM, ACC_COLS, 0, 0, sfmt, sfmt);      // A, B K-major
+        const uint32_t idesc_gate = umma_idesc_16(TM, ACC_COLS, 0, 0, 0, 0);            // A, B K-major, fp16
         const uint32_t idesc_dw = umma_idesc_16(ACC_COLS, N, 1, 1, 1, 1);               // A = dpre (MN-major), B = bf16 state tile (MN-major)
         const uint32_t idesc_de = umma_idesc_bf16(ACC_COLS, 16, 1, 0);        // A = Z tile (MN-major), B = ones (K-major)
         const uint32_t a_base = smem_u32(A_sh), b_base = smem_u32(B_sh), z_base = smem_u32(Z_sh), o_base = smem_u32(ones_sh);
@@ -290,23 +290,33 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                 umma_commit(&bars->z_done);
             }
         };
-        // decay powers rho^r for 8 consecutive channels starting at n0 (r = steps since the reference state), as fp32
-        // values: bf16-exact for NK = 1 (see the table comment), full fp32 for NK = 2
+        // NK = 2: decay powers rho^r for 8 consecutive channels starting at n0 (r = steps since the reference state) from the
+        // two-level fp32 table; the forward kernel fills its fp16 table with the same products, so both build the same tiles
         auto decay8 = [&](int r, int n0, float* out) {
-            if (NK == 1) {
-                const uint4 x = *reinterpret_cast<const uint4*>(Rb_sh + r * N + n0);
-                out[0] = bf16_lo(x.x); out[1] = bf16_hi(x.x); out[2] = bf16_lo(x.y); out[3] = bf16_hi(x.y);
-                out[4] = bf16_lo(x.z); out[5] = bf16_hi(x.z); out[6] = bf16_lo(x.w); out[7] = bf16_hi(x.w);
-            } else {
-                const float* hi = R_sh + (r >> 4) * N + n0;
-                const float* lo = R_sh + (8 + (r & 15)) * N + n0;
-                const float4 h0 = *reinterpret_cast<const float4*>(hi), h1 = *reinterpret_cast<const float4*>(hi + 4);
-                const float4 l0 = *reinterpret_cast<const float4*>(lo), l1 = *reinterpret_cast<const float4*>(lo + 4);
-                out[0] = h0.x * l0.x; out[1] = h0.y * l0.y; out[2] = h0.z * l0.z; out[3] = h0.w * l0.w;
-                out[4] = h1.x * l1.x; out[5] = h1.y * l1.y; out[6] = h1.z * l1.z; out[7] = h1.w * l1.w;
+            const float* hi = R_sh + (r >> 4) * N + n0;
+            const float* lo = R_sh + (8 + (r & 15)) * N + n0;
+            const float4 h0 = *reinterpret_cast<const float4*>(hi), h1 = *reinterpret_cast<const float4*>(hi + 4);
+            const float4 l0 = *reinterpret_cast<const float4*>(lo), l1 = *reinterpret_cast<const float4*>(lo + 4);
+            out[0] = h0.x * l0.x; out[1] = h0.y * l0.y; out[2] = h0.z * l0.z; out[3] = h0.w * l0.w;
+            out[4] = h1.x * l1.x; out[5] = h1.y * l1.y; out[6] = h1.z * l1.z; out[7] = h1.w * l1.w;
+        };
+        // NK = 2: the dW product needs the state tile in bf16 (the format of dpre), and shared memory has no room for a
+        // second copy: once the gate product of slot j has been consumed, every producer thread converts its row of the
+        // fp16 tile to bf16 in place
+        auto convert_tile_inplace = [&](int j) {
+            unsigned char* r0p = A_sh + (j % NA) * STAGE_BYTES + row * 128;
+#pragma unroll
+            for (int hb = 0; hb < 2; ++hb) {       // loads first: a load cannot be moved above an earlier shared-memory store
+                uint4 v[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const uint4*>(r0p + hb * ATOM_BYTES + c * 16);
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    *reinterpret_cast<uint4*>(r0p + hb * ATOM_BYTES + c * 16) =
+                        make_uint4(f16x2_to_bf16x2(v[c].x), f16x2_to_bf16x2(v[c].y), f16x2_to_bf16x2(v[c].z), f16x2_to_bf16x2(v[c].w));
             }
         };
-        // NK = 1: this row's powers as packed bf16 pairs, register-resident (cold rows: packed multiply, as the forward)
+        // NK = 1: this row's powers as packed fp16 pairs, register-resident (cold rows: packed multiply, as the forward)
         uint32_t R2[NK == 1 ? 32 : 1];
         if (NK == 1) {
 #pragma unroll
@@ -353,51 +363,54 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                 for (int cc = 0; cc < N / 8; ++cc) {
                     const float4 b0 = __ldg(reinterpret_cast<const float4*>(base + cc * 8));
                     const float4 b1 = __ldg(reinterpret_cast<const float4*>(base + cc * 8 + 4));
-                    uint4 pk;
-                    if (NK == 1) {   // as the forward: bf16 restart value x bf16 power, packed multiply
-                        const uint4 rv = *reinterpret_cast<const uint4*>(Rb_sh + (row - s) * N + cc * 8);
-                        const float sc = STATE_F16_SCALE;
-                        pk.x = mul_f16x2(pack_f16x2((b0.x + 1.0f) * sc, (b0.y + 1.0f) * sc), rv.x);
-                        pk.y = mul_f16x2(pack_f16x2((b0.z + 1.0f) * sc, (b0.w + 1.0f) * sc), rv.y);
-                        pk.z = mul_f16x2(pack_f16x2((b1.x + 1.0f) * sc, (b1.y + 1.0f) * sc), rv.z);
-                        pk.w = mul_f16x2(pack_f16x2((b1.z + 1.0f) * sc, (b1.w + 1.0f) * sc), rv.w);
-                        *reinterpret_cast<uint4*>(Arow + ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) =
-                            make_uint4(f16x2_to_bf16x2(pk.x), f16x2_to_bf16x2(pk.y), f16x2_to_bf16x2(pk.z), f16x2_to_bf16x2(pk.w));
+                    const float sc = STATE_F16_SCALE;
+                    uint4 pk;     // as the forward: fp16 restart value x fp16 power, packed multiply
+                    pk.x = pack_f16x2((b0.x + 1.0f) * sc, (b0.y + 1.0f) * sc);
+                    pk.y = pack_f16x2((b0.z + 1.0f) * sc, (b0.w + 1.0f) * sc);
+                    pk.z = pack_f16x2((b1.x + 1.0f) * sc, (b1.y + 1.0f) * sc);
+                    pk.w = pack_f16x2((b1.z + 1.0f) * sc, (b1.w + 1.0f) * sc);
+                    uint4 rv;
+                    if (NK == 1) {
+                        rv = *reinterpret_cast<const uint4*>(Rb_sh + (row - s) * N + cc * 8);
                     } else {
                         float rr[8];
                         decay8(row - s, cc * 8, rr);
-                        pk.x = pack_bf16x2(fmaf(b0.x, rr[0], rr[0]), fmaf(b0.y, rr[1], rr[1]));
-                        pk.y = pack_bf16x2(fmaf(b0.z, rr[2], rr[2]), fmaf(b0.w, rr[3], rr[3]));
-                        pk.z = pack_bf16x2(fmaf(b1.x, rr[4], rr[4]), fmaf(b1.y, rr[5], rr[5]));
-                        pk.w = pack_bf16x2(fmaf(b1.z, rr[6], rr[6]), fmaf(b1.w, rr[7], rr[7]));
+                        rv = make_uint4(pack_f16x2(rr[0], rr[1]), pack_f16x2(rr[2], rr[3]), pack_f16x2(rr[4], rr[5]), pack_f16x2(rr[6], rr[7]));
                     }
+                    pk.x = mul_f16x2(pk.x, rv.x); pk.y = mul_f16x2(pk.y, rv.y); pk.z = mul_f16x2(pk.z, rv.z); pk.w = mul_f16x2(pk.w, rv.w);
+                    if (NK == 1)
+                        *reinterpret_cast<uint4*>(Arow + ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) =
+                            make_uint4(f16x2_to_bf16x2(pk.x), f16x2_to_bf16x2(pk.y), f16x2_to_bf16x2(pk.z), f16x2_to_bf16x2(pk.w));
                     *reinterpret_cast<uint4*>(Arow + (cc >> 3) * ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) = pk;
                 }
             } else {
 #pragma unroll
                 for (int cc = 0; cc < N / 8; ++cc) {
                     const uint4 sv = *reinterpret_cast<const uint4*>(rg + cc * 16);
-                    uint4 pk;
+                    uint4 rv;
                     if (NK == 1) {
-                        pk.x = mul_f16x2(sv.x, R2[(4 * cc) & 31]);
-                        pk.y = mul_f16x2(sv.y, R2[(4 * cc + 1) & 31]);
-                        pk.z = mul_f16x2(sv.z, R2[(4 * cc + 2) & 31]);
-                        pk.w = mul_f16x2(sv.w, R2[(4 * cc + 3) & 31]);
-                        *reinterpret_cast<uint4*>(Arow + ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) =
-                            make_uint4(f16x2_to_bf16x2(pk.x), f16x2_to_bf16x2(pk.y), f16x2_to_bf16x2(pk.z), f16x2_to_bf16x2(pk.w));
+                        rv = make_uint4(R2[(4 * cc) & 31], R2[(4 * cc + 1) & 31], R2[(4 * cc + 2) & 31], R2[(4 * cc + 3) & 31]);
                     } else {
                         float rr[8];
                         decay8(row, cc * 8, rr);
-                        pk.x = pack_bf16x2(bf16_lo(sv.x) * rr[0], bf16_hi(sv.x) * rr[1]);
-                        pk.y = pack_bf16x2(bf16_lo(sv.y) * rr[2], bf16_hi(sv.y) * rr[3]);
-                        pk.z = pack_bf16x2(bf16_lo(sv.z) * rr[4], bf16_hi(sv.z) * rr[5]);
-                        pk.w = pack_bf16x2(bf16_lo(sv.w) * rr[6], bf16_hi(sv.w) * rr[7]);
+                        rv = make_uint4(pack_f16x2(rr[0], rr[1]), pack_f16x2(rr[2], rr[3]), pack_f16x2(rr[4], rr[5]), pack_f16x2(rr[6], rr[7]));
                     }
+                    uint4 pk;
+                    pk.x = mul_f16x2(sv.x, rv.x); pk.y = mul_f16x2(sv.y, rv.y); pk.z = mul_f16x2(sv.z, rv.z); pk.w = mul_f16x2(sv.w, rv.w);
+                    if (NK == 1)
+                        *reinterpret_cast<uint4*>(Arow + ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) =
+                            make_uint4(f16x2_to_bf16x2(pk.x), f16x2_to_bf16x2(pk.y), f16x2_to_bf16x2(pk.z), f16x2_to_bf16x2(pk.w));
                     *reinterpret_cast<uint4*>(Arow + (cc >> 3) * ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) = pk;
                 }
             }
             fence_proxy_async_smem();
             named_bar_sync(1, PROD_THREADS);
+            if (NK == 2 && i >= 1) {   // tile i - 1: fp16 -> bf16 once the epilogue has consumed its gate product
+                mbar_wait(&bars->z_full, (uint32_t)((i - 1) & 1), abort_flag);
+                convert_tile_inplace(i - 1);
+                fence_proxy_async_smem();
+                named_bar_sync(2, PROD_THREADS);
+            }
             if (lane == 0) {
                 if (role == 0) {
                     if (i >= NACC) mbar_wait(&bars->acc_empty[sc], (uint32_t)((i / NACC - 1) & 1), abort_flag);
@@ -414,6 +427,12 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                     issue_grad_products(i - 1);
                 }
             }
+        }
+        if (NK == 2 && n_slots > 0) {
+            mbar_wait(&bars->z_full, (uint32_t)((n_slots - 1) & 1), abort_flag);
+            convert_tile_inplace(n_slots - 1);
+            fence_proxy_async_smem();
+            named_bar_sync(2, PROD_THREADS);
         }
         if (lane == 0 && role != 0 && n_slots > 0) issue_grad_products(n_slots - 1);
     } else {
@@ -597,7 +616,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                     for (int j = 0; j < 32; ++j) acc[j] = 0.f;
                 }
 #pragma unroll
-                for (int j = 0; j < 32; ++j) part_out[(size_t)(c * 32 + j) * ACC_COLS + row] = acc[j] * (NK == 1 ? STATE_F16_UNSCALE : 1.0f);
+                for (int j = 0; j < 32; ++j) part_out[(size_t)(c * 32 + j) * ACC_COLS + row] = acc[j] * STATE_F16_UNSCALE;
             }
         }
     }

@@ -231,7 +231,7 @@ k_tile_states(IndexWs w, const int64_t* __restrict__ unique, const float* __rest
     const int32_t* s_pos = w.s_pos + (size_t)b * T;
     float* out = tile_state + ((size_t)b * nT * K + k) * N;  // + tile * K * N
     // the same snapshots in 16 bits follow the fp32 block (operand format of the tensor-core attention kernels:
-    // fp16 of state / 64 when N == 64, bf16 otherwise)
+    // fp16 of state / 64)
     __nv_bfloat16* out16 = reinterpret_cast<__nv_bfloat16*>(tile_state + (size_t)gridDim.y * nT * K * N) +
                            ((size_t)b * nT * K + k) * N;
     if (kv < 0) {
@@ -293,11 +293,8 @@ k_tile_states(IndexWs w, const int64_t* __restrict__ unique, const float* __rest
                 const float pw = (s_ref == 0) ? pw_sh[tile * N + n] : (float)exp2(dt * l2r[i]);
                 const float v = u[i] * pw;
                 out[(size_t)tile * K * N + n] = v;
-                if (N == 64) {   // operand format of the N = 64 tensor-core kernels: fp16 of state / 64, saturated
-                    reinterpret_cast<__half*>(out16)[(size_t)tile * K * N + n] = __float2half_rn(fminf(v * (1.0f / 64.0f), 65504.0f));
-                } else {
-                    out16[(size_t)tile * K * N + n] = __float2bfloat16(v);
-                }
+                // operand format of the tensor-core attention kernels: fp16 of state / 64, saturated
+                reinterpret_cast<__half*>(out16)[(size_t)tile * K * N + n] = __float2half_rn(fminf(v * (1.0f / 64.0f), 65504.0f));
             }
         }
     }

@@ -25,6 +25,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// One poll: the hardware may park the thread for a short, implementation-defined time before it answers.
+// (No suspend-time hint: with a long hint the woken threads resumed late and the kernels ran slower.)
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -38,13 +40,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Bounded wait. `abort_flag` lives in shared memory; once set (by any thread) every later wait returns at once.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+// A wait that expires stores 1 | (tag << 8) there, so the status word the kernel reports names the wait that gave up.
+// SLEEP_NS > 0: the thread sleeps that long between polls.  A polling warp executes instructions, and those take issue
+// slots from the warps that have work, so warps that wait far ahead of their consumer should poll rarely.
+template <unsigned SLEEP_NS = 0>
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int tag = 0) {
     for (unsigned it = 0; it < MBEMA_SPIN_LIMIT; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if ((it & 255u) == 255u && *abort_flag) return false;
     }
-    *abort_flag = 1;
+    *abort_flag = 1 | (tag << 8);
     return false;
+}
+
+// barrier `id` (1..15) among `nthreads` threads of the CTA (a multiple of 32: whole warps)
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
 __device__ __forceinline__ void fence_barrier_init() {
@@ -148,6 +160,32 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, float* v) {
         : "memory");
 }
 
+// The two helpers below keep the compiler free to schedule unrelated arithmetic across a TMEM load and its wait: they
+// carry no memory clobber, and the wait names the loaded registers as in/out operands, which orders every use of the
+// loaded values after the wait (volatile asm statements keep their own order).
+__device__ __forceinline__ void tmem_ld16_nb(uint32_t taddr, float (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]), "=f"(v[8]),
+          "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_ld16(float (&v)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+f"(v[0]), "+f"(v[1]), "+f"(v[2]), "+f"(v[3]), "+f"(v[4]), "+f"(v[5]), "+f"(v[6]), "+f"(v[7]), "+f"(v[8]),
+                   "+f"(v[9]), "+f"(v[10]), "+f"(v[11]), "+f"(v[12]), "+f"(v[13]), "+f"(v[14]), "+f"(v[15]));
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x8(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+        : "r"(taddr)
+        : "memory");
+}
+
 __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const float* v) {
     const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
     asm volatile(
@@ -229,10 +267,41 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
     asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
     return d;
 }
+__device__ __forceinline__ float2 unpack_f16x2(uint32_t v) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&v));
+}
+// as pack_f16x2, values beyond the fp16 range become +-65504 instead of infinity
+__device__ __forceinline__ uint32_t pack_f16x2_sat(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
 __device__ __forceinline__ uint32_t mul_f16x2(uint32_t a, uint32_t b) {
     uint32_t d;
     asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
     return d;
+}
+__device__ __forceinline__ uint32_t fma_f16x2(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+// tanh of both fp16 halves (the MUFU pipe handles the pair at the rate of two scalar operations)
+__device__ __forceinline__ uint32_t tanh_f16x2(uint32_t a) {
+    uint32_t d;
+    asm("tanh.approx.f16x2 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+// a0 += x.lo * y.lo, a1 += x.hi * y.hi with fp16 factors and fp32 accumulation (mixed-precision FMA of sm_100:
+// the product of two fp16 values is exact in fp32)
+__device__ __forceinline__ void fma_f32_f16x2(float& a0, float& a1, uint32_t x, uint32_t y) {
+    asm("{\n\t.reg .b16 xl, xh, yl, yh;\n\t"
+        "mov.b32 {xl, xh}, %2;\n\t"
+        "mov.b32 {yl, yh}, %3;\n\t"
+        "fma.rn.f32.f16 %0, xl, yl, %0;\n\t"
+        "fma.rn.f32.f16 %1, xh, yh, %1;\n\t}"
+        : "+f"(a0), "+f"(a1)
+        : "r"(x), "r"(y));
 }
 // both fp16 halves converted to bf16 (through fp32, round to nearest)
 __device__ __forceinline__ uint32_t f16x2_to_bf16x2(uint32_t v) {

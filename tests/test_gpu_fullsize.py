@@ -68,7 +68,7 @@ def test_config2_full_size_layer(mb):
 
 def test_config3_full_size_layer(mb):
     """Long-chunk stress shape: B=8, T=4096, N=128, bursty repeats.  Forward against the fp32 kernels; the gradients of
-    the tensor-core backward against the fp32 backward of the same forward (dW_pe within the documented 4e-2)."""
+    the tensor-core backward against the fp32 backward of the same forward (all within 2e-2)."""
     from mathbrain_b200 import synth
     batch = synth.make_chunk_batch(31, 8, 4096, 128, bursty=True)
     K = batch["K_max"]
@@ -78,7 +78,7 @@ def test_config3_full_size_layer(mb):
     assert float((tc["O"] - mixed["O"]).abs().max()) == 0.0          # same forward kernel, deterministic
     for k in ("dQ", "dE_k", "dE_v"):
         assert rel_err(tc[k], mixed[k]) < TOL_BF16, (k, rel_err(tc[k], mixed[k]))
-    assert rel_err(tc["dW_pe"], mixed["dW_pe"]) < 4e-2
+    assert rel_err(tc["dW_pe"], mixed["dW_pe"]) < TOL_BF16
     ref = _run(mb, batch, w, "fp32", with_grad=False)
     assert rel_err(tc["O"], ref["O"]) < TOL_BF16
 

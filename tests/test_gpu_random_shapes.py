@@ -33,7 +33,7 @@ def test_tc_matches_fp32_kernels_on_random_shapes(mb, seed):
     w["dO"] = w["dO"] * (steps < batch["fill"].view(-1, 1, 1, 1)).to(w["dO"].dtype)   # padded steps are loss-masked
     tc = _run(mb, batch, w, "tc_bf16")
     ref = _run(mb, batch, w, "fp32")
-    tol = 4e-2 if N == 128 else 2e-2          # N = 128 runs bf16 gate operands (dW_pe error grows with T * K)
+    tol = 2e-2                                # fp16 gate operands for every N
     for k in ref:
         assert torch.isfinite(tc[k]).all(), k
         assert rel_err(tc[k], ref[k]) < tol, (k, rel_err(tc[k], ref[k]), dict(B=B, T=T, H=H, N=N))
