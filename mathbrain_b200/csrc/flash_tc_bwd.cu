@@ -44,8 +44,10 @@ template <int NK> struct Cfg {
     static constexpr int COL_DQ = 384;                 // dQ accumulators [128 t x (2 heads x 64)] fp32, one row per thread
 };
 static constexpr int TMEM_COLS = 512;
-static constexpr int PD = 3, RING = PD + 1;
-static constexpr int RING_STAGE_BYTES = 256 + 2 * ACC_COLS * 4;
+// every producer warp prefetches into its own ring: the slot's fp16 snapshot row (N <= 128) and the 32 columns of E_k / E_v
+// that its lanes convert (fp32 at most); PD slots ahead (N = 128 has shared memory for two stages only)
+__host__ __device__ constexpr int prefetch_dist(int NK) { return NK == 1 ? 3 : 1; }
+static constexpr int RING_STAGE_BYTES = 256 + 2 * 32 * 4;
 static constexpr int MAX_SLOTS = 4096;
 
 struct Smem {
@@ -65,11 +67,11 @@ __host__ __device__ inline Smem smem_layout(int K, int NK) {
     // NK = 2: fp32, two levels [8][128] (r / 16) and [16][128] (r % 16), product rounded once like the forward's fp32 table
     s.r_off = o; o += NK == 1 ? TM * 64 * 2 : 24 * 128 * 4;
     s.e2_off = o; o += NA * 2 * ACC_COLS * 2;     // E_k / E_v rows as bf16 (operands of the packed epilogue arithmetic)
-    s.ring_off = o; o += RING * RING_STAGE_BYTES;
+    s.ring_off = o; o += 4 * (prefetch_dist(NK) + 1) * RING_STAGE_BYTES;
     s.tok_off = o; o += TM * 4;
     s.slot_off = o; o += ((K * 2 + 15) / 16) * 16;
     s.key_off = o; o += ((K * 4 + 15) / 16) * 16;
-    s.bar_off = o; o += 128;
+    s.bar_off = o; o += 256;
     s.total = o + 1024;
     return s;
 }
@@ -86,6 +88,7 @@ struct Bars {
     uint32_t tmem_base;
     int abort_flag;
     int n_slots;
+    unsigned dmax_bits;          // largest |dO| among the CTA's rows (bit pattern of a non-negative float)
 };
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
@@ -122,6 +125,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
     int* key_sh = reinterpret_cast<int*>(sm + L.key_off);
     Bars* bars = reinterpret_cast<Bars*>(sm + L.bar_off);
     uint64_t* a_free = reinterpret_cast<uint64_t*>(sm + L.bar_off + 96);   // [NA] A/E stage released by product (2)
+    uint64_t* a_full = reinterpret_cast<uint64_t*>(sm + L.bar_off + 128);  // [NA] every producer warp has written its rows of the tile and its E columns (4 arrivals)
     volatile int* abort_flag = &bars->abort_flag;
 
     const int tile = blockIdx.x, hp = blockIdx.y, b = a.order ? a.order[blockIdx.z] : (int)blockIdx.z;
@@ -151,10 +155,14 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             mbar_init(&bars->acc_full[i], 2);
             mbar_init(&bars->acc_empty[i], EPI_WARPS);
         }
-        for (int i = 0; i < NA; ++i) mbar_init(&a_free[i], 1);
+        for (int i = 0; i < NA; ++i) {
+            mbar_init(&a_free[i], 1);
+            mbar_init(&a_full[i], 4);
+        }
         mbar_init(&bars->z_full, EPI_WARPS);
         mbar_init(&bars->z_done, 3);
         bars->abort_flag = *reinterpret_cast<volatile int*>(status);
+        bars->dmax_bits = 0u;
         fence_barrier_init();
     }
     if (warp == EPI_WARPS) {
@@ -225,36 +233,46 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
     if (!is_epi) {
         // ============================================================ producer warpgroup
         asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
-        // N = 64: the gate product takes an fp16 state tile (state / 64) and fp16 W (W * 64): 11 significant bits, where
-        // bf16 operands moved the pre-activations of slots with states in the hundreds by ~0.1.  The dW product needs the
-        // tile in the format of dpre (bf16; its gradients do not fit fp16's range), so the producer stores a bf16 copy
-        // of the tile behind the fp16 one.
+        // The gate product takes an fp16 state tile (state / 64) and fp16 W (W * 64): 11 significant bits, where bf16
+        // operands moved the pre-activations of slots with states in the hundreds by ~0.1.  The dW product reads the same
+        // tile: its rounding errors are the same for many consecutive time steps of a slot (the state decays slowly), so
+        // they do not average out over the sum, and 8 significant bits cost 2 % in dW_pe on small batches.  dpre, the
+        // other operand, is therefore fp16 as well, scaled by a power of two chosen per CTA from its rows of dO.
         const uint32_t idesc_gate = umma_idesc_16(TM, ACC_COLS, 0, 0, 0, 0);            // A, B K-major, fp16
-        const uint32_t idesc_dw = umma_idesc_16(ACC_COLS, N, 1, 1, 1, 1);               // A = dpre (MN-major), B = bf16 state tile (MN-major)
+        const uint32_t idesc_dw = umma_idesc_16(ACC_COLS, N, 1, 1, 0, 0);               // A = dpre (MN-major), B = state tile (MN-major), both fp16
         const uint32_t idesc_de = umma_idesc_bf16(ACC_COLS, 16, 1, 0);        // A = Z tile (MN-major), B = ones (K-major)
         const uint32_t a_base = smem_u32(A_sh), b_base = smem_u32(B_sh), z_base = smem_u32(Z_sh), o_base = smem_u32(ones_sh);
         const int wi = row >> 5, bi = row & 31;
+        const int pwarp = warp - EPI_WARPS;
+        constexpr int PD = prefetch_dist(NK), RING = PD + 1;
         const int esize = (a.e_dt == MBEMA_F32) ? 4 : 2;
-        const int s_chunks = N / 8, e_chunks = ACC_COLS * esize / 16;
-        const __nv_bfloat16* snap16 = reinterpret_cast<const __nv_bfloat16*>(a.tile_state + (size_t)a.B * a.nT * a.K * N);
+        const int s_chunks = N / 8, e_chunks = 32 * esize / 16;      // 16-byte chunks: snapshot row; this warp's 32 columns of E_k (E_v)
+        const __half* snap16 = reinterpret_cast<const __half*>(a.tile_state + (size_t)a.B * a.nT * a.K * N);
+        unsigned char* ring_w = ring_sh + pwarp * RING * RING_STAGE_BYTES;
+        // The producer warps do not wait for one another: each prefetches what its own lanes need (the whole snapshot row,
+        // read as broadcasts, and 32 columns of the E rows) and reports its part of the tile on an mbarrier.
         // E row of the next slot to prefetch (tables shared between samples: one index load per slot, a slot ahead)
         size_t erow_next = (ROWS && n_slots > 0) ? (size_t)a.erow[(size_t)b * a.K + slot_sh[0]] : 0;
         auto prefetch = [&](int j) {
-            if (j < n_slots && row < s_chunks + 2 * e_chunks) {   // threads without a chunk to copy skip the address arithmetic too
+            if (j < n_slots) {
                 const int k = slot_sh[j];
                 const size_t er = ROWS ? erow_next : (size_t)b * a.K + k;
                 if (ROWS && j + 1 < n_slots) erow_next = (size_t)a.erow[(size_t)b * a.K + slot_sh[j + 1]];
-                unsigned char* dst = ring_sh + (j % RING) * RING_STAGE_BYTES;
-                const unsigned char* srcS = reinterpret_cast<const unsigned char*>(snap16 + (((size_t)b * a.nT + tile) * a.K + k) * N);
-                const size_t eoff = (er * D + hp * ACC_COLS) * esize;
-                const unsigned char* srcK = reinterpret_cast<const unsigned char*>(a.Ek) + eoff;
-                const unsigned char* srcV = reinterpret_cast<const unsigned char*>(a.Ev) + eoff;
-                for (int c = row; c < s_chunks + 2 * e_chunks; c += PROD_THREADS) {
+                if (lane < s_chunks + 2 * e_chunks) {
+                    unsigned char* dst = ring_w + (j % RING) * RING_STAGE_BYTES;
+                    const size_t eoff = (er * D + hp * ACC_COLS + pwarp * 32) * esize;
                     const unsigned char* src;
                     unsigned char* d;
-                    if (c < s_chunks) { src = srcS + c * 16; d = dst + c * 16; }
-                    else if (c < s_chunks + e_chunks) { src = srcK + (c - s_chunks) * 16; d = dst + 256 + (c - s_chunks) * 16; }
-                    else { src = srcV + (c - s_chunks - e_chunks) * 16; d = dst + 256 + ACC_COLS * 4 + (c - s_chunks - e_chunks) * 16; }
+                    if (lane < s_chunks) {
+                        src = reinterpret_cast<const unsigned char*>(snap16 + (((size_t)b * a.nT + tile) * a.K + k) * N) + lane * 16;
+                        d = dst + lane * 16;
+                    } else if (lane < s_chunks + e_chunks) {
+                        src = reinterpret_cast<const unsigned char*>(a.Ek) + eoff + (lane - s_chunks) * 16;
+                        d = dst + 256 + (lane - s_chunks) * 16;
+                    } else {
+                        src = reinterpret_cast<const unsigned char*>(a.Ev) + eoff + (lane - s_chunks - e_chunks) * 16;
+                        d = dst + 256 + 128 + (lane - s_chunks - e_chunks) * 16;
+                    }
                     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(d)), "l"(src) : "memory");
                 }
             }
@@ -274,7 +292,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             mbar_wait(&bars->z_full, (uint32_t)(j & 1), abort_flag);
             tc_fence_after_sync();
             if (role == 1) {
-                const uint64_t d_at = d_a0 + (uint64_t)(((j % NA) * STAGE_BYTES + (NK == 1 ? ATOM_BYTES : 0)) >> 4);
+                const uint64_t d_at = d_a0 + (uint64_t)(((j % NA) * STAGE_BYTES) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < TM / 16; ++ks)      // contraction over the 128 time steps, 16 per instruction
                     umma_bf16_ss(tmem_base + COL_DW, d_zp + (uint64_t)(ks * (2048 >> 4)), d_at + (uint64_t)(ks * (2048 >> 4)),
@@ -300,22 +318,6 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             out[0] = h0.x * l0.x; out[1] = h0.y * l0.y; out[2] = h0.z * l0.z; out[3] = h0.w * l0.w;
             out[4] = h1.x * l1.x; out[5] = h1.y * l1.y; out[6] = h1.z * l1.z; out[7] = h1.w * l1.w;
         };
-        // NK = 2: the dW product needs the state tile in bf16 (the format of dpre), and shared memory has no room for a
-        // second copy: once the gate product of slot j has been consumed, every producer thread converts its row of the
-        // fp16 tile to bf16 in place
-        auto convert_tile_inplace = [&](int j) {
-            unsigned char* r0p = A_sh + (j % NA) * STAGE_BYTES + row * 128;
-#pragma unroll
-            for (int hb = 0; hb < 2; ++hb) {       // loads first: a load cannot be moved above an earlier shared-memory store
-                uint4 v[8];
-#pragma unroll
-                for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const uint4*>(r0p + hb * ATOM_BYTES + c * 16);
-#pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    *reinterpret_cast<uint4*>(r0p + hb * ATOM_BYTES + c * 16) =
-                        make_uint4(f16x2_to_bf16x2(v[c].x), f16x2_to_bf16x2(v[c].y), f16x2_to_bf16x2(v[c].z), f16x2_to_bf16x2(v[c].w));
-            }
-        };
         // NK = 1: this row's powers as packed fp16 pairs, register-resident (cold rows: packed multiply, as the forward)
         uint32_t R2[NK == 1 ? 32 : 1];
         if (NK == 1) {
@@ -323,24 +325,23 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             for (int j = 0; j < 32; ++j) R2[j] = *reinterpret_cast<const uint32_t*>(Rb_sh + row * N + 2 * j);
         }
         for (int j = 0; j < PD; ++j) prefetch(j);
-        asm volatile("cp.async.wait_group %0;" ::"n"(PD - 1) : "memory");
-        named_bar_sync(1, PROD_THREADS);
         for (int i = 0; i < n_slots; ++i) {
             const int sa = i % NA, sc = i % NACC;
             prefetch(i + PD);
-            asm volatile("cp.async.wait_group %0;" ::"n"(PD - 1) : "memory");
+            asm volatile("cp.async.wait_group %0;" ::"n"(PD) : "memory");   // this lane's copies for slot i have landed
+            __syncwarp();                                                      // ... and so have the other lanes'
             if (i >= NA) mbar_wait(&a_free[sa], (uint32_t)((i / NA - 1) & 1), abort_flag);
             const int keyf = key_sh[i];
             const int key = keyf & 0x7fffffff;
-            const unsigned char* rg = ring_sh + (i % RING) * RING_STAGE_BYTES;
-            {
+            const unsigned char* rg = ring_w + (i % RING) * RING_STAGE_BYTES;
+            {   // column `row` of the head pair's E_k / E_v rows, as bf16
                 float ekv, evv;
                 if (esize == 4) {
-                    ekv = reinterpret_cast<const float*>(rg + 256)[row];
-                    evv = reinterpret_cast<const float*>(rg + 256 + ACC_COLS * 4)[row];
+                    ekv = reinterpret_cast<const float*>(rg + 256)[lane];
+                    evv = reinterpret_cast<const float*>(rg + 256 + 128)[lane];
                 } else {
-                    ekv = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rg + 256)[row]);
-                    evv = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rg + 256 + ACC_COLS * 4)[row]);
+                    ekv = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rg + 256)[lane]);
+                    evv = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rg + 256 + 128)[lane]);
                 }
                 E2_sh[sa * 2 * ACC_COLS + row] = __float2bfloat16(ekv);
                 E2_sh[sa * 2 * ACC_COLS + ACC_COLS + row] = __float2bfloat16(evv);
@@ -378,41 +379,46 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                         rv = make_uint4(pack_f16x2(rr[0], rr[1]), pack_f16x2(rr[2], rr[3]), pack_f16x2(rr[4], rr[5]), pack_f16x2(rr[6], rr[7]));
                     }
                     pk.x = mul_f16x2(pk.x, rv.x); pk.y = mul_f16x2(pk.y, rv.y); pk.z = mul_f16x2(pk.z, rv.z); pk.w = mul_f16x2(pk.w, rv.w);
-                    if (NK == 1)
-                        *reinterpret_cast<uint4*>(Arow + ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) =
-                            make_uint4(f16x2_to_bf16x2(pk.x), f16x2_to_bf16x2(pk.y), f16x2_to_bf16x2(pk.z), f16x2_to_bf16x2(pk.w));
                     *reinterpret_cast<uint4*>(Arow + (cc >> 3) * ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) = pk;
                 }
             } else {
+                // snapshot times decay power.  All loads come first: the compiler cannot move a shared-memory load above an
+                // earlier shared-memory store (it cannot tell the buffers apart), so a load-multiply-store loop would run as
+                // N / 8 load latencies in a row.
+                uint4 svv[N / 8];
 #pragma unroll
-                for (int cc = 0; cc < N / 8; ++cc) {
-                    const uint4 sv = *reinterpret_cast<const uint4*>(rg + cc * 16);
-                    uint4 rv;
-                    if (NK == 1) {
-                        rv = make_uint4(R2[(4 * cc) & 31], R2[(4 * cc + 1) & 31], R2[(4 * cc + 2) & 31], R2[(4 * cc + 3) & 31]);
-                    } else {
+                for (int cc = 0; cc < N / 8; ++cc) svv[cc] = *reinterpret_cast<const uint4*>(rg + cc * 16);
+                if (NK == 2) {
+#pragma unroll
+                    for (int cc = 0; cc < N / 8; ++cc) {
                         float rr[8];
                         decay8(row, cc * 8, rr);
-                        rv = make_uint4(pack_f16x2(rr[0], rr[1]), pack_f16x2(rr[2], rr[3]), pack_f16x2(rr[4], rr[5]), pack_f16x2(rr[6], rr[7]));
+                        svv[cc].x = mul_f16x2(svv[cc].x, pack_f16x2(rr[0], rr[1]));
+                        svv[cc].y = mul_f16x2(svv[cc].y, pack_f16x2(rr[2], rr[3]));
+                        svv[cc].z = mul_f16x2(svv[cc].z, pack_f16x2(rr[4], rr[5]));
+                        svv[cc].w = mul_f16x2(svv[cc].w, pack_f16x2(rr[6], rr[7]));
                     }
-                    uint4 pk;
-                    pk.x = mul_f16x2(sv.x, rv.x); pk.y = mul_f16x2(sv.y, rv.y); pk.z = mul_f16x2(sv.z, rv.z); pk.w = mul_f16x2(sv.w, rv.w);
-                    if (NK == 1)
-                        *reinterpret_cast<uint4*>(Arow + ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) =
-                            make_uint4(f16x2_to_bf16x2(pk.x), f16x2_to_bf16x2(pk.y), f16x2_to_bf16x2(pk.z), f16x2_to_bf16x2(pk.w));
+                } else {
+#pragma unroll
+                    for (int cc = 0; cc < N / 8; ++cc) {
+                        svv[cc].x = mul_f16x2(svv[cc].x, R2[(4 * cc) & 31]);
+                        svv[cc].y = mul_f16x2(svv[cc].y, R2[(4 * cc + 1) & 31]);
+                        svv[cc].z = mul_f16x2(svv[cc].z, R2[(4 * cc + 2) & 31]);
+                        svv[cc].w = mul_f16x2(svv[cc].w, R2[(4 * cc + 3) & 31]);
+                    }
+                }
+#pragma unroll
+                for (int cc = 0; cc < N / 8; ++cc) {
+                    const uint4 pk = svv[cc];
                     *reinterpret_cast<uint4*>(Arow + (cc >> 3) * ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) = pk;
                 }
             }
             fence_proxy_async_smem();
-            named_bar_sync(1, PROD_THREADS);
-            if (NK == 2 && i >= 1) {   // tile i - 1: fp16 -> bf16 once the epilogue has consumed its gate product
-                mbar_wait(&bars->z_full, (uint32_t)((i - 1) & 1), abort_flag);
-                convert_tile_inplace(i - 1);
-                fence_proxy_async_smem();
-                named_bar_sync(2, PROD_THREADS);
-            }
+            __syncwarp();          // this warp's 32 rows of the tile and its E columns are in shared memory
+            if (lane == 0) mbar_arrive(&a_full[sa]);
             if (lane == 0) {
                 if (role == 0) {
+                    mbar_wait(&a_full[sa], (uint32_t)((i / NA) & 1), abort_flag);    // all four warps' rows and E columns
                     if (i >= NACC) mbar_wait(&bars->acc_empty[sc], (uint32_t)((i / NACC - 1) & 1), abort_flag);
                     tc_fence_after_sync();
 #pragma unroll
@@ -427,14 +433,10 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                     issue_grad_products(i - 1);
                 }
             }
-        }
-        if (NK == 2 && n_slots > 0) {
-            mbar_wait(&bars->z_full, (uint32_t)((n_slots - 1) & 1), abort_flag);
-            convert_tile_inplace(n_slots - 1);
-            fence_proxy_async_smem();
-            named_bar_sync(2, PROD_THREADS);
+            __syncwarp();
         }
         if (lane == 0 && role != 0 && n_slots > 0) issue_grad_products(n_slots - 1);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else {
         // ============================================================ epilogue warpgroups: a thread per time step, a head per warpgroup
         asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
@@ -443,7 +445,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
         const size_t qoff = (((size_t)b * a.H + h) * a.T + t) * HD;
         const bool row_ok = t < Lb;
         uint32_t q2[HD / 2], do2[HD / 2];     // q / sqrt(hd) and dO as packed bf16 pairs
-        float drow = 0.f;
+        float drow = 0.f, dmx = 0.f;
 #pragma unroll
         for (int i = 0; i < HD; i += 4) {
             const float4 v = row_ok ? ld4_dyn_f32(a.Q, a.q_dt, qoff + i) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -454,8 +456,25 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             do2[i / 2] = pack_bf16x2(g.x, g.y);
             do2[i / 2 + 1] = pack_bf16x2(g.z, g.w);
             drow += g.x * ov.x + g.y * ov.y + g.z * ov.z + g.w * ov.w;
+            dmx = fmaxf(dmx, fmaxf(fmaxf(fabsf(g.x), fabsf(g.y)), fmaxf(fabsf(g.z), fabsf(g.w))));
         }
         const float lse = row_ok ? a.LSE[((size_t)b * a.H + h) * a.T + t] : 0.f;
+        // dpre enters the dW product as fp16, scaled by a power of two chosen per CTA.  dpre is of the size of p * dO times
+        // factors of order one (gate derivative, E rows, q), and p = exp(score - LSE) is of the size of exp(-LSE) for
+        // scores of a few units, so the scale puts the CTA's largest |dO| * exp(-LSE) at 4: terms 2^-16 below the typical
+        // size keep their full precision, and there are 14 binades of room above it before fp16 saturates.
+        dmx = row_ok ? dmx * __expf(fminf(fmaxf(-lse, -80.0f), 80.0f)) : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) dmx = fmaxf(dmx, __shfl_xor_sync(0xffffffffu, dmx, o));
+        if (lane == 0) atomicMax(&bars->dmax_bits, __float_as_uint(dmx));
+        named_bar_sync(3, EPI_THREADS);
+        float sigma = 1.0f;
+        {
+            const float mx = __uint_as_float(*reinterpret_cast<volatile unsigned*>(&bars->dmax_bits));
+            int e = 0;
+            if (mx > 1.0e-36f && mx < 1.0e36f) { frexpf(mx, &e); sigma = ldexpf(1.0f, 2 - e); }
+        }
+        const float hs = 0.5f * sigma;
         const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t t_dq = t_lane + (uint32_t)(COL_DQ + wg * HD);
         {
@@ -490,7 +509,6 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                 tmem_wait_ld();
 #pragma unroll
                 for (int j8 = 0; j8 < 2; ++j8) {
-                    uint32_t sacc = 0u, dacc = 0u;        // bf16 pair sums of 4 terms each, flushed to fp32 per 8 columns
                     const int w0 = c * 8 + j8 * 4;
                     const uint4 ekp = *reinterpret_cast<const uint4*>(ek2a + w0);
                     const uint4 evp = *reinterpret_cast<const uint4*>(ev2a + w0);
@@ -506,10 +524,10 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                                 if (SILU) {     // h = x / 2, th = tanh(h), sg = sigmoid(x) = (1 + th)/2:  SiLU = h + h*th,  SiLU' = sg + SiLU*(1 - sg)
                                     const float th = tanh_approx(hh);
                                     g[v] = fmaf(hh, th, hh);
-                                    dsl[v] = fmaf(g[v], fmaf(-0.5f, th, 0.5f), fmaf(0.5f, th, 0.5f));
+                                    dsl[v] = fmaf(g[v], fmaf(-hs, th, hs), fmaf(hs, th, hs));      // sigma * SiLU'
                                 } else {
                                     g[v] = hh;
-                                    dsl[v] = 1.0f;
+                                    dsl[v] = sigma;
                                 }
                             }
                             gg = pack_bf16x2(g[0], g[1]);
@@ -517,13 +535,10 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                         }
                         g2[w0 + pr] = gg;
                         dsl2[w0 + pr] = dd;
-                        sacc = fma_bf16x2(gg, mul_bf16x2(q2[w0 + pr], ekw[pr]), sacc);
-                        dacc = fma_bf16x2(gg, mul_bf16x2(do2[w0 + pr], evw[pr]), dacc);
+                        // score and dO.V terms: bf16 x bf16 products are exact in fp32, where they are summed
+                        fma_f32_bf16x2(sp[0], sp[1], gg, mul_bf16x2(q2[w0 + pr], ekw[pr]));
+                        fma_f32_bf16x2(dpp[0], dpp[1], gg, mul_bf16x2(do2[w0 + pr], evw[pr]));
                     }
-                    sp[0] += bf16_lo(sacc);
-                    sp[1] += bf16_hi(sacc);
-                    dpp[0] += bf16_lo(dacc);
-                    dpp[1] += bf16_hi(dacc);
                 }
             }
             const float s = sp[0] + sp[1];
@@ -560,7 +575,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                         const uint32_t bd = mul_bf16x2(p2, do2[w0 + pr]);                 // p * dO
                         zk[pr] = mul_bf16x2(aq, gg);                                      // ds * q * g
                         zv[pr] = mul_bf16x2(bd, gg);                                      // p * dO * g
-                        zp[pr] = mul_bf16x2(fma_bf16x2(bd, evw[pr], mul_bf16x2(aq, ekw[pr])), dsl2[w0 + pr]);   // dgate * SiLU'
+                        zp[pr] = bf16x2_to_f16x2_sat(mul_bf16x2(fma_bf16x2(bd, evw[pr], mul_bf16x2(aq, ekw[pr])), dsl2[w0 + pr]));   // sigma * dgate * SiLU', fp16
                         ge[pr] = mul_bf16x2(gg, ekw[pr]);                                 // K = g * E_k, for dQ
                     }
                     const int chunk = ((c * 2 + j8) ^ (row & 7)) << 4;
@@ -616,7 +631,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                     for (int j = 0; j < 32; ++j) acc[j] = 0.f;
                 }
 #pragma unroll
-                for (int j = 0; j < 32; ++j) part_out[(size_t)(c * 32 + j) * ACC_COLS + row] = acc[j] * STATE_F16_UNSCALE;
+                for (int j = 0; j < 32; ++j) part_out[(size_t)(c * 32 + j) * ACC_COLS + row] = acc[j] * (STATE_F16_UNSCALE / sigma);
             }
         }
     }

@@ -209,6 +209,17 @@ __device__ __forceinline__ float tanh_approx(float x) {
     return y;
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Packed fp32 pairs (sm_100 f32x2 arithmetic): one FMA-pipe instruction per two elements.
 typedef unsigned long long f32x2;
 __device__ __forceinline__ f32x2 pack2(float lo, float hi) {
@@ -303,6 +314,16 @@ __device__ __forceinline__ void fma_f32_f16x2(float& a0, float& a1, uint32_t x, 
         : "+f"(a0), "+f"(a1)
         : "r"(x), "r"(y));
 }
+// the same with bf16 factors
+__device__ __forceinline__ void fma_f32_bf16x2(float& a0, float& a1, uint32_t x, uint32_t y) {
+    asm("{\n\t.reg .b16 xl, xh, yl, yh;\n\t"
+        "mov.b32 {xl, xh}, %2;\n\t"
+        "mov.b32 {yl, yh}, %3;\n\t"
+        "fma.rn.f32.bf16 %0, xl, yl, %0;\n\t"
+        "fma.rn.f32.bf16 %1, xh, yh, %1;\n\t}"
+        : "+f"(a0), "+f"(a1)
+        : "r"(x), "r"(y));
+}
 // both fp16 halves converted to bf16 (through fp32, round to nearest)
 __device__ __forceinline__ uint32_t f16x2_to_bf16x2(uint32_t v) {
     uint32_t d;
@@ -311,6 +332,17 @@ __device__ __forceinline__ uint32_t f16x2_to_bf16x2(uint32_t v) {
         "cvt.f32.f16 fl, l;\n\t"
         "cvt.f32.f16 fh, h;\n\t"
         "cvt.rn.bf16x2.f32 %0, fh, fl;\n\t}"
+        : "=r"(d)
+        : "r"(v));
+    return d;
+}
+// both bf16 halves converted to fp16 (values beyond the fp16 range become +-65504)
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2_sat(uint32_t v) {
+    uint32_t d;
+    asm("{\n\t.reg .f32 fl, fh;\n\t"
+        "shl.b32 fl, %1, 16;\n\t"
+        "and.b32 fh, %1, 0xffff0000;\n\t"
+        "cvt.rn.satfinite.f16x2.f32 %0, fh, fl;\n\t}"
         : "=r"(d)
         : "r"(v));
     return d;
