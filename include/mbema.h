@@ -11,7 +11,14 @@
  *     innermost dimension contiguous, in the shapes written beside each argument;
  *   - the caller owns every buffer, including `workspace` (size from the matching *_workspace_bytes);
  *     the library allocates nothing and keeps no mutable global state, so calls on different streams
- *     may run concurrently as long as their buffers differ;
+ *     may run concurrently as long as their buffers differ (one exception: mbema_query_scan_static, whose
+ *     scratch is a device array inside the library; see there);
+ *   - STATUS WORD of the tensor-core entry points (mbema_flash_fwd / _bwd / _rows in MBEMA_MODE_TC_BF16,
+ *     mbema_decode_attend_tc): the int32 at the start of `workspace` (the workspace must be 256-byte aligned).
+ *     The kernels only ever OR into it and the library never clears it: zero it once, keep passing the same
+ *     buffer, and read it at a synchronisation point of your choice.  Non-zero means a bounded wait inside a
+ *     kernel gave up (bit 0; bits 8.. name the wait): the outputs of that call and of every later call that
+ *     still sees the non-zero word are undefined (their CTAs skip their work).  Zero it again to go on;
  *   - `stream` is a cudaStream_t passed as void*; work is only enqueued, no entry point synchronises;
  *   - the return value is 0 on success, otherwise an MBEMA_ERR_* code (see mbema_strerror); argument
  *     errors are detected before anything is launched;
@@ -31,7 +38,7 @@
 extern "C" {
 #endif
 
-#define MBEMA_VERSION 100
+#define MBEMA_VERSION 200
 
 #define MBEMA_F32 0
 #define MBEMA_BF16 1
@@ -47,6 +54,10 @@ extern "C" {
                                    /* mathbrain/flash_ema_attention.py:76-79                               */
 #define MBEMA_FLAG_CBASE_EXTRA_DECAY 4 /* M_0 = rho * c_base (mathbrain/triton_flash_ema.py:48-50,185)     */
 #define MBEMA_FLAG_FP32_BACKWARD 8     /* MBEMA_MODE_TC_BF16 only: run the backward with the fp32 kernels      */
+/* Test hook of the tensor-core forward: one hand-off between its warps is withheld and the bounded waits give up after
+ * a few polls, so the kernel must end through its give-up path (status word set, TMEM released, outputs undefined).
+ * It exists so that this path can be exercised without hanging or faulting a GPU; never set it otherwise. */
+#define MBEMA_FLAG_TEST_WITHHOLD_ARRIVE (1 << 30)
 
 /* compute modes of the attention kernels */
 #define MBEMA_MODE_FP32 0          /* fp32 arithmetic on the CUDA cores                                    */
@@ -110,7 +121,7 @@ int mbema_query_scan_static(const int64_t* x, const float* rhos, const float* c_
  *   unique [B,K] i64 (-1 = not a slot)   c_base [B,K,N] f32 or NULL (zeros)
  *   out: tile_state [B, nT, K, N] f32 with nT = ceil(T / MBEMA_TILE_T), immediately followed in the same buffer
  *                   by the same values in 16 bits [B, nT, K, N] (6 bytes per element in total): fp16 of
- *                   state / 64 when N == 64 (operand of the fp16 gate product), bf16 otherwise
+ *                   state / 64, saturated (operand of the fp16 gate product)
  *        tok_state  [B, T, N]     f32  state of x[b,t]'s own slot just before step t (0 if unlisted)
  *        kcount     [2B]          i32  [0,B): number of valid (>= 0) entries of unique[b,:];
  *                                       [B,2B): sample indices by decreasing count (launch order of the attention CTAs)
@@ -145,11 +156,15 @@ int mbema_qgate_bwd(const void* dY, int dy_dtype, const void* x_q, int x_dtype, 
  * mathbrain/flash_ema_attention.py:46-82.
  *   Q [B,H,T,hd] (q_dtype)   x [B,T] i64   E_k, E_v [B,K,H*hd] (e_dtype)   W_pe [N,H*hd] f32
  *   rhos [N] f32   unique [B,K] i64   tile_state, tok_state, kcount from mbema_tile_states
- *   seq_lens [B] i32 or NULL: steps >= seq_lens[b] are skipped (their outputs are left untouched)
+ *   seq_lens [B] i32 or NULL: steps >= seq_lens[b] are skipped (O, LSE and dQ are written as zeros there)
  *   out: O [B,H,T,hd] f32, LSE [B,H,T] f32 (log of the softmax normaliser, saved for the backward)
  *   limits: hd == 64; MBEMA_MODE_TC_BF16 needs N in {64, 128}, an even H and a slot list that fits shared memory
  *   (otherwise MBEMA_ERR_UNSUPPORTED; the backward falls back to the fp32 kernels by itself); FP32: N <= 128.
  * ---------------------------------------------------------------------------------------------- */
+/* 1 if MBEMA_MODE_TC_BF16 can run the forward for (H heads of 64, N channels, K listed slots), else 0.  The reference
+ * chooses between its kernels by itself (mathbrain/model.py:78: `if HAS_TRITON and Q_t.is_cuda`); a caller that wants the
+ * same behaviour asks here and passes MBEMA_MODE_FP32 otherwise. */
+int mbema_flash_tc_supported(int64_t H, int64_t N, int64_t K);
 size_t mbema_flash_fwd_workspace_bytes(int64_t B, int64_t H, int64_t T, int64_t hd, int64_t N, int64_t K, int mode);
 int mbema_flash_fwd(const void* Q, int q_dtype, const int64_t* x, const void* E_k, const void* E_v, int e_dtype,
                     const float* W_pe, const float* rhos, const int64_t* unique, const float* tile_state,
@@ -216,7 +231,7 @@ int mbema_decode_attend(const void* q, int q_dtype, const void* E_k, const void*
  * stored as bf16): two
  * tcgen05 passes over 128-slot tiles with a softmax over all V_total slots between them.  Same arguments plus a
  * workspace of mbema_decode_attend_tc_workspace_bytes(B, H, Kcap) bytes; O is zeroed and accumulated by the call.
- * A bounded wait that ran out sets the int32 status word at the 256-byte aligned start of the workspace. */
+ * The int32 at the start of the workspace is the status word described under Conventions. */
 size_t mbema_decode_attend_tc_workspace_bytes(int64_t B, int64_t H, int64_t Kcap);
 int mbema_decode_attend_tc(const void* q, int q_dtype, const void* E_k, const void* E_v, int e_dtype,
                            const float* W_pe, const float* rhos, const float* state, const int32_t* last_t,

@@ -10,6 +10,7 @@ LIB_PATH = os.path.join(HERE, "libmbema.so")
 
 F32, BF16 = 0, 1
 FLAG_SILU, FLAG_LISTED_ONLY, FLAG_CBASE_EXTRA_DECAY, FLAG_FP32_BACKWARD = 1, 2, 4, 8
+FLAG_TEST_WITHHOLD_ARRIVE = 1 << 30
 MODE_FP32, MODE_TC_BF16 = 0, 1
 TILE_T = 128
 
@@ -29,6 +30,7 @@ SIGNATURES = {
     "mbema_qgate_bwd_workspace_bytes": (_sz, [_i64, _i64]),
     "mbema_qgate_bwd": (_i32, [_vp, _i32, _vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                _i64, _i64, _i32, _vp, _sz, _vp]),
+    "mbema_flash_tc_supported": (_i32, [_i64, _i64, _i64]),
     "mbema_flash_fwd_workspace_bytes": (_sz, [_i64] * 6 + [_i32]),
     "mbema_flash_fwd": (_i32, [_vp, _i32, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _vp, _sz, _vp]),

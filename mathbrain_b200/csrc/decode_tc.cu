@@ -313,7 +313,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, 512);
     }
-    if (tid == 0 && bars->abort_flag) atomicExch(status, 1);
+    if (tid == 0 && bars->abort_flag) atomicOr(status, bars->abort_flag);   // sticky: never cleared by the library
 }
 
 // probabilities over all V_total slots, in place: scores[b,h,k] <- exp(s - m) / l
@@ -395,7 +395,6 @@ extern "C" int mbema_decode_attend_tc(const void* q, int q_dtype, const void* E_
                 state, last_t, active, n_active, reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(status) + 256), O,
                 (int)B, (int)H, (int)V, (int)Kcap, (int)t_now, (int)S, t_now_dev, (float)V_total,
                 (flags & MBEMA_FLAG_LISTED_ONLY) ? 1 : 0};
-    MBEMA_CUDA_TRY(cudaMemsetAsync(status, 0, 256, st));
     MBEMA_CUDA_TRY(cudaMemsetAsync(O, 0, (size_t)B * H * hd * sizeof(float), st));
     MBEMA_CUDA_TRY(cudaMemsetAsync(a.scores, 0, (size_t)B * H * Kcap * sizeof(float), st));
     const int smem = dtc::SMEM_BYTES;

@@ -22,6 +22,7 @@ struct FlashArgs {
     int B, H, T, N, K, nT;
     float v_total;
     int silu, listed_only;
+    int test_withhold;      // test hook: see MBEMA_FLAG_TEST_WITHHOLD_ARRIVE
 };
 
 // row of the slot-embedding tables (and of their gradients) that slot (b, k) reads

@@ -27,9 +27,15 @@ static FlashArgs pack(const void* Q, int q_dtype, const int64_t* x, const void* 
     a.v_total = (float)V_total;
     a.silu = (flags & MBEMA_FLAG_SILU) ? 1 : 0;
     a.listed_only = (flags & MBEMA_FLAG_LISTED_ONLY) ? 1 : 0;
+    a.test_withhold = (flags & MBEMA_FLAG_TEST_WITHHOLD_ARRIVE) ? 1 : 0;
     a.erow = nullptr;
     a.e_rows = (long long)B * K;
     return a;
+}
+
+extern "C" int mbema_flash_tc_supported(int64_t H, int64_t N, int64_t K) {
+    if (H < 1 || N < 1 || K < 1 || H > 65535 || K > (1 << 20)) return 0;
+    return flash_tc_supported((int)H, (int)N, (int)K) ? 1 : 0;
 }
 
 extern "C" size_t mbema_flash_fwd_workspace_bytes(int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int) {
@@ -129,7 +135,8 @@ static int flash_bwd_impl(const void* Q, int q_dtype, const int64_t* x, const vo
     if (mode == MBEMA_MODE_TC_BF16) {
         if (!(flags & MBEMA_FLAG_FP32_BACKWARD) && flash_bwd_tc_supported((int)H, (int)N, (int)K))
             return flash_bwd_tc(a, dW_pe, workspace, st);
-        MBEMA_CUDA_TRY(cudaMemsetAsync(workspace, 0, 512, st));   // status word: the fp32 kernels have no bounded waits
+        // (the first 512 bytes stay reserved for the status word of the tensor-core kernels; the fp32 kernels have no
+        // bounded waits and leave it alone)
         return flash_bwd_simt(a, dW_pe, static_cast<unsigned char*>(workspace) + 512, st);
     }
     return flash_bwd_simt(a, dW_pe, workspace, st);

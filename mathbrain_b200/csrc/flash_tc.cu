@@ -115,6 +115,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
     int* key_sh = reinterpret_cast<int*>(sm + L.key_off);
     Bars* bars = reinterpret_cast<Bars*>(sm + L.bar_off);
     volatile int* abort_flag = &bars->abort_flag;
+    const unsigned spin_limit = a.test_withhold ? 64u : MBEMA_SPIN_LIMIT;      // test hook: waits give up after a few polls
 
     const int tile = blockIdx.x, hp = blockIdx.y, b = a.order ? a.order[blockIdx.z] : (int)blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -267,7 +268,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
             __syncwarp();                                                       // ... and so have the other lanes'
             // this warp's stage (A tile, accumulators) is free once the epilogue has read slot i - NSTAGE; by then the
             // epilogue is also done with the E rows of slot i - NE, whose stage the rows of slot i take
-            if (it >= 1 && !mbar_wait(&bars->acc_empty[pw], (uint32_t)((it - 1) & 1), abort_flag, 1)) break;
+            if (it >= 1 && !mbar_wait(&bars->acc_empty[pw], (uint32_t)((it - 1) & 1), abort_flag, 1, spin_limit)) break;
             const int keyf = key_sh[i];
             const unsigned char* rg = ring_w + (it % RW) * RING_STAGE_BYTES;
             // E_k / E_v rows of the slot for the head pair, as fp16 (saturated): lane l converts columns 4l .. 4l+3 of both
@@ -352,7 +353,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
                                  idesc, k16 != 0 ? 1u : 0u);
                 }
                 umma_commit(&bars->acc_full[pw]);   // first arrival: the UMMAs above have completed
-                mbar_arrive(&bars->acc_full[pw]);   // second arrival: releases the staged E rows
+                if (!(a.test_withhold && i == 0)) mbar_arrive(&bars->acc_full[pw]);   // second arrival: releases the staged E rows
+                                                                                        // (test hook: withheld once)
             }
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -405,7 +407,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
         };
         for (int i = 0; i < n_slots; ++i) {
             const int st = i % NSTAGE, u = i / NSTAGE;
-            alive = mbar_wait(&bars->acc_full[st], (uint32_t)(u & 1), abort_flag, 2);
+            alive = mbar_wait(&bars->acc_full[st], (uint32_t)(u & 1), abort_flag, 2, spin_limit);
             if (!alive) break;
             tc_fence_after_sync();
             const uint32_t t_acc = t_lane + st * ACC_COLS;
@@ -488,7 +490,6 @@ size_t flash_fwd_tc_ws() { return 256; }
 
 int flash_fwd_tc(const FlashArgs& a, void* ws, cudaStream_t st) {
     int* status = reinterpret_cast<int*>((reinterpret_cast<uintptr_t>(ws) + 15) & ~uintptr_t(15));
-    MBEMA_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), st));
     const tc::Smem L = tc::smem_layout(a.N, a.K);
     dim3 grid(a.nT, a.H / tc::HPC, a.B);
 #define MBEMA_LAUNCH_FWD(S_, NK_, R_)                                                                                     \

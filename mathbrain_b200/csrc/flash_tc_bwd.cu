@@ -642,7 +642,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, TMEM_COLS);
     }
-    if (tid == 0 && bars->abort_flag) atomicExch(status, 1);
+    if (tid == 0 && bars->abort_flag) atomicOr(status, bars->abort_flag);   // sticky: never cleared by the library
 }
 
 // dW[n, hp*128 + d] = sum over (b, tile) of part[b][hp][tile][n][d]      (fixed order -> deterministic)
@@ -672,7 +672,6 @@ int flash_bwd_tc(FlashArgs a, float* dW, void* ws, cudaStream_t st) {
     const int D = a.H * tcb::HD;
     int* status = reinterpret_cast<int*>((reinterpret_cast<uintptr_t>(ws) + 255) & ~uintptr_t(255));
     a.dW_part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(status) + 256);
-    MBEMA_CUDA_TRY(cudaMemsetAsync(status, 0, 256, st));
     MBEMA_CUDA_TRY(cudaMemsetAsync(a.dEk, 0, (size_t)a.e_rows * D * sizeof(float), st));
     MBEMA_CUDA_TRY(cudaMemsetAsync(a.dEv, 0, (size_t)a.e_rows * D * sizeof(float), st));
     const tcb::Smem L = tcb::smem_layout(a.K, a.N / 64);

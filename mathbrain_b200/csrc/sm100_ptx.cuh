@@ -44,8 +44,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // SLEEP_NS > 0: the thread sleeps that long between polls.  A polling warp executes instructions, and those take issue
 // slots from the warps that have work, so warps that wait far ahead of their consumer should poll rarely.
 template <unsigned SLEEP_NS = 0>
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int tag = 0) {
-    for (unsigned it = 0; it < MBEMA_SPIN_LIMIT; ++it) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int tag = 0,
+                                          unsigned limit = MBEMA_SPIN_LIMIT) {
+    for (unsigned it = 0; it < limit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if ((it & 255u) == 255u && *abort_flag) return false;

@@ -84,13 +84,16 @@ class DecodeState:
         flags = (_lib.FLAG_SILU if use_silu else 0) | (_lib.FLAG_LISTED_ONLY if listed_only else 0)
         tc_ok = self.N == 64 and hd == 64 and H % 2 == 0
         if mode is None:
-            mode = "tc_bf16" if (get_options()["mode"] == "tc_bf16" and tc_ok) else "fp32"
+            mode = "tc_bf16" if (get_options()["mode"] in ("tc_bf16", "auto") and tc_ok) else "fp32"
         if mode == "tc_bf16":
             if E_k.dtype != torch.bfloat16:          # the kernel copies embedding rows as stored: keep bf16 tables to avoid this cast
                 E_k, E_v = E_k.to(torch.bfloat16), E_v.to(torch.bfloat16)
             need = lib.mbema_decode_attend_tc_workspace_bytes(B, H, self.cap)
             if self._ws is None or self._ws.numel() < need:
-                self._ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+                old = self._ws
+                self._ws = torch.zeros(need, dtype=torch.uint8, device=q.device)   # its first int32 is the sticky status word
+                if old is not None:
+                    self._ws[:4].copy_(old[:4])
             rc = lib.mbema_decode_attend_tc(_ptr(q), _dt(q), _ptr(E_k), _ptr(E_v), _dt(E_k), _ptr(W), _ptr(self.rhos),
                                             _ptr(self.state), _ptr(self.last_t), _ptr(self.active),
                                             _ptr(self.n_active), _ptr(O), B, H, hd, self.V, self.N, self.cap,
@@ -118,6 +121,11 @@ class DecodeState:
                                      self.cap, int(t_now), _ptr(self.t_dev), _stream())
         _lib.check(rc, "mbema_decode_update")
         return C_q
+
+    def device_status(self):
+        """Status word of the tensor-core attend kernels since this state was created (synchronises): 0 = ok, else a
+        bounded wait inside a kernel gave up and the outputs since then are invalid."""
+        return 0 if self._ws is None else int(self._ws[:4].view(torch.int32).item())
 
     def check_overflow(self):
         """Synchronises; raises if an active list overflowed or a token was out of range."""

@@ -16,6 +16,7 @@ Reference operators mirrored (paths within the reference tree):
 from __future__ import annotations
 
 import contextlib
+import functools
 from dataclasses import dataclass
 from typing import Optional
 
@@ -26,8 +27,9 @@ from . import _lib
 # mathbrain/model.py takes its GPU operator path when this name is truthy.
 HAS_TRITON = True
 
-_OPTIONS = {"inactive_mass": "full_V", "cbase_extra_decay": False, "mode": "fp32", "fp32_backward": False}
-_MODES = {"fp32": _lib.MODE_FP32, "tc_bf16": _lib.MODE_TC_BF16}
+_OPTIONS = {"inactive_mass": "full_V", "cbase_extra_decay": False, "mode": "auto", "fp32_backward": False,
+            "_test_withhold_arrive": False}
+_MODES = {"fp32": _lib.MODE_FP32, "tc_bf16": _lib.MODE_TC_BF16, "auto": None}
 
 
 def set_options(inactive_mass: Optional[str] = None, cbase_extra_decay: Optional[bool] = None,
@@ -40,7 +42,11 @@ def set_options(inactive_mass: Optional[str] = None, cbase_extra_decay: Optional
     cbase_extra_decay  False (default): the slot state seen at chunk step 0 is exactly c_base
                        (mathbrain/data.py:128-140); True: rho * c_base, the Triton kernels' convention
                        (mathbrain/triton_flash_ema.py:48-50,185).
-    mode               "fp32": fp32 arithmetic on the CUDA cores; "tc_bf16": gate product on the tensor cores.
+    mode               "auto" (default): the tensor-core kernels wherever the shape allows them (hd = 64, N in {64, 128},
+                       an even number of heads, a slot list that fits shared memory), the fp32 kernels otherwise --
+                       like the reference, which takes its fast path by itself (mathbrain/model.py:78);
+                       "tc_bf16": tensor-core kernels (16-bit gate operands, fp32 accumulation; 2e-2 tolerance),
+                       unsupported shapes raise; "fp32": fp32 arithmetic on the CUDA cores (1e-4 tolerance).
     fp32_backward      with mode "tc_bf16": keep the tensor-core forward but run the backward with the fp32 kernels.
     """
     if fp32_backward is not None:
@@ -83,6 +89,26 @@ def _require_cuda(*tensors):
 
 def _ptr(t):
     return None if t is None else t.data_ptr()
+
+
+def _on_tensor_device(fn):
+    """Run `fn` with the device of its CUDA tensor arguments current (kernels are launched on the current device's
+    current stream while the buffers live where the tensors are); tensors on different devices are refused."""
+    @functools.wraps(fn)
+    def wrapper(*args, **kw):
+        dev = None
+        for a in list(args) + list(kw.values()):
+            t = a.tile_state if isinstance(a, TileStates) else a
+            if torch.is_tensor(t) and t.device.type == "cuda":
+                if dev is None:
+                    dev = t.device
+                elif t.device != dev:
+                    raise _lib.MbemaError("operands live on different devices (%s and %s)" % (dev, t.device))
+        if dev is None or dev.index == torch.cuda.current_device():
+            return fn(*args, **kw)
+        with torch.cuda.device(dev):
+            return fn(*args, **kw)
+    return wrapper
 
 
 def _dt(t):
@@ -144,21 +170,55 @@ class _Telemetry:
 
 telemetry = _Telemetry()
 
-# workspace of the most recent tensor-core attention call; its first int32 is the kernel's status word
-_last_tc_workspace = None
+# Workspaces of the tensor-core entry points, one per (device, stream), kept for the life of the process.  Their first
+# int32 is the kernels' status word: the kernels OR into it and nothing clears it until clear_status(), so a bounded
+# wait that gave up in any call of a step is still visible when the step ends.
+_tc_workspaces = {}
 
 
-def device_status():
-    """Status word of the most recent tensor-core attention kernel (synchronises): 0 = ok, 1 = a bounded wait
-    inside the kernel expired (the results of that call are invalid)."""
-    if _last_tc_workspace is None:
-        return 0
-    return int(_last_tc_workspace[:4].view(torch.int32).item())
+def _tc_workspace(nbytes, device):
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    ws = _tc_workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        new = torch.zeros(max(int(nbytes), 4096), dtype=torch.uint8, device=device)
+        if ws is not None:
+            new[:4].copy_(ws[:4])          # carry the status word over
+        _tc_workspaces[key] = ws = new
+    return ws
+
+
+def device_status(device=None):
+    """Status of the tensor-core kernels on `device` (default: the current one) since the last clear_status();
+    synchronises.  0 = ok; otherwise bit 0 says that a bounded wait inside a kernel gave up (bits 8.. name the wait)
+    and the results produced since then are invalid."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    st = 0
+    for (d, _), ws in _tc_workspaces.items():
+        if d == dev:
+            st |= int(ws[:4].view(torch.int32).item())
+    return st
+
+
+def check_status(device=None):
+    """Raise if a tensor-core kernel reported a failed wait since the last clear_status() (synchronises)."""
+    st = device_status(device)
+    if st:
+        raise _lib.MbemaError("a bounded wait inside a tensor-core kernel gave up (status 0x%x): results since the last "
+                              "check are invalid" % st)
+
+
+def clear_status(device=None):
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    for (d, _), ws in _tc_workspaces.items():
+        if d == dev:
+            ws[:4].zero_()
 
 
 # ---------------------------------------------------------------------------------------------
 # query-side scan
 # ---------------------------------------------------------------------------------------------
+@_on_tensor_device
 def compute_query_ema_history(x, rhos, vocab_size, c_init=None, c_init_keys=None, doc_ids=None):
     """C_seq[b, t, :] = EMA state of token x[b, t] just before step t, float32 [B, L, N].
 
@@ -208,6 +268,7 @@ class TileStates:
     shape: tuple                        # (B, T, K, N)
 
 
+@_on_tensor_device
 def precompute_boundaries(x, unique_tensor, rhos, Br, c_init=None, doc_ids=None, seq_lens=None):
     """Slot-state snapshots per time tile; drop-in for mathbrain/triton_flash_ema.py:81.
 
@@ -272,12 +333,22 @@ def _build_unique_index(x, device=None):
 # ---------------------------------------------------------------------------------------------
 # flash-EMA attention
 # ---------------------------------------------------------------------------------------------
+def _flash_mode(H, N, K):
+    """Compute mode of an attention call under the current options."""
+    m = _OPTIONS["mode"]
+    if m == "auto":
+        return _lib.MODE_TC_BF16 if _lib.load().mbema_flash_tc_supported(H, N, K) else _lib.MODE_FP32
+    return _MODES[m]
+
+
 def _flash_flags(use_silu):
     f = _lib.FLAG_SILU if use_silu else 0
     if _OPTIONS["inactive_mass"] == "listed_only":
         f |= _lib.FLAG_LISTED_ONLY
     if _OPTIONS["fp32_backward"]:
         f |= _lib.FLAG_FP32_BACKWARD
+    if _OPTIONS["_test_withhold_arrive"]:      # test hook of the tensor-core forward (see include/mbema.h)
+        f |= _lib.FLAG_TEST_WITHHOLD_ARRIVE
     return f
 
 
@@ -290,6 +361,7 @@ class FlashEMAFunction(torch.autograd.Function):
     """
 
     @staticmethod
+    @_on_tensor_device
     def forward(ctx, Q, x, E_k_active, E_v_active, W_pe, rhos, V_total, unique_tensor, K_max, C_bounds,
                 use_silu=True, Br=64):
         _require_cuda(Q, x, E_k_active, E_v_active, W_pe, rhos, unique_tensor)
@@ -299,7 +371,9 @@ class FlashEMAFunction(torch.autograd.Function):
         B, H, L, hd = Q.shape
         D = H * hd
         N = rhos.shape[0]
-        K = int(K_max)
+        # the reference forces K_max >= 16 and then slices the slot list to K_max columns (mathbrain/model.py:169-171);
+        # a list narrower than that arrives with its own width, which is what counts here
+        K = min(int(K_max), unique_tensor.shape[1])
         if C_bounds.shape != (B, L, K, N):
             raise _lib.MbemaError("C_bounds was built for (B,L,K,N)=%s, operator called with %s"
                                   % (C_bounds.shape, (B, L, K, N)))
@@ -317,9 +391,10 @@ class FlashEMAFunction(torch.autograd.Function):
         xx = x.long().contiguous()
         O = torch.empty(B, H, L, hd, dtype=torch.float32, device=Q.device)
         LSE = torch.empty(B, H, L, dtype=torch.float32, device=Q.device)
-        mode = _MODES[_OPTIONS["mode"]]
+        mode = _flash_mode(H, N, K)
         flags = _flash_flags(use_silu)
-        ws = _workspace(lib.mbema_flash_fwd_workspace_bytes(B, H, L, hd, N, K, mode), Q.device)
+        need = lib.mbema_flash_fwd_workspace_bytes(B, H, L, hd, N, K, mode)
+        ws = _tc_workspace(need, Q.device) if mode == _lib.MODE_TC_BF16 else _workspace(need, Q.device)
         _ev = telemetry.begin("mbema_flash_fwd")
         rc = lib.mbema_flash_fwd(_ptr(Qc), _dt(Qc), _ptr(xx), _ptr(Ek), _ptr(Ev), _dt(Ek), _ptr(W), _ptr(rh),
                                  _ptr(C_bounds.unique), _ptr(C_bounds.tile_state), _ptr(C_bounds.tok_state),
@@ -327,9 +402,6 @@ class FlashEMAFunction(torch.autograd.Function):
                                  B, H, L, hd, N, K, int(V_total), flags, mode, _ptr(ws), ws.numel(), _stream())
         telemetry.end("mbema_flash_fwd", _ev)
         _lib.check(rc, "mbema_flash_fwd")
-        if mode == _lib.MODE_TC_BF16:
-            global _last_tc_workspace
-            _last_tc_workspace = ws
         ctx.save_for_backward(Qc, xx, Ek, Ev, W, rh, O, LSE)
         ctx.handle = C_bounds
         ctx.meta = (B, H, L, hd, N, K, int(V_total), flags, mode)
@@ -337,6 +409,7 @@ class FlashEMAFunction(torch.autograd.Function):
         return O
 
     @staticmethod
+    @_on_tensor_device
     def backward(ctx, dO):
         lib = _lib.load()
         Qc, xx, Ek, Ev, W, rh, O, LSE = ctx.saved_tensors
@@ -348,7 +421,8 @@ class FlashEMAFunction(torch.autograd.Function):
         dEk = torch.empty(B, K, D, dtype=torch.float32, device=dO.device)
         dEv = torch.empty(B, K, D, dtype=torch.float32, device=dO.device)
         dW = torch.empty(N, D, dtype=torch.float32, device=dO.device)
-        ws = _workspace(lib.mbema_flash_bwd_workspace_bytes(B, H, L, hd, N, K, mode), dO.device)
+        need = lib.mbema_flash_bwd_workspace_bytes(B, H, L, hd, N, K, mode)
+        ws = _tc_workspace(need, dO.device) if mode == _lib.MODE_TC_BF16 else _workspace(need, dO.device)
         _ev = telemetry.begin("mbema_flash_bwd")
         rc = lib.mbema_flash_bwd(_ptr(Qc), _dt(Qc), _ptr(xx), _ptr(Ek), _ptr(Ev), _dt(Ek), _ptr(W), _ptr(rh),
                                  _ptr(h.unique), _ptr(h.tile_state), _ptr(h.tok_state), _ptr(h.kcount),
@@ -357,9 +431,6 @@ class FlashEMAFunction(torch.autograd.Function):
                                  _stream())
         telemetry.end("mbema_flash_bwd", _ev)
         _lib.check(rc, "mbema_flash_bwd")
-        if mode == _lib.MODE_TC_BF16:
-            global _last_tc_workspace
-            _last_tc_workspace = ws
         qd, kd, vd, wd = ctx.in_dtypes
         return (dQ.to(qd), None, dEk.to(kd), dEv.to(vd), dW.to(wd), None, None, None, None, None, None, None)
 
@@ -386,6 +457,7 @@ class FlashEMARowsFunction(torch.autograd.Function):
     all slots sharing a row.  backward returns (dQ, None, dE_k_rows, dE_v_rows, None, dW_pe, None x 6)."""
 
     @staticmethod
+    @_on_tensor_device
     def forward(ctx, Q, x, E_k_rows, E_v_rows, row_index, W_pe, rhos, V_total, unique_tensor, K_max, C_bounds,
                 use_silu=True):
         _require_cuda(Q, x, E_k_rows, E_v_rows, row_index, W_pe, rhos, unique_tensor)
@@ -395,7 +467,7 @@ class FlashEMARowsFunction(torch.autograd.Function):
         B, H, L, hd = Q.shape
         D = H * hd
         N = rhos.shape[0]
-        K = int(K_max)
+        K = min(int(K_max), unique_tensor.shape[1])
         if C_bounds.shape != (B, L, K, N):
             raise _lib.MbemaError("C_bounds was built for (B,L,K,N)=%s, operator called with %s"
                                   % (C_bounds.shape, (B, L, K, N)))
@@ -415,9 +487,10 @@ class FlashEMARowsFunction(torch.autograd.Function):
         xx = x.long().contiguous()
         O = torch.empty(B, H, L, hd, dtype=torch.float32, device=Q.device)
         LSE = torch.empty(B, H, L, dtype=torch.float32, device=Q.device)
-        mode = _MODES[_OPTIONS["mode"]]
+        mode = _flash_mode(H, N, K)
         flags = _flash_flags(use_silu)
-        ws = _workspace(lib.mbema_flash_fwd_workspace_bytes(B, H, L, hd, N, K, mode), Q.device)
+        need = lib.mbema_flash_fwd_workspace_bytes(B, H, L, hd, N, K, mode)
+        ws = _tc_workspace(need, Q.device) if mode == _lib.MODE_TC_BF16 else _workspace(need, Q.device)
         _ev = telemetry.begin("mbema_flash_fwd")
         rc = lib.mbema_flash_fwd_rows(_ptr(Qc), _dt(Qc), _ptr(xx), _ptr(Ek), _ptr(Ev), _dt(Ek), _ptr(ri), U, _ptr(W),
                                       _ptr(rh), _ptr(C_bounds.unique), _ptr(C_bounds.tile_state),
@@ -426,9 +499,6 @@ class FlashEMARowsFunction(torch.autograd.Function):
                                       ws.numel(), _stream())
         telemetry.end("mbema_flash_fwd", _ev)
         _lib.check(rc, "mbema_flash_fwd_rows")
-        if mode == _lib.MODE_TC_BF16:
-            global _last_tc_workspace
-            _last_tc_workspace = ws
         ctx.save_for_backward(Qc, xx, Ek, Ev, ri, W, rh, O, LSE)
         ctx.handle = C_bounds
         ctx.meta = (B, H, L, hd, N, K, U, int(V_total), flags, mode)
@@ -436,6 +506,7 @@ class FlashEMARowsFunction(torch.autograd.Function):
         return O
 
     @staticmethod
+    @_on_tensor_device
     def backward(ctx, dO):
         lib = _lib.load()
         Qc, xx, Ek, Ev, ri, W, rh, O, LSE = ctx.saved_tensors
@@ -447,7 +518,8 @@ class FlashEMARowsFunction(torch.autograd.Function):
         dEk = torch.empty(U, D, dtype=torch.float32, device=dO.device)
         dEv = torch.empty(U, D, dtype=torch.float32, device=dO.device)
         dW = torch.empty(N, D, dtype=torch.float32, device=dO.device)
-        ws = _workspace(lib.mbema_flash_bwd_workspace_bytes(B, H, L, hd, N, K, mode), dO.device)
+        need = lib.mbema_flash_bwd_workspace_bytes(B, H, L, hd, N, K, mode)
+        ws = _tc_workspace(need, dO.device) if mode == _lib.MODE_TC_BF16 else _workspace(need, dO.device)
         _ev = telemetry.begin("mbema_flash_bwd")
         rc = lib.mbema_flash_bwd_rows(_ptr(Qc), _dt(Qc), _ptr(xx), _ptr(Ek), _ptr(Ev), _dt(Ek), _ptr(ri), U, _ptr(W),
                                       _ptr(rh), _ptr(h.unique), _ptr(h.tile_state), _ptr(h.tok_state), _ptr(h.kcount),
@@ -456,9 +528,6 @@ class FlashEMARowsFunction(torch.autograd.Function):
                                       ws.numel(), _stream())
         telemetry.end("mbema_flash_bwd", _ev)
         _lib.check(rc, "mbema_flash_bwd_rows")
-        if mode == _lib.MODE_TC_BF16:
-            global _last_tc_workspace
-            _last_tc_workspace = ws
         qd, kd, vd, wd = ctx.in_dtypes
         return (dQ.to(qd), None, dEk.to(kd), dEv.to(vd), None, dW.to(wd), None, None, None, None, None, None)
 
@@ -471,6 +540,7 @@ class FusedGatingFunction(torch.autograd.Function):
     Drop-in for mathbrain/triton_fused_gating.py:122; backward returns (dx_q, dp_pre, dbias, dln_w, dln_b, None)."""
 
     @staticmethod
+    @_on_tensor_device
     def forward(ctx, x_q, p_pre, bias, ln_w, ln_b, use_silu=True):
         _require_cuda(x_q, p_pre, bias, ln_w, ln_b)
         lib = _lib.load()
@@ -496,6 +566,7 @@ class FusedGatingFunction(torch.autograd.Function):
         return y
 
     @staticmethod
+    @_on_tensor_device
     def backward(ctx, dy):
         lib = _lib.load()
         xq, pp, bb, lw, mu, rstd = ctx.saved_tensors

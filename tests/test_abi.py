@@ -28,7 +28,7 @@ def test_header_symbols_exported(lib):
 
 
 def test_version_and_strerror(lib):
-    assert lib.mbema_version() == 100
+    assert lib.mbema_version() == 200
     assert lib.mbema_strerror(0) == b"ok"
     assert b"workspace" in lib.mbema_strerror(4)
 

@@ -28,7 +28,7 @@ def test_decode_matches_dense_loop(B, V, N, H, steps, dt):
     for t in range(steps):
         if int((last >= 0).sum(1).max()) >= cap and not bool(((last[torch.arange(B), x[:, t]]) >= 0).all()):
             break                                    # the next token would overflow the active list of this small test
-        O = st.attend(Q[:, :, t].cuda(), E_k.cuda(), E_v.cuda(), W.cuda(), t)
+        O = st.attend(Q[:, :, t].cuda(), E_k.cuda(), E_v.cuda(), W.cuda(), t, mode="fp32")      # the exact kernel
         Cq = st.update(x[:, t].cuda(), t)
         O_ref, Cq_ref = orc.decode_step(state, last, t, x[:, t], Q[:, :, t].float(), E_k.float(), E_v.float(), W, rhos, V)
         assert rel_err(O.cpu(), O_ref) < (1e-4 if dt == torch.float32 else 2e-2), t

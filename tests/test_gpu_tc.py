@@ -149,3 +149,33 @@ def test_shared_embedding_rows_match_per_sample_tensors(mb, mode):
         ref = torch.zeros(U, D, device=dev)
         ref.index_add_(0, row_index.long().reshape(-1), (per_sample.float() * valid).reshape(-1, D))
         assert rel_err(rows_grad.float().cpu(), ref.cpu()) < (2e-2 if mode == "tc_bf16" else 1e-5)   # atomics: order differs
+
+
+def test_bounded_wait_gives_up_cleanly(mb):
+    """The give-up path of the tensor-core forward: with the library's test hook one hand-off between the kernel's warps
+    is withheld and its waits expire after a few polls.  The launch must end by itself, the sticky status word must name
+    the failed wait and stay set over later calls, and -- once cleared -- the next launch must run normally, which it can
+    only do if the first one released its tensor memory.  Nothing here hangs or faults the GPU: every wait is bounded."""
+    inp, c_base, _ = make_case(901, B=2, T=200, N=64, H=2, vocab=300, max_prefix=100, min_hl=4.0, max_hl=500.0)
+    assert mb.device_status() == 0
+    mb.ops._OPTIONS["_test_withhold_arrive"] = True
+    try:
+        with mb.options(mode="tc_bf16"):
+            run_flash(mb, inp, c_base, dtype=torch.bfloat16, with_grad=False)
+    finally:
+        mb.ops._OPTIONS["_test_withhold_arrive"] = False
+    torch.cuda.synchronize()
+    st = mb.device_status()
+    assert st & 1, hex(st)                       # a bounded wait gave up ...
+    assert (st >> 8) in (1, 2, 3), hex(st)       # ... and the word says which one
+    with pytest.raises(mb._lib.MbemaError):
+        mb.ops.check_status()
+    # sticky: a later call does not clear it (its CTAs see the word and skip their work)
+    with mb.options(mode="tc_bf16"):
+        run_flash(mb, inp, c_base, dtype=torch.bfloat16, with_grad=False)
+    assert mb.device_status() == st
+    mb.ops.clear_status()
+    out = run_tc(mb, inp, c_base, with_grad=False)
+    with mb.options(mode="fp32"):
+        ref = run_flash(mb, inp, c_base, dtype=torch.bfloat16, with_grad=False)
+    assert rel_err(out["O"], ref["O"]) < TOL_BF16
