@@ -1,6 +1,7 @@
 """The BASELINE configurations at their full sizes: the tensor-core path against the fp32 kernels (which the small
 cases pin on the oracle and the reference fixtures), plus size-independent properties.  One layer each."""
 import pytest
+import numpy as np
 import torch
 
 from helpers import rel_err
@@ -110,3 +111,97 @@ def test_config4_full_size_decode_step(mb):
     st.update(tok, 8192)
     st.check_overflow()
     assert int(st.n_active.max()) <= K + 1
+
+
+def _sample_inputs(batch, w, i):
+    """Sample i of a batch on its own: its valid slots only, its own prefix state, all T steps."""
+    kb = int(batch["pad_mask"][i].sum())
+    sub = dict(batch)
+    for key in ("x", "fill", "prefix_len"):
+        if key in sub and torch.is_tensor(sub[key]) and sub[key].dim() > 0:
+            sub[key] = sub[key][i:i + 1]
+    sub["unique_slots"] = batch["unique_slots"][i:i + 1, :kb]
+    sub["pad_mask"] = batch["pad_mask"][i:i + 1, :kb]
+    sub["c_base"] = batch["c_base"][i:i + 1, :kb]
+    sub["K_max"] = kb
+    ws = {"Q": w["Q"][i:i + 1], "dO": w["dO"][i:i + 1], "E_k": w["E_k"][i:i + 1, :kb], "E_v": w["E_v"][i:i + 1, :kb],
+          "W_pe": w["W_pe"]}
+    return sub, ws
+
+
+def _against_oracle(mb, sub, ws, tol):
+    from oracle import ema_oracle as orc
+    tc = _run(mb, sub, ws, "tc_bf16")
+    unique = sub["unique_slots"].clone()
+    unique[~sub["pad_mask"]] = -1
+    f = lambda t: t.float()
+    ref = orc.flash_ema(f(ws["Q"]), sub["x"], f(ws["E_k"]), f(ws["E_v"]), f(ws["W_pe"]), sub["rhos"], sub["vocab"],
+                        unique, c_base=sub["c_base"], dO=f(ws["dO"]))
+    for k in ("O", "dQ", "dE_k", "dE_v", "dW_pe"):
+        assert rel_err(tc[k], ref[k]) < tol, (k, rel_err(tc[k], ref[k]))
+
+
+def test_config2_samples_against_the_oracle(mb):
+    """Whole samples of the full-size 46M batch, each run alone through the tensor-core kernels and through the CPU
+    oracle (fp32, all 512 steps, its real prefix state): the samples with the fewest and the most listed slots, the longest
+    prefix and the shortest fill.  Everything within 2e-2, dW_pe included (a sample's own contribution)."""
+    from mathbrain_b200 import synth
+    batch = synth.make_chunk_batch(2024, 56, 512, 64)
+    w = synth.make_layer_weights(7, 56, batch["K_max"], 512, 64, 512, 8, std=0.02, dtype=torch.bfloat16)
+    steps = torch.arange(512).view(1, 1, 512, 1)
+    w["dO"] = w["dO"] * (steps < batch["fill"].view(-1, 1, 1, 1)).to(w["dO"].dtype)       # padded steps are loss-masked
+    kb = batch["pad_mask"].sum(1)
+    cmax = batch["c_base"].abs().amax(dim=(1, 2))
+    picks = {int(kb.argmin()), int(kb.argmax()), int(cmax.argmax()), int(batch["fill"].argmin())}
+    assert len(picks) >= 3
+    for i in sorted(picks):
+        sub, ws = _sample_inputs(batch, w, i)
+        _against_oracle(mb, sub, ws, TOL_BF16)
+
+
+def test_config3_sample_against_the_oracle(mb):
+    """One whole sample of the long-chunk batch (T=4096, N=128, bursty repeats) against the CPU oracle."""
+    from mathbrain_b200 import synth
+    batch = synth.make_chunk_batch(31, 8, 4096, 128, bursty=True)
+    w = synth.make_layer_weights(9, 8, batch["K_max"], 512, 128, 4096, 8, std=0.02, dtype=torch.bfloat16)
+    steps = torch.arange(4096).view(1, 1, 4096, 1)
+    w["dO"] = w["dO"] * (steps < batch["fill"].view(-1, 1, 1, 1)).to(w["dO"].dtype)      # padded steps are loss-masked
+    i = int(batch["pad_mask"].sum(1).argmin())           # the sample with the fewest slots keeps the oracle in seconds
+    sub, ws = _sample_inputs(batch, w, i)
+    _against_oracle(mb, sub, ws, TOL_BF16)
+
+
+def test_config4_decode_window_against_the_oracle(mb):
+    """Streaming decode at the full vocabulary: 64 steps of one sequence with thousands of seen slots, tensor-core attend
+    against the oracle's dense step on the active slots."""
+    from oracle import ema_oracle as orc
+    from mathbrain_b200 import synth
+    from mathbrain_b200.decode import DecodeState
+    g = torch.Generator().manual_seed(11)
+    B, V, N, H, K = 1, synth.VOCAB, 64, 8, 3000
+    D = 64 * H
+    rhos = synth.make_rhos(N)
+    st = DecodeState(B, V, rhos.cuda(), capacity=K + 128)
+    seen = torch.randperm(V, generator=g)[:K]
+    state = torch.zeros(B, V, N)
+    last = torch.full((B, V), -1, dtype=torch.long)
+    state[0, seen] = torch.rand(K, N, generator=g) * 3 + 1
+    last[0, seen] = torch.randint(0, 8192, (K,), generator=g)
+    st.active[0, :K] = seen.to(torch.int32).cuda()
+    st.last_t[0, seen.cuda()] = last[0, seen].to(torch.int32).cuda()
+    st.state[0, seen.cuda()] = state[0, seen].cuda()
+    st.n_active.fill_(K)
+    E_k = (torch.randn(V, D, generator=g) * 0.02).to(torch.bfloat16)
+    E_v = (torch.randn(V, D, generator=g) * 0.02).to(torch.bfloat16)
+    W = torch.randn(N, D, generator=g) * 0.02
+    E_kc, E_vc, Wc = E_k.cuda(), E_v.cuda(), W.cuda()
+    toks = torch.from_numpy(synth.Zipf(V).draw(np.random.Generator(np.random.PCG64(3)), 64)).view(64, 1)
+    for j in range(64):
+        t = 8192 + j
+        q = (torch.randn(B, H, 64, generator=g) * 0.02).to(torch.bfloat16)
+        O = st.attend(q.cuda(), E_kc, E_vc, Wc, t, mode="tc_bf16")
+        st.update(toks[j].cuda(), t)
+        O_ref, _ = orc.decode_step(state, last, t, toks[j], q.float(), E_k.float(), E_v.float(), W, rhos, V)
+        assert rel_err(O.cpu(), O_ref) < TOL_BF16, j
+    st.check_overflow()
+    assert st.device_status() == 0
