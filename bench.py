@@ -27,6 +27,11 @@ if ROOT not in sys.path:
 
 CFG = dict(B=56, T=512, D=512, H=8, N=64, L=6, V=50257, min_hl=1024.0, max_hl=4096.0, max_prefix=8192, min_fill=64)
 METRIC = "flash_ema_fwd_bwd_tokens_per_s"
+# DRAM traffic of the attention backward, bytes per slot-step (one listed slot of one sample at one time step):
+# dram__bytes_read.sum + dram__bytes_write.sum of one profiler capture of the B=16 profile case divided by that
+# launch's slot-steps.  Traffic grows in proportion to the slot-steps, so a full launch is this figure times its own.
+BWD_DRAM_BYTES_PER_SLOT_STEP = 22.7
+DECODE = dict(B=64, K0=3000, capacity=4608, steps=2048, warmup=16)
 
 
 def peaks():
@@ -144,8 +149,8 @@ class HotPath:
         kb = self.host["pad_mask"].sum(1).double()
         self.slot_steps = float((kb * c["T"]).sum())          # sum_b T * K_b   (all T steps are computed)
         self.tokens = B * T
-        self.result = torch.zeros(1, device=dev)
-        self.result_host = torch.zeros(1).pin_memory()
+        self.result = torch.zeros(2, device=dev)             # [sum of the outputs, kernel status word]
+        self.result_host = torch.zeros(2).pin_memory()
 
     def zero_grads(self):
         for lay in self.layers:
@@ -192,7 +197,8 @@ class HotPath:
                     grads = [lay[k].grad for lay in self.layers for k in ("E_k", "E_v")]
                     self.dE_vocab = dp.slot_embedding_grad(grads, unique_tensor, c["V"], out=self.dE_vocab)
                 dp.allreduce_gradients(self.params, extra=[self.dE_vocab])
-            self.result.copy_(acc.reshape(1))
+            self.result[:1].copy_(acc.reshape(1))
+            self.result[1:].copy_(mb.ops.status_word(self.dev))
 
     def step_resident(self):
         self.step(self.resident)
@@ -219,6 +225,8 @@ class HotPath:
         self.step(batch)
         self.result_host.copy_(self.result, non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        if self.result_host[1] != 0:        # the kernels' sticky status word, read back with the result every step
+            raise RuntimeError("a bounded wait inside a kernel gave up: status 0x%x" % int(self.result_host[1]))
         return float(self.result_host[0])
 
 
@@ -308,19 +316,17 @@ def aux_case(args):
     print(json.dumps(out))
 
 
-def decode_case(args):
-    """Streaming decode (64 sequences, V=50257, N=64, 4096 slots seen per sequence, 6 layers): device time per step
-    of [6 x attend, update].  Weights and projected slot embeddings are random; no benchmark line."""
-    import mathbrain_b200 as mb
+def make_decode_setup(dev, K, capacity, n_tokens, mode):
+    """Streaming-decode workload: 64 sequences with a resident [V, N] fp32 state each, K distinct slots already seen
+    per sequence at random earlier steps, 6 layers of projected slot embeddings (bf16, random), Zipf(1.1) tokens."""
+    import numpy as np
     from mathbrain_b200 import synth
     from mathbrain_b200.decode import DecodeState
     c = CFG
-    dev = torch.device("cuda", 0)
-    B, V, N, H, D, L, K = 64, c["V"], c["N"], c["H"], c["D"], c["L"], 4096
+    B, V, N, H, D, L = DECODE["B"], c["V"], c["N"], c["H"], c["D"], c["L"]
     g = torch.Generator().manual_seed(0)
     rhos = synth.make_rhos(N, c["min_hl"], c["max_hl"]).to(dev)
-    st = DecodeState(B, V, rhos, capacity=K + 512)
-    # warm state: every sequence has seen K distinct slots at random earlier steps
+    st = DecodeState(B, V, rhos, capacity=capacity, device=dev)
     for b in range(B):
         seen = torch.randperm(V, generator=g)[:K]
         st.active[b, :K] = seen.to(torch.int32).to(dev)
@@ -331,11 +337,60 @@ def decode_case(args):
     E_v = [(torch.randn(V, D, generator=g) * 0.02).to(torch.bfloat16).to(dev) for _ in range(L)]
     W = [(torch.randn(N, D, generator=g) * 0.02).to(dev) for _ in range(L)]
     q = (torch.randn(B, H, D // H, generator=g) * 0.02).to(torch.bfloat16).to(dev)
-    zipf = synth.Zipf(V)
-    import numpy as np
     rng = np.random.Generator(np.random.PCG64(1))
-    toks = torch.from_numpy(zipf.draw(rng, B * 40).reshape(40, B)).to(dev)
-    mode = "tc_bf16" if args.mode == "tc_bf16" else "fp32"
+    toks = torch.from_numpy(synth.Zipf(V).draw(rng, B * n_tokens).reshape(n_tokens, B)).to(dev)
+    return dict(st=st, E_k=E_k, E_v=E_v, W=W, q=q, toks=toks, mode="tc_bf16" if mode == "tc_bf16" else "fp32")
+
+
+def decode_bytes_per_step(mean_active):
+    c = CFG    # state row + last_t + E_k/E_v rows per active slot, per sequence and layer
+    return DECODE["B"] * c["L"] * mean_active * (c["N"] * 4 + 4 + 2 * c["D"] * 2)
+
+
+def decode_bench(dev, mode):
+    """The streaming-decode configuration: 64 sequences, one Zipf(1.1) token per step, every step = 6 x attend over the
+    slots seen so far + the scan update, replayed from one CUDA graph; 2048 steps timed with CUDA events."""
+    d = DECODE
+    s = make_decode_setup(dev, d["K0"], d["capacity"], d["steps"] + d["warmup"], mode)
+    st, L = s["st"], CFG["L"]
+    st.use_device_step(8192)
+    tok_static = s["toks"][0].clone()
+    graph, _, _ = st.capture_step([s["q"]] * L, s["E_k"], s["E_v"], s["W"], tok_static, mode=s["mode"])
+    for i in range(d["warmup"]):
+        tok_static.copy_(s["toks"][i])
+        graph.replay()
+    n0 = float(st.n_active.float().mean())
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(d["warmup"], d["warmup"] + d["steps"]):
+        tok_static.copy_(s["toks"][i])
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    st.check_overflow()
+    if st.device_status():
+        raise RuntimeError("decode: a bounded wait inside the attend kernel gave up (status 0x%x)" % st.device_status())
+    ms = e0.elapsed_time(e1) / d["steps"]
+    n1 = float(st.n_active.float().mean())
+    nbytes = decode_bytes_per_step(0.5 * (n0 + n1))
+    pk = peaks()
+    return {"workload": "streaming decode: 64 sequences, resident [50257 x 64] fp32 state each, 6 x attend + update per step",
+            "value": d["B"] / ms * 1000.0, "unit": "tokens/s", "steps": d["steps"], "warmup": d["warmup"],
+            "ms_per_step": ms, "mode": s["mode"], "launch": "one CUDA graph replay per step",
+            "active_slots_per_sequence": [n0, n1], "gpu_launches_per_step": L + 2,
+            "roofline": {"bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": pk["hbm"], "unit": "GB/s",
+                         "frac": nbytes / ms / 1e6 / pk["hbm"], "bytes_per_step": nbytes}}
+
+
+def decode_case(args):
+    """Streaming decode (64 sequences, V=50257, N=64, 4096 slots seen per sequence, 6 layers): device time per step
+    of [6 x attend, update], launched one by one and replayed from a CUDA graph; no benchmark line."""
+    import mathbrain_b200 as mb
+    dev = torch.device("cuda", 0)
+    K = 4096
+    s = make_decode_setup(dev, K, K + 512, 40, args.mode)
+    st, q, E_k, E_v, W, toks, mode, L = s["st"], s["q"], s["E_k"], s["E_v"], s["W"], s["toks"], s["mode"], CFG["L"]
     o_tc = st.attend(q, E_k[0], E_v[0], W[0], 8192, mode=mode)
     o_32 = st.attend(q, E_k[0], E_v[0], W[0], 8192, mode="fp32")
     diff = float((o_tc - o_32).abs().max() / o_32.abs().max())
@@ -367,10 +422,102 @@ def decode_case(args):
         gtimes.append(e0.elapsed_time(e1))
     st.check_overflow()
     ms_graph = sorted(gtimes[4:])[len(gtimes[4:]) // 2]
-    bytes_step = B * L * K * (N * 4 + 4 + 2 * D * 2)            # state rows + last_t + E_k/E_v rows per active slot
-    print(json.dumps({"profile_case": "decode", "mode": mode, "rel_diff_vs_fp32_kernel": diff, "sequences": B, "active_slots": K, "layers": L, "ms_per_step": ms, "ms_per_step_cuda_graph": ms_graph,
-                      "tokens_per_s": B / ms * 1000.0, "algorithmic_GB_per_step": bytes_step / 1e9,
-                      "achieved_GBps": bytes_step / ms / 1e6, "hbm_peak_GBps": peaks()["hbm"]}))
+    bytes_step = decode_bytes_per_step(K)
+    print(json.dumps({"profile_case": "decode", "mode": mode, "rel_diff_vs_fp32_kernel": diff, "sequences": DECODE["B"],
+                      "active_slots": K, "layers": L, "ms_per_step": ms, "ms_per_step_cuda_graph": ms_graph,
+                      "tokens_per_s": DECODE["B"] / ms_graph * 1000.0, "algorithmic_GB_per_step": bytes_step / 1e9,
+                      "achieved_GBps": bytes_step / ms_graph / 1e6, "hbm_peak_GBps": peaks()["hbm"],
+                      "status": st.device_status()}))
+
+
+def reference_package():
+    """Import the unmodified reference package from baseline/_ref (placed there by baseline/install_reference.py; it
+    travels with the working tree but is not committed).  Returns (module, None) or (None, reason)."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isfile(os.path.join(ref, "mathbrain", "triton_flash_ema.py")):
+        return None, "baseline/_ref/mathbrain is absent (run baseline/install_reference.py where the reference is at hand)"
+    for k in [k for k in sys.modules if k == "mathbrain" or k.startswith("mathbrain.")]:
+        del sys.modules[k]
+    sys.path.insert(0, ref)
+    try:
+        import importlib
+        tfe = importlib.import_module("mathbrain.triton_flash_ema")
+    except Exception as e:                                     # noqa: BLE001
+        return None, "import of the reference failed: %r" % (e,)
+    finally:
+        sys.path.remove(ref)
+    if not getattr(tfe, "HAS_TRITON", False):
+        return None, "the reference reports HAS_TRITON = False (triton is not importable)"
+    return tfe, None
+
+
+def triton_case(args):
+    """The reference's own Triton kernels on this GPU, on the B=16 one-layer profile case (fp32 operands, which is what
+    its autograd function casts to), timed with CUDA events beside this library's kernels on the same tensors, and the
+    outputs of the two compared.  Prints one JSON line; `unavailable` with the reason when the reference cannot run."""
+    import mathbrain_b200 as mb
+    from mathbrain_b200 import synth
+    tfe, why = reference_package()
+    if tfe is None:
+        print(json.dumps({"profile_case": "triton", "unavailable": why}))
+        return
+    c = CFG
+    dev = torch.device("cuda", 0)
+    B = int(os.environ.get("MBEMA_TRITON_B", "16"))
+    host = synth.make_chunk_batch(1000, B, c["T"], c["N"], vocab=c["V"], max_prefix=c["max_prefix"],
+                                  min_fill=c["min_fill"], min_hl=c["min_hl"], max_hl=c["max_hl"])
+    K = host["K_max"]
+    w = synth.make_layer_weights(1, B, K, c["D"], c["N"], c["T"], c["H"])
+    x = host["x"].to(dev)
+    unique = host["unique_slots"].clone()
+    unique[~host["pad_mask"]] = -1
+    unique = unique.to(dev)
+    rhos, c_base, dO = host["rhos"].to(dev), host["c_base"].to(dev), w["dO"].to(dev)
+
+    def leaves():
+        return [w[k].to(dev).requires_grad_(True) for k in ("Q", "E_k", "E_v", "W_pe")]
+
+    def run(fn_cls, bounds, reps):
+        fwd, bwd, out = [], [], None
+        for _ in range(reps):
+            Q, Ek, Ev, W = leaves()
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            e[0].record()
+            O = fn_cls.apply(Q, x, Ek, Ev, W, rhos, c["V"], unique, K, bounds, True)
+            e[1].record()
+            O.backward(dO)
+            e[2].record()
+            torch.cuda.synchronize()
+            fwd.append(e[0].elapsed_time(e[1]))
+            bwd.append(e[1].elapsed_time(e[2]))
+            out = dict(O=O.detach(), dQ=Q.grad, dE_k=Ek.grad, dE_v=Ev.grad, dW_pe=W.grad)
+        return min(fwd[1:] or fwd), min(bwd[1:] or bwd), out
+
+    try:
+        t0 = time.perf_counter()
+        ref_bounds = tfe.precompute_boundaries(x, unique, rhos, 64, c_init=c_base)
+        ref_fwd, ref_bwd, ref = run(tfe.FlashEMAFunction, ref_bounds, 3)
+        compile_s = time.perf_counter() - t0
+    except Exception as e:                                     # noqa: BLE001
+        print(json.dumps({"profile_case": "triton", "unavailable": "the reference's Triton kernels did not run here: %r" % (e,)}))
+        return
+
+    def rel(a, r):
+        return float((a.double() - r.double()).norm() / r.double().norm().clamp_min(1e-300))
+
+    out = {"profile_case": "triton", "B": B, "T": c["T"], "K_max": K, "triton": getattr(__import__("triton"), "__version__", "?"),
+           "slot_steps": float(host["pad_mask"].sum(1).double().sum() * c["T"]), "first_call_s": compile_s,
+           "reference_fwd_ms": ref_fwd, "reference_bwd_ms": ref_bwd, "native": {}}
+    for mode in ("fp32", "tc_bf16"):
+        for mass in ("listed_only", "full_V"):
+            for decay in (True, False):
+                with mb.options(mode=mode, inactive_mass=mass, cbase_extra_decay=decay):
+                    h = mb.precompute_boundaries(x, unique, rhos, 64, c_init=c_base)
+                    f, b, got = run(mb.FlashEMAFunction, h, 3)
+                key = "%s/%s/%s" % (mode, mass, "rho*c_base" if decay else "c_base")
+                out["native"][key] = {"fwd_ms": f, "bwd_ms": b, "rel_err_vs_reference": {k: rel(got[k], ref[k]) for k in ref}}
+    out["status"] = mb.device_status()
+    print(json.dumps(out))
 
 
 def timed(fn, steps, warmup, barrier):
@@ -463,7 +610,8 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--mode", default=os.environ.get("MBEMA_BENCH_MODE", "tc_bf16"), choices=["fp32", "tc_bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd", "long", "aux", "decode"],
+    ap.add_argument("--no-decode", action="store_true", help="skip the streaming-decode measurement (extra key `decode`)")
+    ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd", "long", "aux", "decode", "triton"],
                     help="run a small one-layer attention workload (for ncu captures) instead of the benchmark")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
@@ -482,6 +630,9 @@ def main():
         return
     if args.profile_case == "decode":
         decode_case(args)
+        return
+    if args.profile_case == "triton":
+        triton_case(args)
         return
     if args.profile_case:
         profile_case(args)
@@ -524,6 +675,10 @@ def main():
     secs_rows = timed(hp.step_resident_rows, args.steps, 1, barrier)
     # end-to-end measurement: batch copied from pinned host memory each step, result scalar read back
     secs_e2e = timed(hp.step_e2e, args.steps, 1, barrier)
+    mb.ops.check_status()               # resident steps: the status word is sticky, one read covers them all
+    decode = None
+    if world == 1 and not args.no_decode:
+        decode = decode_bench(dev, args.mode)
 
     t = torch.tensor([secs, secs_e2e, secs_skip], device=dev, dtype=torch.float64)
     if dist_on:
@@ -559,16 +714,17 @@ def main():
                             "per_sample_rows": c["B"] * hp.K},
             "clocks": clocks,
             "e2e": {"value": tokens * args.steps / secs_e2e, "unit": "tokens/s", "h2d_bytes_per_step": hp.h2d_bytes,
-                    "d2h_bytes_per_step": 4},
+                    "d2h_bytes_per_step": 8},
             "roofline": {"bound": "tensor", "kernel": "flash-EMA backward (one layer)", "achieved": ach,
                          "peak": pk["tflops"], "unit": "TFLOP/s", "frac": ach / pk["tflops"],
-                         # DRAM bytes per launch: 22.7 B per slot-step (dram__bytes_read+write of an ncu capture of
-                         # the B=16 case, 308 MB for 13.59 M slot-steps), scaled by the slot-steps of this launch
-                         "traffic": 22.7 * hp.slot_steps, "traffic_unit": "bytes/launch (scaled from profiles/flash_bwd_tc_B16_T512_N64.md)",
+                         "traffic": BWD_DRAM_BYTES_PER_SLOT_STEP * hp.slot_steps,
+                         "traffic_unit": "bytes/launch (profiler capture of the B=16 profile case, scaled by slot-steps)",
                          "peak_source": pk["src"], "flops_per_launch": flops_bwd, "ms_per_launch": avg_bwd * 1000.0,
                          "forward": {"achieved": flops_fwd / avg_fwd / 1e12, "ms_per_launch": avg_fwd * 1000.0},
                          "scan_ms": sum(scan_ms) / max(1, len(scan_ms)), "gate_ms_per_step": sum(gate_ms) / args.steps},
         }
+        if decode is not None:
+            line["decode"] = decode
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             cpu_baseline_sample(hp.host, threads, steps_t=4)

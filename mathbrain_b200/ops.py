@@ -200,6 +200,19 @@ def device_status(device=None):
     return st
 
 
+def status_word(device=None):
+    """The status of device_status() as a device tensor (int32 [1]), without synchronising: copy it to the host together
+    with a step's results and test it there."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    words = [ws[:4].view(torch.int32) for (d, _), ws in _tc_workspaces.items() if d == dev]
+    if not words:
+        return torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", dev))
+    out = words[0]
+    for w in words[1:]:
+        out = out | w
+    return out
+
+
 def check_status(device=None):
     """Raise if a tensor-core kernel reported a failed wait since the last clear_status() (synchronises)."""
     st = device_status(device)

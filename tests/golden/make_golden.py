@@ -25,7 +25,9 @@ import numpy as np
 import torch
 import torch.nn as nn
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MATHBRAIN_REFERENCE", "")
+if not REF:
+    sys.exit("usage: make_golden.py <reference checkout>  (or set MATHBRAIN_REFERENCE)")
 sys.path.insert(0, REF)
 HERE = os.path.dirname(os.path.abspath(__file__))
 

@@ -1,0 +1,156 @@
+"""The reference's own SlotTransformerLM (mathbrain/model.py, unmodified, from baseline/_ref) hosted on this library's
+operators through install_as_mathbrain(), against the same model run by the reference's PyTorch path on the CPU.
+
+The reference package is not part of this repository: baseline/install_reference.py places it under baseline/_ref/
+where a checkout is at hand, and the tests skip with that reason where it is absent."""
+import importlib
+import os
+import sys
+
+import pytest
+import torch
+
+from helpers import rel_err
+
+pytestmark = pytest.mark.gpu
+
+REF = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref")
+needs_ref = pytest.mark.skipif(not os.path.isfile(os.path.join(REF, "mathbrain", "model.py")),
+                               reason="baseline/_ref/mathbrain is absent (baseline/install_reference.py places it)")
+
+
+def _import_model(hosted):
+    """mathbrain.model of the reference, with its own operator modules (hosted=False) or with this library's
+    operators registered under their names first (hosted=True)."""
+    for k in [k for k in sys.modules if k == "mathbrain" or k.startswith("mathbrain.")]:
+        del sys.modules[k]
+    if hosted:
+        import mathbrain_b200
+        mathbrain_b200.install_as_mathbrain()
+    sys.path.insert(0, REF)
+    try:
+        return importlib.import_module("mathbrain.model")
+    finally:
+        sys.path.remove(REF)
+
+
+def _batch(seed, B, T, vocab, n_pad=0):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randint(0, vocab, (B, T), generator=g)
+    y = torch.randint(0, vocab, (B, T), generator=g)
+    lists = [torch.unique(x[b]) for b in range(B)]              # sorted distinct tokens of every chunk
+    K = max(len(u) for u in lists) + n_pad
+    unique = torch.zeros(B, K, dtype=torch.long)                # the collate function pads with token 0
+    mask = torch.zeros(B, K, dtype=torch.bool)
+    for b, u in enumerate(lists):
+        unique[b, :len(u)] = u
+        mask[b, :len(u)] = True
+    return x, y, unique, mask
+
+
+def _loss_and_grads(model, x, y, **kw):
+    model.zero_grad(set_to_none=True)
+    logits = model(x, **kw)
+    loss = torch.nn.functional.cross_entropy(logits.float().view(-1, logits.shape[-1]), y.view(-1))
+    loss.backward()
+    return logits.detach().float().cpu(), {n: p.grad.detach().float().cpu() for n, p in model.named_parameters()}
+
+
+CASES = [   # vocab, T, B, pad columns
+    (211, 96, 3, 2),
+    (12, 20, 2, 0),      # fewer than 16 listed slots: the model forces K_max to 16 over a narrower slot list
+]
+
+
+@needs_ref
+@pytest.mark.parametrize("vocab,T,B,n_pad", CASES)
+@pytest.mark.parametrize("mode,tol", [("fp32", 1e-4), ("auto", 2e-2)])
+def test_reference_model_hosted_on_native_operators(vocab, T, B, n_pad, mode, tol):
+    import mathbrain_b200 as mb
+    cfg = dict(vocab_size=vocab, d_model=128, n_layers=2, n_heads=2, N=64, dropout=0.0, min_hl=2.0, max_hl=64.0)
+    x, y, unique, mask = _batch(vocab + T, B, T, vocab, n_pad)
+
+    ref_mod = _import_model(hosted=False)
+    torch.manual_seed(0)
+    ref_model = ref_mod.SlotTransformerLM(**cfg)               # CPU, fp32: the reference's PyTorch path over the whole vocabulary
+    state = {k: v.clone() for k, v in ref_model.state_dict().items()}
+    for layer in ref_model.layers:     # the reference's CPU loop updates the state in place after projecting it: give the
+        pe = layer.attn.pe_proj        # projection a private copy of its input so that autograd accepts the graph
+        pe.forward = (lambda inp, pe=pe: torch.nn.functional.linear(inp.clone(), pe.weight))
+    ref_logits, ref_grads = _loss_and_grads(ref_model, x, y)
+
+    hosted_mod = _import_model(hosted=True)
+    assert hosted_mod.compute_query_ema_history is mb.compute_query_ema_history
+    assert hosted_mod.FlashEMAFunction is mb.FlashEMAFunction
+    model = hosted_mod.SlotTransformerLM(**cfg)
+    model.load_state_dict({k: v.float() for k, v in state.items()})
+    model = model.cuda()
+    N = cfg["N"]
+    c_base = torch.zeros(B, unique.shape[1], N)
+    runs = {"chunk-local slot list (no loader metadata)": {},
+            "loader slot list, pad mask and zero prefix state": dict(unique_slots=unique.cuda(), pad_mask=mask.cuda(),
+                                                                    c_base=c_base.cuda())}
+    with mb.options(mode=mode, inactive_mass="full_V", cbase_extra_decay=False):
+        for name, kw in runs.items():
+            logits, grads = _loss_and_grads(model, x.cuda(), y.cuda(), **kw)
+            assert rel_err(logits, ref_logits) < tol, (name, "logits")
+            for n, gref in ref_grads.items():
+                if float(gref.abs().max()) == 0.0:
+                    continue
+                assert rel_err(grads[n], gref) < tol, (name, n, rel_err(grads[n], gref))
+    assert mb.device_status() == 0
+
+
+@needs_ref
+def test_default_mode_takes_the_tensor_core_kernels():
+    import mathbrain_b200 as mb
+    assert mb.get_options()["mode"] == "auto"
+    assert mb.ops._flash_mode(8, 64, 500) == mb._lib.MODE_TC_BF16
+    assert mb.ops._flash_mode(2, 64, 12) in (mb._lib.MODE_TC_BF16, mb._lib.MODE_FP32)
+    assert mb.ops._flash_mode(3, 64, 500) == mb._lib.MODE_FP32          # odd head count: fp32 kernels, no error
+    assert mb.ops._flash_mode(8, 16, 500) == mb._lib.MODE_FP32
+
+
+@needs_ref
+@pytest.mark.parametrize("mode,tol", [("fp32", 1e-2), ("tc_bf16", 2e-2)])
+def test_operators_against_the_reference_triton_kernels(mode, tol):
+    """The reference's GPU operators themselves (Triton, compiled for this GPU) on the same tensors.  Their softmax runs
+    over the listed slots only, which is this library's `inactive_mass="listed_only"`; their fp32 tl.dot runs in tf32,
+    hence 1e-2 for the fp32 kernels."""
+    import mathbrain_b200 as mb
+    from mathbrain_b200 import synth
+    for k in [k for k in sys.modules if k == "mathbrain" or k.startswith("mathbrain.")]:
+        del sys.modules[k]
+    sys.path.insert(0, REF)
+    try:
+        tfe = importlib.import_module("mathbrain.triton_flash_ema")
+        teq = importlib.import_module("mathbrain.triton_ema_query")
+    finally:
+        sys.path.remove(REF)
+    if not (tfe.HAS_TRITON and teq.HAS_TRITON):
+        pytest.skip("triton is not importable here")
+    B, T, N, H, D, V = 3, 200, 64, 2, 128, 50257
+    b = synth.make_chunk_batch(5, B, T, N, vocab=V, max_prefix=500, min_fill=T, min_hl=1024.0, max_hl=4096.0)
+    K = b["K_max"]
+    w = synth.make_layer_weights(2, B, K, D, N, T, H, std=0.05)
+    dev = "cuda"
+    x, rhos, c_base = b["x"].to(dev), b["rhos"].to(dev), b["c_base"].to(dev)
+    unique = b["unique_slots"].clone()
+    unique[~b["pad_mask"]] = -1
+    unique = unique.to(dev)
+
+    def run(mod_fn, bounds):
+        leaves = [w[k].to(dev).requires_grad_(True) for k in ("Q", "E_k", "E_v", "W_pe")]
+        O = mod_fn.apply(leaves[0], x, leaves[1], leaves[2], leaves[3], rhos, V, unique, K, bounds, True)
+        O.backward(w["dO"].to(dev))
+        return [O.detach()] + [t.grad for t in leaves]
+
+    ref = run(tfe.FlashEMAFunction, tfe.precompute_boundaries(x, unique, rhos, 64, c_init=c_base))
+    ref_scan = teq.compute_query_ema_history(x, rhos, V, c_base, b["unique_slots"].to(dev))
+    with mb.options(mode=mode, inactive_mass="listed_only", cbase_extra_decay=True):
+        got = run(mb.FlashEMAFunction, mb.precompute_boundaries(x, unique, rhos, 64, c_init=c_base))
+    for name, a, r in zip(("O", "dQ", "dE_k", "dE_v", "dW_pe"), got, ref):
+        assert rel_err(a.cpu(), r.cpu()) < tol, (name, rel_err(a.cpu(), r.cpu()))
+    scan = mb.compute_query_ema_history(x, rhos, V, c_base, b["unique_slots"].to(dev))
+    assert rel_err(scan.cpu(), ref_scan.cpu()) < 1e-5
+    assert mb.device_status() == 0
