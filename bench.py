@@ -98,15 +98,22 @@ class ClockSampler:
 WORKLOAD = "46M-config hot path: scan + snapshots + 6 x (query gate, flash-EMA fwd, bwd of both)"
 
 
-def make_rank_batch(rank, world):
+def make_rank_batch(rank, world, data="chunks"):
     """The global batch of the 8-GPU configuration (8 x B samples) is drawn identically on every rank and split into
     8 cost-balanced shards (cost = listed slots; all T steps are computed).  Rank r runs shard r at every N, so the
-    per-GPU work does not change with N and the slowest rank stays close to the mean."""
+    per-GPU work does not change with N and the slowest rank stays close to the mean.
+    data "chunks": one chunk per document with a uniform 0..8192-token prefix (the single-GPU configuration);
+    "documents": lognormal document lengths (median 1500, sigma 1.0) chunked per document, every chunk with the state
+    of its own document's prefix (the 8-GPU configuration)."""
     from mathbrain_b200 import dp, synth
     c = CFG
     n_shards = max(8, world)
-    host = synth.make_chunk_batch(1000, c["B"] * n_shards, c["T"], c["N"], vocab=c["V"], max_prefix=c["max_prefix"],
-                                  min_fill=c["min_fill"], min_hl=c["min_hl"], max_hl=c["max_hl"])
+    if data == "documents":
+        host = synth.make_document_batch(1000, c["B"] * n_shards, c["T"], c["N"], vocab=c["V"], min_hl=c["min_hl"],
+                                         max_hl=c["max_hl"])
+    else:
+        host = synth.make_chunk_batch(1000, c["B"] * n_shards, c["T"], c["N"], vocab=c["V"], max_prefix=c["max_prefix"],
+                                      min_fill=c["min_fill"], min_hl=c["min_hl"], max_hl=c["max_hl"])
     shards = dp.balanced_shards(host["pad_mask"].sum(1).tolist(), n_shards)
     return synth.select_samples(host, shards[rank])
 
@@ -114,13 +121,13 @@ def make_rank_batch(rank, world):
 class HotPath:
     """Device-resident operands of the 6-layer hot path and the step function."""
 
-    def __init__(self, rank, dev, mode, world=1):
+    def __init__(self, rank, dev, mode, world=1, data="chunks", dist_on=False):
         import mathbrain_b200 as mb
         from mathbrain_b200 import synth
         self.mb = mb
         self.dev = dev
         c = CFG
-        self.host = make_rank_batch(rank, world)
+        self.host = make_rank_batch(rank, world, data)
         self.K = self.host["K_max"]
         self.pinned = {k: self.host[k].pin_memory() for k in ("x", "unique_slots", "pad_mask", "c_base", "fill")}
         self.h2d_bytes = sum(t.numel() * t.element_size() for t in self.pinned.values())
@@ -143,8 +150,17 @@ class HotPath:
             self.layers.append(lay)
         self.params = [p for lay in self.layers for m in (lay["pe"], lay["ln"], lay["qp"]) for p in m.parameters()]
         self.mode = mode
-        self.dist = False
+        self.dist = dist_on
         self.dE_vocab = None
+        self.buckets = None
+        self.phases = None           # {name: [(event, event), ...]} while per-phase timing is on
+        if dist_on:
+            from mathbrain_b200 import dp
+            # one flat fp32 gradient bucket per layer (the parameters' .grad are views into it) and the
+            # vocabulary-sized slot-embedding gradient all layers accumulate into
+            self.buckets = [dp.GradBucket([p for m in (lay["pe"], lay["ln"], lay["qp"]) for p in m.parameters()])
+                            for lay in self.layers]
+            self.dE_vocab = torch.zeros(c["V"], D, dtype=torch.float32, device=dev)
         self.resident = {k: v.to(dev) for k, v in self.pinned.items()}
         kb = self.host["pad_mask"].sum(1).double()
         self.slot_steps = float((kb * c["T"]).sum())          # sum_b T * K_b   (all T steps are computed)
@@ -155,8 +171,28 @@ class HotPath:
     def zero_grads(self):
         for lay in self.layers:
             lay["x_q"].grad = lay["E_k"].grad = lay["E_v"].grad = None
+        if self.buckets is not None:
+            if not self.dist:            # otherwise zeroed inside the step's exchange phase (timed as such)
+                for bk in self.buckets:
+                    bk.zero()
+            return
         for p in self.params:
             p.grad = None
+
+    def _phase(self, name):
+        """CUDA-event pair around a phase of the gradient exchange (on the launching stream)."""
+        class _P:
+            def __enter__(q):
+                if self.phases is not None:
+                    q.e0 = torch.cuda.Event(enable_timing=True)
+                    q.e0.record()
+
+            def __exit__(q, *exc):
+                if self.phases is not None:
+                    e1 = torch.cuda.Event(enable_timing=True)
+                    e1.record()
+                    self.phases.setdefault(name, []).append((q.e0, e1))
+        return _P()
 
     def step(self, batch, skip_padding=False, shared_rows=False):
         mb, c = self.mb, CFG
@@ -172,7 +208,12 @@ class HotPath:
             handle = mb.precompute_boundaries(x, unique_tensor, self.rhos, 64, c_init=c_base,
                                               seq_lens=batch["fill"] if skip_padding else None)
             acc = None
-            for lay in self.layers:
+            if self.dist:
+                with self._phase("zero_buffers"):
+                    self.dE_vocab.zero_()
+                    for bk in self.buckets:
+                        bk.zero()
+            for li, lay in enumerate(self.layers):
                 with torch.autocast("cuda", dtype=torch.bfloat16):
                     Q_t = mb.fused_apply_symmetric_query_gating(lay["x_q"], C_seq, lay["pe"], lay["ln"], lay["qp"], True)
                     Q_mha = Q_t.view(B, T, H, D // H).transpose(1, 2).contiguous()
@@ -186,17 +227,24 @@ class HotPath:
                 O.backward(lay["dO"])
                 s = O.detach().float().sum()
                 acc = s if acc is None else acc + s
+                if self.dist:
+                    # this layer's gradients are complete: its slot gradients go into the vocabulary-sized table (one
+                    # pass over dE_k and dE_v) and its parameter bucket goes to NCCL, which reduces it on its own
+                    # stream while the next layers run
+                    with self._phase("slot_grad_scatter"):
+                        if shared_rows:      # row r belongs to token self.row_tokens[r]
+                            mb.slot_grad_scatter(lay["E_k_rows"].grad, lay["E_v_rows"].grad, self.row_tokens, self.dE_vocab)
+                        else:
+                            mb.slot_grad_scatter(lay["E_k"].grad, lay["E_v"].grad, unique_tensor, self.dE_vocab)
+                    with self._phase("bucket_issue"):
+                        self.buckets[li].all_reduce_async()
             if self.dist:
-                from mathbrain_b200 import dp
-                if shared_rows:      # row r belongs to token self.row_tokens[r]
-                    rg = sum(lay[k].grad.float() for lay in self.layers for k in ("E_k_rows", "E_v_rows"))
-                    if self.dE_vocab is None:
-                        self.dE_vocab = torch.zeros(c["V"], D, dtype=torch.float32, device=self.dev)
-                    self.dE_vocab.zero_().index_add_(0, self.row_tokens, rg)
-                else:
-                    grads = [lay[k].grad for lay in self.layers for k in ("E_k", "E_v")]
-                    self.dE_vocab = dp.slot_embedding_grad(grads, unique_tensor, c["V"], out=self.dE_vocab)
-                dp.allreduce_gradients(self.params, extra=[self.dE_vocab])
+                import torch.distributed as dist
+                with self._phase("embedding_grad_all_reduce_and_waits"):
+                    h = dist.all_reduce(self.dE_vocab, async_op=True)
+                    for bk in self.buckets:
+                        bk.wait()
+                    h.wait()
             self.result[:1].copy_(acc.reshape(1))
             self.result[1:].copy_(mb.ops.status_word(self.dev))
 
@@ -520,6 +568,32 @@ def triton_case(args):
     print(json.dumps(out))
 
 
+def exchange_phases(hp, steps, barrier, dev):
+    """Where a data-parallel step spends its time beyond the single-GPU work: the same resident step timed with the
+    exchange (CUDA-event pairs around each phase, on the launching stream) and without it, all as the max over ranks.
+    `exposed_ms` is what the exchange adds to the step; the phase entries are the stream time between their events
+    (for the final entry that includes waiting for the collectives handed to NCCL earlier)."""
+    import torch.distributed as dist
+    hp.phases = {}
+    secs_with = timed(hp.step_resident, steps, 1, barrier)
+    torch.cuda.synchronize()
+    phases = {k: sum(a.elapsed_time(b) for a, b in v[-steps * (len(v) // (steps + 1)):]) / steps for k, v in hp.phases.items()}
+    hp.phases = None
+    hp.dist = False
+    secs_without = timed(hp.step_resident, steps, 1, barrier)
+    hp.dist = True
+    names = sorted(phases)
+    t = torch.tensor([secs_with / steps * 1e3, secs_without / steps * 1e3] + [phases[k] for k in names], device=dev,
+                     dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    out = {"step_ms": float(t[0]), "compute_only_ms": float(t[1]), "exposed_ms": float(t[0] - t[1]),
+           "phases_ms_per_step": {k: float(t[2 + i]) for i, k in enumerate(names)},
+           "bytes_all_reduced_per_step": int(hp.dE_vocab.numel() * 4 + sum(b.flat.numel() * 4 for b in hp.buckets)),
+           "note": "max over ranks; parameter buckets are reduced per layer while later layers run, the "
+                   "vocabulary-sized slot-embedding gradient once after the last layer"}
+    return out
+
+
 def timed(fn, steps, warmup, barrier):
     for _ in range(warmup):
         fn()
@@ -610,6 +684,8 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--mode", default=os.environ.get("MBEMA_BENCH_MODE", "tc_bf16"), choices=["fp32", "tc_bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-documents", action="store_true",
+                    help="skip the measurement on the 8-GPU configuration's document data (extra key `documents`)")
     ap.add_argument("--no-decode", action="store_true", help="skip the streaming-decode measurement (extra key `decode`)")
     ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd", "long", "aux", "decode", "triton"],
                     help="run a small one-layer attention workload (for ncu captures) instead of the benchmark")
@@ -649,8 +725,7 @@ def main():
         def barrier():
             return None
 
-    hp = HotPath(rank, dev, args.mode, world)
-    hp.dist = dist_on
+    hp = HotPath(rank, dev, args.mode, world, data="chunks", dist_on=dist_on)
     tel = mb.ops.telemetry
 
     sampler = ClockSampler(local_rank)
@@ -684,6 +759,26 @@ def main():
     if dist_on:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     secs, secs_e2e, secs_skip = float(t[0]), float(t[1]), float(t[2])
+    dp_info = exchange_phases(hp, args.steps, barrier, dev) if dist_on else None
+    documents = None
+    if not args.no_documents:
+        # the 8-GPU configuration's data (lognormal documents chunked per document): rank r runs shard r of the same
+        # 448-chunk global batch at every N, so value(N) / (N * value(1)) of THIS key is like for like
+        n_tok = hp.tokens * world
+        del hp.layers[:]
+        hp_doc = HotPath(rank, dev, args.mode, world, data="documents", dist_on=dist_on)
+        secs_doc = timed(hp_doc.step_resident, args.steps, 2, barrier)
+        td = torch.tensor([secs_doc], device=dev, dtype=torch.float64)
+        if dist_on:
+            dist.all_reduce(td, op=dist.ReduceOp.MAX)
+        documents = {"value": n_tok * args.steps / float(td[0]), "unit": "tokens/s",
+                     "ms_per_step": float(td[0]) / args.steps * 1000.0,
+                     "data": "lognormal document lengths (median 1500, sigma 1.0), chunked per document, c_base from the "
+                             "document's own prefix; 448-chunk global batch in 8 cost-balanced shards, rank r runs shard r",
+                     "rank0_K_max": hp_doc.K, "rank0_mean_slots": hp_doc.slot_steps / (CFG["B"] * CFG["T"])}
+        if dist_on:
+            documents["dp"] = exchange_phases(hp_doc, args.steps, barrier, dev)
+        mb.ops.check_status()
 
     if rank == 0:
         c = CFG
@@ -725,6 +820,10 @@ def main():
         }
         if decode is not None:
             line["decode"] = decode
+        if dp_info is not None:
+            line["dp"] = dp_info
+        if documents is not None:
+            line["documents"] = documents
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             cpu_baseline_sample(hp.host, threads, steps_t=4)

@@ -210,6 +210,17 @@ int mbema_flash_bwd_rows(const void* Q, int q_dtype, const int64_t* x, const voi
                          void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Slot-gradient scatter: out[slots[r], :] += dE_a[r, :] + dE_b[r, :] for every row r with 0 <= slots[r] < V.
+ * Stands in for autograd's backward of F.embedding(safe_unique, E_slots) in mathbrain/model.py:63-64 (the sum, per
+ * token, of the gradients of all listed slots that hold it), taking the attention backward's dE_k and dE_v of one
+ * layer in one pass.  out is ACCUMULATED (zero it once per step, then call per layer); rows with slots[r] < 0 are
+ * skipped.   dE_a, dE_b [R, D] (dtype code; dE_b may be NULL)   slots [R] i64   out [V, D] f32.   D % 8 == 0.
+ * Reductions into out are atomic, so the summation order (and the last bits of the result) can differ between runs.
+ * ---------------------------------------------------------------------------------------------- */
+int mbema_slot_grad_scatter(const void* dE_a, const void* dE_b, int dtype, const int64_t* slots, float* out, int64_t R,
+                            int64_t D, int64_t V, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Streaming decode with resident per-sequence slot state.  The reference has no decode loop; one step is one
  * iteration of the loop body of mathbrain/flash_ema_attention.py:46-82 (attention over the slots, then the
  * "+1" of the current token) plus the query-side read of mathbrain/triton_ema_query.py:36-64.

@@ -53,6 +53,38 @@ def slot_embedding_grad(dE_list, unique_tensor, vocab, out=None):
     return out
 
 
+class GradBucket:
+    """The gradients of a group of parameters (one layer's, say) laid out in ONE flat fp32 buffer: every p.grad is a
+    view into it, so autograd accumulates straight into the bucket and the exchange needs neither a flatten copy nor
+    a copy back.  all_reduce_async() hands the bucket to the process group as soon as the group's backward has been
+    enqueued (the collective runs on the backend's own stream, behind the work already queued on the current stream)
+    and returns at once; wait() makes the current stream wait for it."""
+
+    def __init__(self, params, group=None):
+        self.params = [p for p in params if p.requires_grad]
+        n = sum(p.numel() for p in self.params)
+        dev = self.params[0].device if self.params else None
+        self.flat = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.group = group
+        self.handle = None
+        off = 0
+        for p in self.params:
+            p.grad = self.flat[off:off + p.numel()].view_as(p)
+            off += p.numel()
+
+    def zero(self):
+        self.flat.zero_()
+
+    def all_reduce_async(self):
+        self.handle = dist.all_reduce(self.flat, group=self.group, async_op=True)
+        return self.handle
+
+    def wait(self):
+        if self.handle is not None:
+            self.handle.wait()
+            self.handle = None
+
+
 def allreduce_gradients(params, extra=(), group=None):
     """Sum the .grad of `params` (flattened into one bucket) and every tensor in `extra` over all ranks, in place."""
     grads = [p.grad for p in params if p.grad is not None]

@@ -448,6 +448,28 @@ class FlashEMAFunction(torch.autograd.Function):
         return (dQ.to(qd), None, dEk.to(kd), dEv.to(vd), dW.to(wd), None, None, None, None, None, None, None)
 
 
+@_on_tensor_device
+def slot_grad_scatter(dE_k, dE_v, unique_tensor, out):
+    """out[token] += dE_k[b, k] + dE_v[b, k] for every listed slot (b, k) holding `token` (unique_tensor < 0: skipped).
+
+    dE_k, dE_v [B, K, D] (float32 or bfloat16; dE_v may be None), unique_tensor [B, K] int64, out [V, D] float32,
+    accumulated in place and returned.  This is the embedding-table side of the attention backward: what autograd's
+    backward of `F.embedding(safe_unique, E_slots)` (mathbrain/model.py:63-64) computes, for one layer's K and V rows
+    in one pass over them."""
+    _require_cuda(dE_k, dE_v, unique_tensor, out)
+    if out.dtype != torch.float32 or not out.is_contiguous():
+        raise _lib.MbemaError("slot_grad_scatter: `out` must be a contiguous float32 [V, D] tensor")
+    a = _f32_or_bf16(dE_k).contiguous()
+    b = None if dE_v is None else dE_v.to(a.dtype).contiguous()
+    ut = unique_tensor.long().contiguous()
+    R, D = ut.numel(), a.shape[-1]
+    if a.numel() != R * D or out.shape[1] != D:
+        raise _lib.MbemaError("slot_grad_scatter: shapes do not match")
+    rc = _lib.load().mbema_slot_grad_scatter(_ptr(a), _ptr(b), _dt(a), _ptr(ut), _ptr(out), R, D, out.shape[0], _stream())
+    _lib.check(rc, "mbema_slot_grad_scatter")
+    return out
+
+
 def shared_slot_rows(unique_tensor):
     """Rows for slot-embedding tables shared between samples: returns (tokens[U] int64, row_index[B,K] int32) with
     tokens the sorted distinct tokens listed anywhere in `unique_tensor` (entries < 0 are padding) and

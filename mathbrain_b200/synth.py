@@ -97,13 +97,60 @@ def make_chunk_batch(seed, B, T, N, vocab=VOCAB, max_prefix=8192, min_fill=64, b
                 fill=torch.tensor(fills, dtype=torch.int32), K_max=K, vocab=vocab)
 
 
+def make_document_batch(seed, n_samples, T, N, vocab=VOCAB, median_len=1500.0, sigma=1.0, min_hl=1024.0, max_hl=4096.0):
+    """`n_samples` chunks of synthetic documents with lognormal lengths exp(N(ln median_len, sigma)), Zipf(1.1)
+    tokens, chunked per document by the reference's rule (data.document_chunks; no chunk crosses a document, the last
+    chunk of a document is short), every chunk carrying the slot state of its own document's prefix as c_base.
+    Documents are drawn until their chunks number n_samples; same wire format as make_chunk_batch, plus `doc` and
+    `prefix_len` per sample."""
+    from .data import document_chunks
+    rng = np.random.Generator(np.random.PCG64(seed))
+    zipf = Zipf(vocab)
+    rhos = make_rhos(N, min_hl, max_hl)
+    rhos64 = rhos.double().numpy()
+    xs, uniqs, cbs, fills, docs, prefixes = [], [], [], [], [], []
+    d = 0
+    while len(xs) < n_samples:
+        n = int(math.exp(rng.normal(math.log(median_len), sigma)))
+        doc = zipf.draw(rng, max(n, 0))
+        for _, cs, ce in document_chunks([n], T):
+            if len(xs) == n_samples:
+                break
+            chunk = doc[cs:ce - 1]                       # inputs; the last token of the range is only a target
+            prefix = doc[:cs]
+            cu = np.unique(chunk)
+            hu = np.setdiff1d(np.unique(prefix), cu) if cs else np.zeros(0, np.int64)
+            keys = np.concatenate([cu, hu])
+            xs.append(np.concatenate([chunk, np.zeros(T - len(chunk), np.int64)]))
+            uniqs.append(keys)
+            cbs.append(prefix_state(prefix, keys, rhos64))
+            fills.append(len(chunk))
+            docs.append(d)
+            prefixes.append(cs)
+        d += 1
+    K = max(16, max(len(u) for u in uniqs))
+    B = n_samples
+    unique_slots = torch.zeros(B, K, dtype=torch.long)
+    pad_mask = torch.zeros(B, K, dtype=torch.bool)
+    c_base = torch.zeros(B, K, N)
+    for b in range(B):
+        k = len(uniqs[b])
+        unique_slots[b, :k] = torch.from_numpy(uniqs[b])
+        pad_mask[b, :k] = True
+        c_base[b, :k] = torch.from_numpy(cbs[b])
+    return dict(x=torch.from_numpy(np.stack(xs)), unique_slots=unique_slots, pad_mask=pad_mask, c_base=c_base, rhos=rhos,
+                fill=torch.tensor(fills, dtype=torch.int32), K_max=K, vocab=vocab,
+                doc=torch.tensor(docs, dtype=torch.int64), prefix_len=torch.tensor(prefixes, dtype=torch.int64))
+
+
 def select_samples(batch, idx):
     """The sub-batch of `make_chunk_batch` output holding samples `idx`, slot lists trimmed to the subset's longest."""
     idx = torch.as_tensor(idx, dtype=torch.long)
     K = max(16, int(batch["pad_mask"][idx].sum(1).max()))
     out = dict(batch)
-    for k in ("x", "fill"):
-        out[k] = batch[k][idx].contiguous()
+    for k in ("x", "fill", "doc", "prefix_len"):
+        if k in batch:
+            out[k] = batch[k][idx].contiguous()
     for k in ("unique_slots", "pad_mask", "c_base"):
         out[k] = batch[k][idx][:, :K].contiguous()
     out["K_max"] = K

@@ -299,3 +299,30 @@ def test_build_unique_index(mb):
     u, k = mb._build_unique_index(x.cuda(), "cuda")
     ur, kr = orc.build_unique_index(x)
     assert k == kr and torch.equal(u.cpu(), ur)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_slot_grad_scatter_matches_embedding_backward(mb, dtype):
+    """out[token] += dE_k + dE_v per listed slot: against autograd's backward of F.embedding over the same slot lists
+    (mathbrain/model.py:63-64), with padded entries (-1), tokens listed by several samples and a second accumulating
+    call."""
+    g = torch.Generator().manual_seed(11)
+    B, K, D, V = 5, 37, 64, 90
+    unique = torch.randint(0, V, (B, K), generator=g)
+    unique[:, 30:] = -1
+    unique[2, 5] = -1
+    dEk = torch.randn(B, K, D, generator=g).to(dtype)
+    dEv = torch.randn(B, K, D, generator=g).to(dtype)
+    E = torch.zeros(V, D, dtype=torch.float64, requires_grad=True)
+    rows = torch.nn.functional.embedding(unique.clamp_min(0), E)
+    mask = (unique >= 0).unsqueeze(-1).double()
+    (rows * (dEk.double() + dEv.double()) * mask).sum().backward()
+    out = torch.zeros(V, D, device="cuda")
+    mb.slot_grad_scatter(dEk.cuda(), dEv.cuda(), unique.cuda(), out)
+    assert rel_err(out.cpu(), E.grad) < 1e-6
+    mb.slot_grad_scatter(dEk.cuda(), None, unique.cuda(), out)          # accumulates; dE_v optional
+    E2 = torch.zeros(V, D, dtype=torch.float64, requires_grad=True)
+    (torch.nn.functional.embedding(unique.clamp_min(0), E2) * dEk.double() * mask).sum().backward()
+    assert rel_err(out.cpu(), E.grad + E2.grad) < 1e-6
+    with pytest.raises(mb._lib.MbemaError):
+        mb.slot_grad_scatter(dEk[..., :60].cuda(), None, unique.cuda(), torch.zeros(V, 60, device="cuda"))   # D % 8
