@@ -55,7 +55,9 @@ static int flash_fwd_impl(const void* Q, int q_dtype, const int64_t* x, const vo
     if (!Q || !x || !E_k || !E_v || !W_pe || !rhos || !unique || !tile_state || !tok_state || !kcount || !O || !LSE)
         return MBEMA_ERR_NULL;
     if (!dt_ok(q_dtype) || !dt_ok(e_dtype)) return MBEMA_ERR_DTYPE;
-    if (((uintptr_t)Q | (uintptr_t)E_k | (uintptr_t)E_v | (uintptr_t)O) & 15) return MBEMA_ERR_ALIGN;
+    if (((uintptr_t)Q | (uintptr_t)E_k | (uintptr_t)E_v | (uintptr_t)O | (uintptr_t)W_pe | (uintptr_t)tile_state |
+         (uintptr_t)tok_state) & 15)      // all of these are read with 16-byte vector or cp.async accesses
+        return MBEMA_ERR_ALIGN;
     FlashArgs a = pack(Q, q_dtype, x, E_k, E_v, e_dtype, W_pe, rhos, unique, tile_state, tok_state, kcount, seq_lens,
                        B, H, T, N, K, V_total, flags);
     a.O = O; a.LSE = LSE;
@@ -123,7 +125,8 @@ static int flash_bwd_impl(const void* Q, int q_dtype, const int64_t* x, const vo
         !dO || !dQ || !dE_k || !dE_v || !workspace)
         return MBEMA_ERR_NULL;
     if (!dt_ok(q_dtype) || !dt_ok(e_dtype) || !dt_ok(do_dtype)) return MBEMA_ERR_DTYPE;
-    if (((uintptr_t)Q | (uintptr_t)E_k | (uintptr_t)E_v | (uintptr_t)O | (uintptr_t)dO | (uintptr_t)dQ) & 15)
+    if (((uintptr_t)Q | (uintptr_t)E_k | (uintptr_t)E_v | (uintptr_t)O | (uintptr_t)dO | (uintptr_t)dQ | (uintptr_t)W_pe |
+         (uintptr_t)tile_state | (uintptr_t)tok_state | (uintptr_t)dE_k | (uintptr_t)dE_v | (uintptr_t)dW_pe) & 15)
         return MBEMA_ERR_ALIGN;
     if (workspace_bytes < mbema_flash_bwd_workspace_bytes(B, H, T, hd, N, K, mode)) return MBEMA_ERR_WORKSPACE;
     FlashArgs a = pack(Q, q_dtype, x, E_k, E_v, e_dtype, W_pe, rhos, unique, tile_state, tok_state, kcount, seq_lens,

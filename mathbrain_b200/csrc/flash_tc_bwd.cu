@@ -545,7 +545,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             const float p = row_ok ? __expf(s - lse) : 0.f;
             const float dsr = p * ((dpp[0] + dpp[1]) - drow);     // d loss / d score
             const float dsq = dsr * 0.125f;
-            const uint32_t dsr2 = pack_bf16x2(dsr, dsr), p2 = pack_bf16x2(p, p);
+            const uint32_t dsr2 = pack_bf16x2(dsr, dsr), p2 = pack_bf16x2(p, p), dsq2 = pack_bf16x2(dsq, dsq);
             // ---- column sums of the previous slot (also: its Z tiles have been consumed)
             if (i >= 1) {
                 mbar_wait(&bars->z_done, (uint32_t)((i - 1) & 1), abort_flag);
@@ -584,10 +584,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                     st_shared_v4(zrow + 2 * HPC * ATOM_BYTES + chunk, zv[0], zv[1], zv[2], zv[3]);
                     if (j8 == 0) tmem_wait_ld();
 #pragma unroll
-                    for (int pr = 0; pr < 4; ++pr) {
-                        dq[j8 * 8 + pr * 2] = fmaf(dsq, bf16_lo(ge[pr]), dq[j8 * 8 + pr * 2]);
-                        dq[j8 * 8 + pr * 2 + 1] = fmaf(dsq, bf16_hi(ge[pr]), dq[j8 * 8 + pr * 2 + 1]);
-                    }
+                    for (int pr = 0; pr < 4; ++pr)      // dq += (ds / 8) * K in fp32: bf16 x bf16 products are exact
+                        fma_f32_bf16x2(dq[j8 * 8 + pr * 2], dq[j8 * 8 + pr * 2 + 1], ge[pr], dsq2);
                 }
                 tmem_st_32x32b_x16(t_dq + c * 16, dq);
             }

@@ -11,6 +11,8 @@
 #include <math.h>
 
 #include <cuda_fp16.h>
+#include <atomic>
+
 #include "common.cuh"
 
 namespace mbema {
@@ -403,7 +405,9 @@ namespace mbema {
 // that loads the library carries this array until the process exits.
 static __device__ __align__(256) int32_t g_static_scan_scratch[4 * MBEMA_STATIC_SCAN_MAX_TOKENS + 2 * MBEMA_STATIC_SCAN_MAX_BATCH + 128];
 static constexpr int MAX_DEVICES = 64;
-static void* g_static_scan_addr[MAX_DEVICES] = {nullptr};   // device address of the array, per device, filled on first use
+// device address of the array, per device, filled on first use; atomic because two host threads may make their first
+// call on the same device at the same time (both look the address up and store the same value)
+static std::atomic<void*> g_static_scan_addr[MAX_DEVICES];
 }  // namespace mbema
 
 extern "C" int mbema_query_scan_static(const int64_t* x, const float* rhos, const float* c_init,
@@ -418,14 +422,14 @@ extern "C" int mbema_query_scan_static(const int64_t* x, const float* rhos, cons
     int dev = 0;
     MBEMA_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= MAX_DEVICES) return MBEMA_ERR_UNSUPPORTED;
-    if (g_static_scan_addr[dev] == nullptr) {
+    void* scratch = g_static_scan_addr[dev].load(std::memory_order_acquire);
+    if (scratch == nullptr) {
         // In host code the array's name is only a handle; the kernels need its address on the current device.
-        void* p = nullptr;
-        MBEMA_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scan_scratch));
-        g_static_scan_addr[dev] = p;
+        MBEMA_CUDA_TRY(cudaGetSymbolAddress(&scratch, g_static_scan_scratch));
+        g_static_scan_addr[dev].store(scratch, std::memory_order_release);
     }
     cudaStream_t st = (cudaStream_t)stream;
-    IndexWs w = carve_index_ws(g_static_scan_addr[dev], B, T);
+    IndexWs w = carve_index_ws(scratch, B, T);
     rc = launch_sort_link(x, c_init_keys, w, B, T, c_init_keys ? K : 0, st);
     if (rc) return rc;
     dim3 grid((unsigned)((T + CHAIN_WARPS - 1) / CHAIN_WARPS), (unsigned)B);
