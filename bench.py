@@ -30,7 +30,7 @@ METRIC = "flash_ema_fwd_bwd_tokens_per_s"
 # DRAM traffic of the attention backward, bytes per slot-step (one listed slot of one sample at one time step):
 # dram__bytes_read.sum + dram__bytes_write.sum of one profiler capture of the B=16 profile case divided by that
 # launch's slot-steps.  Traffic grows in proportion to the slot-steps, so a full launch is this figure times its own.
-BWD_DRAM_BYTES_PER_SLOT_STEP = 22.7
+BWD_DRAM_BYTES_PER_SLOT_STEP = 22.3
 DECODE = dict(B=64, K0=3000, capacity=4608, steps=2048, warmup=16)
 
 
