@@ -221,6 +221,31 @@ int mbema_slot_grad_scatter(const void* dE_a, const void* dE_b, int dtype, const
                             int64_t D, int64_t V, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Gather + LayerNorm over distinct slot tokens: out[u, :] = LayerNorm(E[tokens[u], :]) * ln_w + ln_b.
+ * Stands in for F.embedding(safe_unique, E_slots) followed by ln_kv (mathbrain/model.py:63-65), computed once per
+ * DISTINCT token of the batch (rows for mbema_flash_fwd_rows after the caller's k_proj / v_proj) instead of once per
+ * sample and slot.   E [V, D] (dtype code)   tokens [U] i64 (entries outside [0, V) give zero rows)
+ * ln_w, ln_b [D] f32   out [U, D] (out dtype code)   mu, rstd [U] f32 (saved for the backward).  D % 4 == 0, D <= 1024.
+ * Backward: dY [U, D] -> dE[tokens[u], :] += dx (ACCUMULATED into the [V, D] f32 table: zero it once per step),
+ * dln_w, dln_b [D] f32 (ACCUMULATED as well; fp32 atomics, so the last bits depend on the order).
+ * ---------------------------------------------------------------------------------------------- */
+int mbema_slot_ln_fwd(const void* E, int e_dtype, const int64_t* tokens, const float* ln_w, const float* ln_b, float eps,
+                      void* out, int out_dtype, float* mu, float* rstd, int64_t U, int64_t D, int64_t V, void* stream);
+int mbema_slot_ln_bwd(const void* dY, int dy_dtype, const void* E, int e_dtype, const int64_t* tokens, const float* ln_w,
+                      const float* mu, const float* rstd, float* dE, float* dln_w, float* dln_b, int64_t U, int64_t D,
+                      int64_t V, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Chunk-start state of listed slots from RESIDENT per-document state (the layout of the decode entry points below):
+ *   c_base[b, k, :] = state[b, v, :] * rho^(t0[b] - last_t[b, v])   for v = slots[b, k] with last_t >= 0, else 0.
+ * Stands in for the per-chunk state lookup of the reference's dataset (mathbrain/data.py:128-140), which reads
+ * states.bin in a Python loop.   state [B,V,N] f32, last_t [B,V] i32 (-1 = never), slots [B,K] i64 (< 0: zero row),
+ * t0 [B] i32 (step of the chunk's first token), rhos [N] f32 -> c_base [B,K,N] f32.
+ * ---------------------------------------------------------------------------------------------- */
+int mbema_slot_state_gather(const float* state, const int32_t* last_t, const int64_t* slots, const int32_t* t0,
+                            const float* rhos, float* c_base, int64_t B, int64_t K, int64_t V, int64_t N, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Streaming decode with resident per-sequence slot state.  The reference has no decode loop; one step is one
  * iteration of the loop body of mathbrain/flash_ema_attention.py:46-82 (attention over the slots, then the
  * "+1" of the current token) plus the query-side read of mathbrain/triton_ema_query.py:36-64.

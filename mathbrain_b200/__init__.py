@@ -4,11 +4,11 @@ import sys
 import types
 
 from . import _lib
-from .ops import (HAS_TRITON, device_status, check_status, clear_status, status_word, FlashEMAFunction, FlashEMARowsFunction, shared_slot_rows, slot_grad_scatter, FusedGatingFunction, TileStates, _build_unique_index,
+from .ops import (HAS_TRITON, device_status, check_status, clear_status, status_word, FlashEMAFunction, FlashEMARowsFunction, shared_slot_rows, slot_grad_scatter, SlotLayerNormFunction, project_slot_rows, FusedGatingFunction, TileStates, _build_unique_index,
                   compute_query_ema_history, fused_apply_symmetric_query_gating, get_options, options,
                   precompute_boundaries, set_options)
 
-__all__ = ["HAS_TRITON", "FlashEMAFunction", "FlashEMARowsFunction", "shared_slot_rows", "slot_grad_scatter", "FusedGatingFunction", "TileStates", "_build_unique_index",
+__all__ = ["HAS_TRITON", "FlashEMAFunction", "FlashEMARowsFunction", "shared_slot_rows", "slot_grad_scatter", "SlotLayerNormFunction", "project_slot_rows", "FusedGatingFunction", "TileStates", "_build_unique_index",
            "compute_query_ema_history", "fused_apply_symmetric_query_gating", "precompute_boundaries",
            "set_options", "device_status", "check_status", "clear_status", "status_word", "get_options", "options", "install_as_mathbrain", "library_path"]
 

@@ -59,3 +59,48 @@ extern "C" int mbema_slot_grad_scatter(const void* dE_a, const void* dE_b, int d
         k_slot_grad_scatter<MBEMA_BF16><<<grid, SG_WARPS * 32, 0, st>>>(dE_a, dE_b, slots, out, R, (int)D, V);
     return check_launch();
 }
+
+// ------------------------------------------------------------------------------------------------
+// Chunk-start state of listed slots from resident per-document state:
+//   c_base[b, k, :] = state[b, v, :] * rho^(t0[b] - last_t[b, v])  for v = slots[b, k] seen before, else 0.
+// This is the quantity the reference's dataset computes per chunk in Python (mathbrain/data.py:128-140) from
+// states.bin; with the state resident (the decode layout: value after the last update + step of that update) it is
+// one gather + decay pass.  One warp per (b, k) row, channels on the lanes (coalesced 4N-byte rows).
+// ------------------------------------------------------------------------------------------------
+namespace mbema {
+
+__global__ void __launch_bounds__(SG_WARPS * 32)
+k_slot_state_gather(const float* __restrict__ state, const int32_t* __restrict__ last_t, const int64_t* __restrict__ slots,
+                    const int32_t* __restrict__ t0, const float* __restrict__ rhos, float* __restrict__ c_base,
+                    int64_t B, int64_t K, int64_t V, int N) {
+    const int lane = threadIdx.x & 31;
+    const int64_t R = B * K, stride = (int64_t)gridDim.x * SG_WARPS;
+    for (int64_t r = (int64_t)blockIdx.x * SG_WARPS + (threadIdx.x >> 5); r < R; r += stride) {
+        const int64_t b = r / K, v = slots[r];
+        int lt = -1;
+        if (v >= 0 && v < V) lt = last_t[b * V + v];
+        const float dt = (float)(t0[b] - lt);
+        for (int n = lane; n < N; n += 32) {
+            float out = 0.f;
+            if (lt >= 0) out = state[(b * V + v) * N + n] * exp2f(dt * log2f(rhos[n]));
+            c_base[r * N + n] = out;
+        }
+    }
+}
+
+}  // namespace mbema
+
+extern "C" int mbema_slot_state_gather(const float* state, const int32_t* last_t, const int64_t* slots, const int32_t* t0,
+                                       const float* rhos, float* c_base, int64_t B, int64_t K, int64_t V, int64_t N,
+                                       void* stream) {
+    if (B < 0 || K < 0 || V <= 0 || N <= 0 || N > 1024) return MBEMA_ERR_SHAPE;
+    if (B == 0 || K == 0) return MBEMA_OK;
+    if (!state || !last_t || !slots || !t0 || !rhos || !c_base) return MBEMA_ERR_NULL;
+    int dev = 0, sms = 148;
+    MBEMA_CUDA_TRY(cudaGetDevice(&dev));
+    MBEMA_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int64_t want = (B * K + SG_WARPS - 1) / SG_WARPS, cap = (int64_t)sms * 8;
+    k_slot_state_gather<<<(int)(want < cap ? want : cap), SG_WARPS * 32, 0, (cudaStream_t)stream>>>(
+        state, last_t, slots, t0, rhos, c_base, B, K, V, (int)N);
+    return check_launch();
+}

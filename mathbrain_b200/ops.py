@@ -470,6 +470,63 @@ def slot_grad_scatter(dE_k, dE_v, unique_tensor, out):
     return out
 
 
+class SlotLayerNormFunction(torch.autograd.Function):
+    """memory_base[u] = LayerNorm(E_slots[tokens[u]]) for the DISTINCT tokens of a batch (rows for FlashEMARowsFunction
+    after k_proj / v_proj): `F.embedding(safe_unique, E_slots)` + `ln_kv` of mathbrain/model.py:63-65, once per token
+    instead of once per sample and slot.  The backward returns the dense [V, D] embedding gradient (LayerNorm backward
+    fused with the scatter) and the LayerNorm parameter gradients."""
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda")
+    def forward(ctx, E_slots, tokens, ln_w, ln_b, eps=1e-5, out_dtype=None):
+        _require_cuda(E_slots, tokens, ln_w, ln_b)
+        lib = _lib.load()
+        with torch.cuda.device(E_slots.device):
+            E = _f32_or_bf16(E_slots).contiguous()
+            tok = tokens.long().contiguous()
+            w, b = ln_w.float().contiguous(), ln_b.float().contiguous()
+            U, (V, D) = tok.numel(), E.shape
+            if out_dtype is None:
+                out_dtype = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else E.dtype
+            if out_dtype not in (torch.float32, torch.bfloat16):
+                out_dtype = torch.float32
+            out = torch.empty(U, D, dtype=out_dtype, device=E.device)
+            mu = torch.empty(U, dtype=torch.float32, device=E.device)
+            rstd = torch.empty(U, dtype=torch.float32, device=E.device)
+            rc = lib.mbema_slot_ln_fwd(_ptr(E), _dt(E), _ptr(tok), _ptr(w), _ptr(b), float(eps), _ptr(out), _dt(out),
+                                       _ptr(mu), _ptr(rstd), U, D, V, _stream())
+            _lib.check(rc, "mbema_slot_ln_fwd")
+        ctx.save_for_backward(E, tok, w, mu, rstd)
+        ctx.in_dtypes = (E_slots.dtype, ln_w.dtype, ln_b.dtype)
+        return out
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, dY):
+        E, tok, w, mu, rstd = ctx.saved_tensors
+        lib = _lib.load()
+        with torch.cuda.device(E.device):
+            dYc = _f32_or_bf16(dY).contiguous()
+            U, (V, D) = tok.numel(), E.shape
+            dE = torch.zeros(V, D, dtype=torch.float32, device=E.device)
+            dw = torch.zeros(D, dtype=torch.float32, device=E.device)
+            db = torch.zeros(D, dtype=torch.float32, device=E.device)
+            rc = lib.mbema_slot_ln_bwd(_ptr(dYc), _dt(dYc), _ptr(E), _dt(E), _ptr(tok), _ptr(w), _ptr(mu), _ptr(rstd),
+                                       _ptr(dE), _ptr(dw), _ptr(db), U, D, V, _stream())
+            _lib.check(rc, "mbema_slot_ln_bwd")
+        ed, wd, bd = ctx.in_dtypes
+        return dE.to(ed), None, dw.to(wd), db.to(bd), None, None
+
+
+def project_slot_rows(E_slots, tokens, ln_kv, k_proj, v_proj):
+    """(E_k_rows, E_v_rows) [U, D]: `k_proj(ln_kv(E_slots[tokens]))`, `v_proj(...)` over the distinct tokens of a batch
+    (`tokens` from shared_slot_rows), the operands of FlashEMARowsFunction.  Same values as the rows of the reference's
+    per-sample `E_k_active / E_v_active` (mathbrain/model.py:63-68), each computed once; gradients reach `E_slots`,
+    `ln_kv`, `k_proj` and `v_proj` through autograd.  The two projections are library GEMMs, as in the reference."""
+    mem = SlotLayerNormFunction.apply(E_slots, tokens, ln_kv.weight, ln_kv.bias, ln_kv.eps)
+    return k_proj(mem), v_proj(mem)
+
+
 def shared_slot_rows(unique_tensor):
     """Rows for slot-embedding tables shared between samples: returns (tokens[U] int64, row_index[B,K] int32) with
     tokens the sorted distinct tokens listed anywhere in `unique_tensor` (entries < 0 are padding) and

@@ -326,3 +326,53 @@ def test_slot_grad_scatter_matches_embedding_backward(mb, dtype):
     assert rel_err(out.cpu(), E.grad + E2.grad) < 1e-6
     with pytest.raises(mb._lib.MbemaError):
         mb.slot_grad_scatter(dEk[..., :60].cuda(), None, unique.cuda(), torch.zeros(V, 60, device="cuda"))   # D % 8
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1e-2)])
+def test_slot_rows_projection_matches_the_per_sample_reference(mb, dtype, tol):
+    """embedding -> ln_kv -> k_proj / v_proj over the DISTINCT tokens of a batch (project_slot_rows) against the
+    reference's per-sample formulation (mathbrain/model.py:63-68) in float64: the gathered rows are the same values,
+    and the gradients of E, ln_kv, k_proj and v_proj are those of the per-sample graph."""
+    g = torch.Generator().manual_seed(21)
+    B, K, D, V = 4, 23, 128, 60
+    unique = torch.randint(0, V, (B, K), generator=g)
+    for b in range(B):                                    # distinct within a sample, like a slot list
+        unique[b] = torch.randperm(V, generator=g)[:K]
+    unique[:, 19:] = -1
+    E = torch.randn(V, D, generator=g)
+    ln = torch.nn.LayerNorm(D)
+    kp, vp = torch.nn.Linear(D, D, bias=False), torch.nn.Linear(D, D, bias=False)
+    with torch.no_grad():
+        ln.weight.copy_(1 + 0.1 * torch.randn(D, generator=g))
+        ln.bias.copy_(0.1 * torch.randn(D, generator=g))
+    Rk, Rv = torch.randn(B, K, D, generator=g), torch.randn(B, K, D, generator=g)
+    mask = (unique >= 0).unsqueeze(-1)
+
+    def loss_of(Ek_act, Ev_act):
+        return ((Ek_act * Rk.to(Ek_act)) + (Ev_act * Rv.to(Ek_act))).mul(mask.to(Ek_act.device)).sum()
+
+    # reference: per sample, float64, on the CPU
+    E64 = E.double().requires_grad_(True)
+    ln64, kp64, vp64 = (torch.nn.LayerNorm(D).double(), torch.nn.Linear(D, D, bias=False).double(),
+                        torch.nn.Linear(D, D, bias=False).double())
+    ln64.load_state_dict(ln.state_dict()); kp64.load_state_dict(kp.state_dict()); vp64.load_state_dict(vp.state_dict())
+    mem = ln64(torch.nn.functional.embedding(unique.clamp_min(0), E64))
+    ref_k, ref_v = kp64(mem), vp64(mem)
+    loss_of(ref_k, ref_v).backward()
+
+    dev = "cuda"
+    Ed = E.to(dev).requires_grad_(True)
+    ln, kp, vp = ln.to(dev), kp.to(dev), vp.to(dev)
+    tokens, row_index = mb.shared_slot_rows(unique.to(dev))
+    with torch.autocast("cuda", dtype=torch.bfloat16, enabled=(dtype == torch.bfloat16)):
+        Ek_rows, Ev_rows = mb.project_slot_rows(Ed, tokens, ln, kp, vp)
+        assert Ek_rows.dtype == dtype and Ek_rows.shape == (tokens.numel(), D)
+        Ek_act, Ev_act = Ek_rows[row_index.long()], Ev_rows[row_index.long()]       # what the attention kernel gathers
+        Rk, Rv = Rk.to(dev), Rv.to(dev)
+        loss_of(Ek_act.float(), Ev_act.float()).backward()
+    m = mask.expand(-1, -1, D)
+    assert rel_err(Ek_act.detach().float().cpu()[m], ref_k.detach()[m]) < tol
+    assert rel_err(Ev_act.detach().float().cpu()[m], ref_v.detach()[m]) < tol
+    assert rel_err(Ed.grad.cpu(), E64.grad) < tol
+    assert rel_err(ln.weight.grad.cpu(), ln64.weight.grad) < tol and rel_err(ln.bias.grad.cpu(), ln64.bias.grad) < tol
+    assert rel_err(kp.weight.grad.cpu(), kp64.weight.grad) < tol and rel_err(vp.weight.grad.cpu(), vp64.weight.grad) < tol
