@@ -594,6 +594,99 @@ def exchange_phases(hp, steps, barrier, dev):
     return out
 
 
+def next_rows_bench(hp, dev, steps=5):
+    """The callers either side of the path, each beside its plain-PyTorch formulation on the same tensors (device time
+    per call, forward + backward, bf16 autocast; one layer for the slot projection):
+    slot K/V projection over distinct tokens (mathbrain/model.py:63-68), chunked lm_head + masked cross-entropy
+    (mathbrain/model.py:185-186, train.py:320-323) and the GPU-side construction of the slot lists (mathbrain/data.py:95-148)."""
+    import torch.nn.functional as F
+    import mathbrain_b200 as mb
+    from mathbrain_b200.feeder import ChunkFeeder
+    from mathbrain_b200.lmhead import lm_head_cross_entropy
+    c = CFG
+    B, T, D, V, N = c["B"], c["T"], c["D"], c["V"], c["N"]
+    g = torch.Generator().manual_seed(5)
+    res = hp.resident
+    unique = res["unique_slots"].clone()
+    unique[~res["pad_mask"]] = -1
+    K = unique.shape[1]
+
+    def time_it(fn, n=steps):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    out = {}
+    # ---- slot K/V projection
+    E = (torch.randn(V, D, generator=g) * 0.02).to(dev).requires_grad_(True)
+    ln = torch.nn.LayerNorm(D).to(dev)
+    kp, vp = torch.nn.Linear(D, D, bias=False).to(dev), torch.nn.Linear(D, D, bias=False).to(dev)
+    tokens, row_index = mb.shared_slot_rows(unique)
+    U = int(tokens.numel())
+    gk = torch.randn(B, K, D, generator=g).to(dev).to(torch.bfloat16)
+    gr = torch.randn(U, D, generator=g).to(dev).to(torch.bfloat16)
+
+    def per_sample():
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            mem = ln(F.embedding(unique.clamp_min(0), E))
+            Ek, Ev = kp(mem), vp(mem)
+        torch.autograd.backward([Ek, Ev], [gk, gk])
+        E.grad = None
+
+    def distinct_rows():
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            Ek, Ev = mb.project_slot_rows(E, tokens, ln, kp, vp)
+        torch.autograd.backward([Ek, Ev], [gr, gr])
+        E.grad = None
+
+    t_ref, t_new = time_it(per_sample), time_it(distinct_rows)
+    out["slot_projection"] = {"per_sample_torch_ms": t_ref, "distinct_rows_ms": t_new, "rows_per_sample_layout": B * K,
+                              "distinct_rows": U, "unit": "ms per layer, forward + backward"}
+    del gk, gr
+    # ---- tied lm_head + masked cross-entropy
+    h = torch.randn(B, T, D, generator=g).to(dev).requires_grad_(True)
+    y = torch.randint(0, V, (B, T), generator=g).to(dev)
+    y[torch.arange(T, device=dev).unsqueeze(0) >= res["fill"].unsqueeze(1)] = -100
+    n_valid = int((y != -100).sum())
+
+    def full_logits():
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            logits = F.linear(h, E)
+            loss = F.cross_entropy(logits.view(-1, V), y.view(-1), ignore_index=-100)
+        loss.backward()
+        h.grad = E.grad = None
+
+    def chunked():
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = lm_head_cross_entropy(h, E, y)
+        loss.backward()
+        h.grad = E.grad = None
+
+    t_ref, t_new = time_it(full_logits, 3), time_it(chunked, 3)
+    out["lm_head_ce"] = {"full_logits_torch_ms": t_ref, "chunked_valid_rows_ms": t_new, "rows": B * T, "valid_rows": n_valid,
+                         "unit": "ms, forward + backward", "logits_bytes_avoided": B * T * V * 2}
+    # ---- slot lists and chunk-start states from resident document state
+    feeder = ChunkFeeder(B, V, hp.rhos, capacity=8192 + 1024, device=dev)
+    x, fill = res["x"], res["fill"]
+
+    def feed():
+        batch = feeder.next_batch(x, fill)
+        C_seq = mb.compute_query_ema_history(x, hp.rhos, V, batch["c_base"], batch["unique_slots"])
+        feeder.advance(x, fill, C_seq)
+
+    t_feed = time_it(feed, 8)
+    out["feeder"] = {"next_batch_scan_advance_ms": t_feed, "documents": B, "seen_tokens_per_document": float(feeder.n_seen.float().mean()),
+                     "unit": "ms per chunk batch (slot lists + c_base + scan + state advance), on the GPU"}
+    return out
+
+
 def timed(fn, steps, warmup, barrier):
     for _ in range(warmup):
         fn()
@@ -684,6 +777,8 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--mode", default=os.environ.get("MBEMA_BENCH_MODE", "tc_bf16"), choices=["fp32", "tc_bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-next-rows", action="store_true",
+                    help="skip the measurements of the callers either side of the path (extra key `next_rows`)")
     ap.add_argument("--no-documents", action="store_true",
                     help="skip the measurement on the 8-GPU configuration's document data (extra key `documents`)")
     ap.add_argument("--no-decode", action="store_true", help="skip the streaming-decode measurement (extra key `decode`)")
@@ -754,6 +849,9 @@ def main():
     decode = None
     if world == 1 and not args.no_decode:
         decode = decode_bench(dev, args.mode)
+    next_rows = None
+    if world == 1 and not args.no_next_rows:
+        next_rows = next_rows_bench(hp, dev)
 
     t = torch.tensor([secs, secs_e2e, secs_skip], device=dev, dtype=torch.float64)
     if dist_on:
@@ -820,6 +918,8 @@ def main():
         }
         if decode is not None:
             line["decode"] = decode
+        if next_rows is not None:
+            line["next_rows"] = next_rows
         if dp_info is not None:
             line["dp"] = dp_info
         if documents is not None:

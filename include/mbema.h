@@ -246,6 +246,18 @@ int mbema_slot_state_gather(const float* state, const int32_t* last_t, const int
                             const float* rhos, float* c_base, int64_t B, int64_t K, int64_t V, int64_t N, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Softmax cross-entropy over a chunk of logits rows, forward and backward in one launch, IN PLACE:
+ *   loss_rows[r] = logsumexp(logits[r, 0:V]) - logits[r, targets[r]]
+ *   logits[r, c] <- (softmax(logits[r, 0:V])[c] - [c == targets[r]]) * scale     (columns [V, ld) <- 0)
+ * The building block of a chunked tied lm_head + masked cross-entropy (mathbrain/model.py:185-186,
+ * train.py:320-323: the reference materialises [B*T, V] logits): GEMM per chunk of valid rows, this kernel, two GEMMs.
+ *   logits [R, ld] (dtype code; ld >= V, ld % 8 == 0: every row 16-byte aligned)   targets [R] i64 (outside [0, V):
+ *   the row's loss and gradient are zero)   loss_rows [R] f32.
+ * ---------------------------------------------------------------------------------------------- */
+int mbema_ce_rows(void* logits, int dtype, const int64_t* targets, float scale, float* loss_rows, int64_t R, int64_t V,
+                  int64_t ld, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Streaming decode with resident per-sequence slot state.  The reference has no decode loop; one step is one
  * iteration of the loop body of mathbrain/flash_ema_attention.py:46-82 (attention over the slots, then the
  * "+1" of the current token) plus the query-side read of mathbrain/triton_ema_query.py:36-64.

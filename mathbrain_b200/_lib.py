@@ -52,6 +52,7 @@ SIGNATURES = {
     "mbema_slot_ln_fwd": (_i32, [_vp, _i32, _vp, _vp, _vp, _f32, _vp, _i32, _vp, _vp, _i64, _i64, _i64, _vp]),
     "mbema_slot_ln_bwd": (_i32, [_vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "mbema_slot_state_gather": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
+    "mbema_ce_rows": (_i32, [_vp, _i32, _vp, _f32, _vp, _i64, _i64, _i64, _vp]),
     "mbema_slot_grad_scatter": (_i32, [_vp, _vp, _i32, _vp, _vp, _i64, _i64, _i64, _vp]),
 }
 
