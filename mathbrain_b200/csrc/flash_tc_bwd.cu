@@ -475,6 +475,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             if (mx > 1.0e-36f && mx < 1.0e36f) { frexpf(mx, &e); sigma = ldexpf(1.0f, 2 - e); }
         }
         const float hs = 0.5f * sigma;
+        const uint32_t hs2 = pack_bf16x2(hs, hs), nhs2 = pack_bf16x2(-hs, -hs), sig2 = pack_bf16x2(sigma, sigma);   // powers of two: exact
         const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t t_dq = t_lane + (uint32_t)(COL_DQ + wg * HD);
         {
@@ -517,21 +518,20 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                     for (int pr = 0; pr < 4; ++pr) {
                         uint32_t gg, dd;
                         {   // gate and derivative in fp32 (packing the pre-activation first costs 2-3x in dW_pe accuracy), then packed
-                            float g[2], dsl[2];
+                            float g[2], th[2];
 #pragma unroll
                             for (int v = 0; v < 2; ++v) {
                                 const float hh = pre[j8 * 8 + pr * 2 + v];
-                                if (SILU) {     // h = x / 2, th = tanh(h), sg = sigmoid(x) = (1 + th)/2:  SiLU = h + h*th,  SiLU' = sg + SiLU*(1 - sg)
-                                    const float th = tanh_approx(hh);
-                                    g[v] = fmaf(hh, th, hh);
-                                    dsl[v] = fmaf(g[v], fmaf(-hs, th, hs), fmaf(hs, th, hs));      // sigma * SiLU'
-                                } else {
-                                    g[v] = hh;
-                                    dsl[v] = sigma;
-                                }
+                                th[v] = SILU ? tanh_approx(hh) : 0.f;
+                                g[v] = SILU ? fmaf(hh, th[v], hh) : hh;       // h = x / 2, th = tanh(h): SiLU = h + h*th
                             }
                             gg = pack_bf16x2(g[0], g[1]);
-                            dd = pack_bf16x2(dsl[0], dsl[1]);
+                            if (SILU) {     // sg = sigmoid(x) = (1 + th)/2, SiLU' = sg + SiLU*(1 - sg); times sigma, in packed bf16 from the fp32 tanh
+                                const uint32_t th2 = pack_bf16x2(th[0], th[1]);
+                                dd = fma_bf16x2(gg, fma_bf16x2(nhs2, th2, hs2), fma_bf16x2(hs2, th2, hs2));
+                            } else {
+                                dd = sig2;
+                            }
                         }
                         g2[w0 + pr] = gg;
                         dsl2[w0 + pr] = dd;
@@ -575,7 +575,11 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                         const uint32_t bd = mul_bf16x2(p2, do2[w0 + pr]);                 // p * dO
                         zk[pr] = mul_bf16x2(aq, gg);                                      // ds * q * g
                         zv[pr] = mul_bf16x2(bd, gg);                                      // p * dO * g
-                        zp[pr] = bf16x2_to_f16x2_sat(mul_bf16x2(fma_bf16x2(bd, evw[pr], mul_bf16x2(aq, ekw[pr])), dsl2[w0 + pr]));   // sigma * dgate * SiLU', fp16
+                        {   // sigma * dgate * SiLU' -> fp16: the last product exactly in fp32 (mixed-precision FMA), one conversion
+                            float z0 = 0.f, z1 = 0.f;
+                            fma_f32_bf16x2(z0, z1, fma_bf16x2(bd, evw[pr], mul_bf16x2(aq, ekw[pr])), dsl2[w0 + pr]);
+                            zp[pr] = pack_f16x2_sat(z0, z1);
+                        }
                         ge[pr] = mul_bf16x2(gg, ekw[pr]);                                 // K = g * E_k, for dQ
                     }
                     const int chunk = ((c * 2 + j8) ^ (row & 7)) << 4;

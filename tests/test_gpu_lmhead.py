@@ -39,4 +39,4 @@ def test_lm_head_cross_entropy_all_masked():
     E = torch.randn(20, 8, device="cuda", requires_grad=True)
     loss = lm_head_cross_entropy(h, E, torch.full((4,), -100, device="cuda"))
     loss.backward()
-    assert float(loss) == 0.0 and float(h.grad.abs().max()) == 0.0 and float(E.grad.abs().max()) == 0.0
+    assert float(loss.detach()) == 0.0 and float(h.grad.abs().max()) == 0.0 and float(E.grad.abs().max()) == 0.0
