@@ -145,11 +145,111 @@ k_sort_link(const int64_t* __restrict__ x, const int64_t* __restrict__ keys, Ind
 // one warp per chain; lanes hold channels lane, lane+32, lane+64, lane+96
 // ----------------------------------------------------------------------------------------------
 static constexpr int CHAIN_WARPS = 8;
+static constexpr int LONG_CHAIN = 64;      // occurrences from which a chain is scanned with warp shuffles instead of walked
+static constexpr int COOP_BLOCKS = 2;      // CTAs per sample, at the end of the grid, that scan the long chains
+
+// Long chains (the padding token, the most frequent tokens) are not walked but scanned: with U the carried value
+// (state + 1 after the previous occurrence; the seed before the first), occurrence j reads v_j = A_j U_j and hands on
+// U_{j+1} = A_j U_j + 1, A_j = keep_j rho^(t_j - t_{j-1}): an affine map per occurrence.  32 occurrences sit on the
+// lanes and the maps are composed with warp shuffles (a segmented prefix product over time, five steps per block of
+// 32); the N channels are split over the eight warps of the CTA, so a chain of L occurrences costs L/32 * N/8 short
+// scans instead of L dependent steps.  Results go through shared memory so that a row's channels leave together.
+__device__ void scan_long_chains(const IndexWs& w, const float* __restrict__ rhos, const float* __restrict__ c_init,
+                                 const int32_t* __restrict__ doc_ids, float* __restrict__ out, int T, int N, int K,
+                                 int extra_decay, int b, int q) {
+    __shared__ int lst[8192 / LONG_CHAIN];
+    __shared__ int n_long;
+    __shared__ float tile[CHAIN_WARPS][32][17];
+    __shared__ int tile_t[CHAIN_WARPS][32];
+    const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
+    const int nch = w.n_chain[b];
+    const int32_t* ch_off = w.ch_off + (size_t)b * T;
+    const int32_t* s_pos = w.s_pos + (size_t)b * T;
+    if (tid == 0) n_long = 0;
+    __syncthreads();
+    for (int c = tid; c < nch; c += blockDim.x) {
+        const int len = ((c + 1 < nch) ? ch_off[c + 1] : T) - ch_off[c];
+        if (len >= LONG_CHAIN) lst[atomicAdd(&n_long, 1)] = c;
+    }
+    __syncthreads();
+    const int nk = (N + CHAIN_WARPS - 1) / CHAIN_WARPS;          // channels of this warp: [wp * nk, wp * nk + nk)
+    const int n_mine = wp * nk + lane;                           // lane k < nk keeps rho, its log and the carry of channel k
+    const bool mine = lane < nk && n_mine < N;
+    const float rho_k = mine ? rhos[n_mine] : 1.0f;
+    const double l2r_k = mine ? log2((double)rho_k) : 0.0;
+    int kmax = min(nk, N - wp * nk);
+    if (kmax < 0) kmax = 0;
+    for (int li = q; li < n_long; li += COOP_BLOCKS) {
+        const int c = lst[li];
+        const int j0 = ch_off[c];
+        const int j1 = (c + 1 < nch) ? ch_off[c + 1] : T;
+        const int sd = w.seed[(size_t)b * T + j0];
+        float car = 0.0f;
+        if (sd != NO_SEED && mine && c_init != nullptr) {
+            car = c_init[((size_t)b * K + sd) * N + n_mine];
+            if (extra_decay) car *= rho_k;
+        }
+        bool has = (sd != NO_SEED);
+        int s_ref = 0;
+        int last_doc = (doc_ids != nullptr) ? doc_ids[(size_t)b * T] : 0;
+        for (int jb = j0; jb < j1; jb += 32) {
+            const int cnt = min(32, j1 - jb);
+            const bool live = lane < cnt;
+            const int t_l = live ? s_pos[jb + lane] : 0;
+            int t_prev = __shfl_up_sync(0xffffffffu, t_l, 1);
+            if (lane == 0) t_prev = s_ref;
+            bool keep = (lane == 0) ? has : true;
+            if (doc_ids != nullptr) {
+                const int d_l = live ? doc_ids[(size_t)b * T + t_l] : 0;
+                int d_prev = __shfl_up_sync(0xffffffffu, d_l, 1);
+                if (lane == 0) d_prev = last_doc;
+                if (d_l != d_prev) keep = false;
+                last_doc = __shfl_sync(0xffffffffu, d_l, cnt - 1);
+            }
+            const int di = t_l - t_prev;
+            const double dt = (double)di;
+            tile_t[wp][lane] = t_l;
+            for (int k = 0; k < kmax; ++k) {
+                const float rn = __shfl_sync(0xffffffffu, rho_k, k);
+                const double l2 = __shfl_sync(0xffffffffu, l2r_k, k);
+                // one step since the last occurrence: the decay is rho itself; longer gaps take the power in double
+                float A = 0.f;
+                if (live && keep) A = (di == 1) ? rn : (float)exp2(dt * l2);
+                const float A_own = A;
+                float Bv = live ? 1.0f : 0.0f;       // dead lanes carry the identity map: lane 31 ends with the last live result
+                if (!live) A = 1.0f;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {    // inclusive composition with the maps of the earlier lanes
+                    const float Ap = __shfl_up_sync(0xffffffffu, A, o), Bp = __shfl_up_sync(0xffffffffu, Bv, o);
+                    if (lane >= o) { Bv = fmaf(A, Bp, Bv); A *= Ap; }
+                }
+                const float U_in = __shfl_sync(0xffffffffu, car, k);
+                float Ae = __shfl_up_sync(0xffffffffu, A, 1), Be = __shfl_up_sync(0xffffffffu, Bv, 1);
+                if (lane == 0) { Ae = 1.0f; Be = 0.0f; }
+                tile[wp][lane][k] = A_own * fmaf(Ae, U_in, Be);                       // v_j = A_j U_j
+                const float U_out = __shfl_sync(0xffffffffu, fmaf(A, U_in, Bv), 31);  // carried past the block
+                if (lane == k) car = U_out;
+            }
+            __syncwarp();
+            for (int idx = lane; idx < cnt * kmax; idx += 32) {
+                const int r = idx / kmax, k = idx - r * kmax;
+                out[((size_t)b * T + tile_t[wp][r]) * N + wp * nk + k] = tile[wp][r][k];
+            }
+            __syncwarp();
+            s_ref = __shfl_sync(0xffffffffu, t_l, cnt - 1);
+            has = true;
+        }
+    }
+}
 
 __global__ void __launch_bounds__(CHAIN_WARPS * 32)
 k_chain_scan(IndexWs w, const float* __restrict__ rhos, const float* __restrict__ c_init,
              const int32_t* __restrict__ doc_ids, float* __restrict__ out, int T, int N, int K, int extra_decay) {
     const int b = blockIdx.y;
+    if ((int)blockIdx.x >= (int)gridDim.x - COOP_BLOCKS) {
+        scan_long_chains(w, rhos, c_init, doc_ids, out, T, N, K, extra_decay, b, (int)blockIdx.x - ((int)gridDim.x - COOP_BLOCKS));
+        return;
+    }
     const int c = blockIdx.x * CHAIN_WARPS + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     const int nch = w.n_chain[b];
@@ -177,6 +277,7 @@ k_chain_scan(IndexWs w, const float* __restrict__ rhos, const float* __restrict_
     bool has = (sd != NO_SEED);
     int s_ref = 0;
     int last_doc = (doc_ids != nullptr) ? doc_ids[(size_t)b * T] : 0;
+    if (j1 - j0 >= LONG_CHAIN) return;      // scanned by the cooperative blocks at the end of the grid
     // The chain is walked 32 occurrences at a time: every lane fetches one position (and document id), the steps then
     // take them from registers with shuffles, so a long chain pays the load latency once per 32 steps, not per step.
     for (int jb = j0; jb < j1; jb += 32) {
@@ -358,7 +459,7 @@ extern "C" int mbema_query_scan(const int64_t* x, const float* rhos, const float
     IndexWs w = carve_index_ws(workspace, B, T);
     rc = launch_sort_link(x, c_init_keys, w, B, T, c_init_keys ? K : 0, st);
     if (rc) return rc;
-    dim3 grid((unsigned)((T + CHAIN_WARPS - 1) / CHAIN_WARPS), (unsigned)B);
+    dim3 grid((unsigned)((T + CHAIN_WARPS - 1) / CHAIN_WARPS + COOP_BLOCKS), (unsigned)B);
     k_chain_scan<<<grid, CHAIN_WARPS * 32, 0, st>>>(w, rhos, c_init, doc_ids, C_seq, (int)T, (int)N, (int)K,
                                                     (flags & MBEMA_FLAG_CBASE_EXTRA_DECAY) ? 1 : 0);
     return check_launch();
@@ -379,7 +480,7 @@ extern "C" int mbema_tile_states(const int64_t* x, const int64_t* unique, const 
     const int extra = (flags & MBEMA_FLAG_CBASE_EXTRA_DECAY) ? 1 : 0;
     rc = launch_sort_link(x, unique, w, B, T, K, st);
     if (rc) return rc;
-    dim3 g1((unsigned)((T + CHAIN_WARPS - 1) / CHAIN_WARPS), (unsigned)B);
+    dim3 g1((unsigned)((T + CHAIN_WARPS - 1) / CHAIN_WARPS + COOP_BLOCKS), (unsigned)B);
     // a chain without a listed key keeps zero state in tok_state only if it is unlisted: such tokens own no slot,
     // so their rows are never read by the attention kernels; they are still written (query-scan semantics).
     k_chain_scan<<<g1, CHAIN_WARPS * 32, 0, st>>>(w, rhos, c_base, nullptr, tok_state, (int)T, (int)N, (int)K, extra);
@@ -432,7 +533,7 @@ extern "C" int mbema_query_scan_static(const int64_t* x, const float* rhos, cons
     IndexWs w = carve_index_ws(scratch, B, T);
     rc = launch_sort_link(x, c_init_keys, w, B, T, c_init_keys ? K : 0, st);
     if (rc) return rc;
-    dim3 grid((unsigned)((T + CHAIN_WARPS - 1) / CHAIN_WARPS), (unsigned)B);
+    dim3 grid((unsigned)((T + CHAIN_WARPS - 1) / CHAIN_WARPS + COOP_BLOCKS), (unsigned)B);
     k_chain_scan<<<grid, CHAIN_WARPS * 32, 0, st>>>(w, rhos, c_init, doc_ids, C_seq, (int)T, (int)N, (int)K,
                                                     (flags & MBEMA_FLAG_CBASE_EXTRA_DECAY) ? 1 : 0);
     return check_launch();

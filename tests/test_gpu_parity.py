@@ -376,3 +376,31 @@ def test_slot_rows_projection_matches_the_per_sample_reference(mb, dtype, tol):
     assert rel_err(Ed.grad.cpu(), E64.grad) < tol
     assert rel_err(ln.weight.grad.cpu(), ln64.weight.grad) < tol and rel_err(ln.bias.grad.cpu(), ln64.bias.grad) < tol
     assert rel_err(kp.weight.grad.cpu(), kp64.weight.grad) < tol and rel_err(vp.weight.grad.cpu(), vp64.weight.grad) < tol
+
+
+@pytest.mark.parametrize("N,with_docs", [(64, False), (33, True), (128, True), (4, False)])
+def test_scan_long_chains(mb, N, with_docs):
+    """Chains of hundreds of occurrences (a vocabulary of a few tokens, runs of one token as in the padding, half-lives
+    from one step to thousands): the warp-shuffle segmented scan of long chains against the oracle, with listed keys,
+    without, and across document boundaries."""
+    from mathbrain_b200 import synth
+    g = torch.Generator().manual_seed(N)
+    B, T, V = 3, 700, 5
+    x = torch.randint(0, V, (B, T), generator=g)
+    x[0, 300:] = 0                                         # a run of 400 repeats (gaps of one step)
+    x[1, ::2] = 3                                          # gaps of two
+    rhos = synth.make_rhos(N, 1.0, 4096.0)
+    keys = torch.tensor([[0, 1, 2, 3, 4, 0, 0], [4, 3, -1, 1, 0, 2, 0], [2, -1, -1, -1, -1, -1, -1]])
+    c_init = torch.rand(B, 7, N, generator=g) * 3.0
+    doc = None
+    if with_docs:
+        doc = torch.zeros(B, T, dtype=torch.long)
+        doc[0, 350:] = 1
+        doc[1, 100:] = 1
+        doc[1, 433:] = 2
+    ref = orc.query_scan(x, rhos, V, c_init, keys, doc_ids=doc, dtype=torch.float64)
+    C = mb.compute_query_ema_history(cu(x), cu(rhos), V, cu(c_init), cu(keys), cu(doc))
+    assert rel_err(C.cpu(), ref) < TOL_STATE
+    ref0 = orc.query_scan(x, rhos, V, doc_ids=doc, dtype=torch.float64)
+    C0 = mb.compute_query_ema_history(cu(x), cu(rhos), V, doc_ids=cu(doc))
+    assert rel_err(C0.cpu(), ref0) < TOL_STATE
