@@ -85,6 +85,7 @@ struct Bars {
     uint64_t drain;                   // every issuing lane's UMMAs have completed (PROD_WARPS arrivals, teardown)
     uint32_t tmem_base;
     int abort_flag;
+    unsigned spin_limit;         // poll limit of the waits (shortened by the test hook)
     int n_slots;
     int drain_flag;                   // give-up flag of the teardown wait (kept apart from abort_flag: that wait must not be cut short)
 };
@@ -115,7 +116,6 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
     int* key_sh = reinterpret_cast<int*>(sm + L.key_off);
     Bars* bars = reinterpret_cast<Bars*>(sm + L.bar_off);
     volatile int* abort_flag = &bars->abort_flag;
-    const unsigned spin_limit = a.test_withhold ? 64u : MBEMA_SPIN_LIMIT;      // test hook: waits give up after a few polls
 
     const int tile = blockIdx.x, hp = blockIdx.y, b = a.order ? a.order[blockIdx.z] : (int)blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -144,7 +144,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
             mbar_init(&bars->acc_empty[i], EPI_WARPS);
         }
         mbar_init(&bars->drain, PROD_WARPS);
-        bars->abort_flag = *reinterpret_cast<volatile int*>(status);   // an earlier CTA already gave up: do nothing
+        bars->abort_flag = *reinterpret_cast<volatile int*>(status);
+        bars->spin_limit = a.test_withhold ? 64u : MBEMA_SPIN_LIMIT;   // an earlier CTA already gave up: do nothing
         bars->drain_flag = 0;
         fence_barrier_init();
     }
@@ -268,7 +269,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
             __syncwarp();                                                       // ... and so have the other lanes'
             // this warp's stage (A tile, accumulators) is free once the epilogue has read slot i - NSTAGE; by then the
             // epilogue is also done with the E rows of slot i - NE, whose stage the rows of slot i take
-            if (it >= 1 && !mbar_wait(&bars->acc_empty[pw], (uint32_t)((it - 1) & 1), abort_flag, 1, spin_limit)) break;
+            if (it >= 1 && !mbar_wait(&bars->acc_empty[pw], (uint32_t)((it - 1) & 1), abort_flag, 1, &bars->spin_limit)) break;
             const int keyf = key_sh[i];
             const unsigned char* rg = ring_w + (it % RW) * RING_STAGE_BYTES;
             // E_k / E_v rows of the slot for the head pair, as fp16 (saturated): lane l converts columns 4l .. 4l+3 of both
@@ -407,7 +408,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
         };
         for (int i = 0; i < n_slots; ++i) {
             const int st = i % NSTAGE, u = i / NSTAGE;
-            alive = mbar_wait(&bars->acc_full[st], (uint32_t)(u & 1), abort_flag, 2, spin_limit);
+            alive = mbar_wait(&bars->acc_full[st], (uint32_t)(u & 1), abort_flag, 2, &bars->spin_limit);
             if (!alive) break;
             tc_fence_after_sync();
             const uint32_t t_acc = t_lane + st * ACC_COLS;

@@ -85,8 +85,11 @@ struct Bars {
     uint64_t acc_empty[2];       // all epilogue warps finished reading the stage      (EPI_WARPS arrivals)
     uint64_t z_full;             // all epilogue warps wrote their part of the Z tiles (EPI_WARPS arrivals)
     uint64_t z_done;             // products (2) and (3) of the slot have completed    (3 arrivals: one commit per issuing warp)
+    uint64_t drain;              // every issuing lane's UMMAs have completed (4 arrivals, teardown)
     uint32_t tmem_base;
     int abort_flag;
+    unsigned spin_limit;         // poll limit of the waits (shortened by the test hook)
+    int drain_flag;              // give-up flag of the teardown wait (apart from abort_flag: that wait must not be cut short)
     int n_slots;
     unsigned dmax_bits;          // largest |dO| among the CTA's rows (bit pattern of a non-negative float)
 };
@@ -161,7 +164,10 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
         }
         mbar_init(&bars->z_full, EPI_WARPS);
         mbar_init(&bars->z_done, 3);
+        mbar_init(&bars->drain, 4);
+        bars->drain_flag = 0;
         bars->abort_flag = *reinterpret_cast<volatile int*>(status);
+        bars->spin_limit = a.test_withhold ? 64u : MBEMA_SPIN_LIMIT;
         bars->dmax_bits = 0u;
         fence_barrier_init();
     }
@@ -289,7 +295,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
         const uint64_t d_ak0 = umma_desc_k_sw128(a_base), d_b0 = umma_desc_k_sw128(b_base);
         const int role = warp - EPI_WARPS;          // 0: gate, 1: dW^T, 2: dE_k, 3: dE_v
         auto issue_grad_products = [&](int j) {
-            mbar_wait(&bars->z_full, (uint32_t)(j & 1), abort_flag);
+            mbar_wait(&bars->z_full, (uint32_t)(j & 1), abort_flag, 1, &bars->spin_limit);
             tc_fence_after_sync();
             if (role == 1) {
                 const uint64_t d_at = d_a0 + (uint64_t)(((j % NA) * STAGE_BYTES) >> 4);
@@ -330,7 +336,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             prefetch(i + PD);
             asm volatile("cp.async.wait_group %0;" ::"n"(PD) : "memory");   // this lane's copies for slot i have landed
             __syncwarp();                                                      // ... and so have the other lanes'
-            if (i >= NA) mbar_wait(&a_free[sa], (uint32_t)((i / NA - 1) & 1), abort_flag);
+            if (i >= NA && !mbar_wait(&a_free[sa], (uint32_t)((i / NA - 1) & 1), abort_flag, 2, &bars->spin_limit)) break;   // gave up: drain and leave
             const int keyf = key_sh[i];
             const int key = keyf & 0x7fffffff;
             const unsigned char* rg = ring_w + (i % RING) * RING_STAGE_BYTES;
@@ -418,8 +424,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             if (lane == 0) mbar_arrive(&a_full[sa]);
             if (lane == 0) {
                 if (role == 0) {
-                    mbar_wait(&a_full[sa], (uint32_t)((i / NA) & 1), abort_flag);    // all four warps' rows and E columns
-                    if (i >= NACC) mbar_wait(&bars->acc_empty[sc], (uint32_t)((i / NACC - 1) & 1), abort_flag);
+                    mbar_wait(&a_full[sa], (uint32_t)((i / NA) & 1), abort_flag, 3, &bars->spin_limit);    // all four warps' rows and E columns
+                    if (i >= NACC) mbar_wait(&bars->acc_empty[sc], (uint32_t)((i / NACC - 1) & 1), abort_flag, 4, &bars->spin_limit);
                     tc_fence_after_sync();
 #pragma unroll
                     for (int k16 = 0; k16 < 4 * NK; ++k16) {     // contraction over n, 16 per instruction, 64 per swizzle atom
@@ -428,15 +434,16 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                                      d_b0 + (uint64_t)(off >> 4), idesc_gate, k16 != 0 ? 1u : 0u);
                     }
                     umma_commit(&bars->acc_full[sc]);
-                    mbar_arrive(&bars->acc_full[sc]);
+                    if (!(a.test_withhold && i == 0)) mbar_arrive(&bars->acc_full[sc]);   // withheld once by the test hook
                 } else if (i >= 1) {
                     issue_grad_products(i - 1);
                 }
             }
             __syncwarp();
         }
-        if (lane == 0 && role != 0 && n_slots > 0) issue_grad_products(n_slots - 1);
+        if (lane == 0 && role != 0 && n_slots > 0 && !*abort_flag) issue_grad_products(n_slots - 1);
         asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (lane == 0) umma_commit(&bars->drain);    // arrives once every UMMA this lane issued has completed
     } else {
         // ============================================================ epilogue warpgroups: a thread per time step, a head per warpgroup
         asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
@@ -491,11 +498,12 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
         size_t de_row_prev = 0;                                          // E row of slot i - 1
         const uint32_t t_de = t_lane + (wg == 0 ? COL_DEK : COL_DEV);
 
+        bool alive = true;
         for (int i = 0; i < n_slots; ++i) {
             const int sa = i % NA, sc = i % NACC;
             size_t de_row_cur = 0;                                      // used one iteration later: the load has a whole slot to land
             if (ROWS) de_row_cur = (size_t)a.erow[(size_t)b * a.K + slot_sh[i]];
-            mbar_wait(&bars->acc_full[sc], (uint32_t)((i / NACC) & 1), abort_flag);
+            if (!mbar_wait(&bars->acc_full[sc], (uint32_t)((i / NACC) & 1), abort_flag, 5, &bars->spin_limit)) { alive = false; break; }
             tc_fence_after_sync();
             const uint32_t t_acc = t_lane + (uint32_t)(sc * ACC_COLS + wg * HD);
             // ---- pass 1: gate, its derivative, score and dO.V; gate and derivative are kept as packed bf16 pairs
@@ -548,7 +556,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             const uint32_t dsr2 = pack_bf16x2(dsr, dsr), p2 = pack_bf16x2(p, p), dsq2 = pack_bf16x2(dsq, dsq);
             // ---- column sums of the previous slot (also: its Z tiles have been consumed)
             if (i >= 1) {
-                mbar_wait(&bars->z_done, (uint32_t)((i - 1) & 1), abort_flag);
+                if (!mbar_wait(&bars->z_done, (uint32_t)((i - 1) & 1), abort_flag, 6, &bars->spin_limit)) { alive = false; break; }
                 tc_fence_after_sync();
                 const float v = tmem_ld_1(t_de);
                 tmem_wait_ld();
@@ -603,8 +611,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             }
             if (ROWS) de_row_prev = de_row_cur;
         }
-        if (n_slots > 0) {
-            mbar_wait(&bars->z_done, (uint32_t)((n_slots - 1) & 1), abort_flag);
+        if (n_slots > 0 && alive && mbar_wait(&bars->z_done, (uint32_t)((n_slots - 1) & 1), abort_flag, 7, &bars->spin_limit)) {
             tc_fence_after_sync();
             const float v = tmem_ld_1(t_de);
             tmem_wait_ld();
@@ -615,7 +622,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             float dq[16];
             tmem_ld_32x32b_x16(t_dq + c * 16, dq);
             tmem_wait_ld();
-            if (t < a.T) {
+            if (t < a.T && !*abort_flag) {      // after a give-up nothing of this CTA is stored (the status word says so)
 #pragma unroll
                 for (int i = 0; i < 16; i += 4)
                     *reinterpret_cast<float4*>(a.dQ + qoff + c * 16 + i) = make_float4(dq[i], dq[i + 1], dq[i + 2], dq[i + 3]);
@@ -625,7 +632,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             float acc[32];
 #pragma unroll
             for (int c = 0; c < N / 32; ++c) {
-                if (n_slots > 0) {
+                if (n_slots > 0 && !*abort_flag) {
                     tmem_ld_32x32b_x32(t_lane + COL_DW + c * 32, acc);
                     tmem_wait_ld();
                 } else {
@@ -641,10 +648,11 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
     tc_fence_before_sync();
     __syncthreads();
     if (warp == EPI_WARPS) {
+        mbar_wait<100>(&bars->drain, 0u, &bars->drain_flag, 8);    // bounded: no UMMA of this CTA is in flight when TMEM is released
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, TMEM_COLS);
     }
-    if (tid == 0 && bars->abort_flag) atomicOr(status, bars->abort_flag);   // sticky: never cleared by the library
+    if (tid == 0 && (bars->abort_flag | bars->drain_flag)) atomicOr(status, bars->abort_flag | bars->drain_flag);   // sticky: never cleared by the library
 }
 
 // dW[n, hp*128 + d] = sum over (b, tile) of part[b][hp][tile][n][d]      (fixed order -> deterministic)

@@ -43,9 +43,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // A wait that expires stores 1 | (tag << 8) there, so the status word the kernel reports names the wait that gave up.
 // SLEEP_NS > 0: the thread sleeps that long between polls.  A polling warp executes instructions, and those take issue
 // slots from the warps that have work, so warps that wait far ahead of their consumer should poll rarely.
+// `limit_ptr` (shared memory, optional): poll limit set by a test hook; it is read only after the first poll has failed, so
+// the common case costs one try_wait and a branch and keeps no extra value in a register (a run-time limit held in a
+// register across the kernel made the backward 14 % slower).
 template <unsigned SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int tag = 0,
-                                          unsigned limit = MBEMA_SPIN_LIMIT) {
+                                          const volatile unsigned* limit_ptr = nullptr) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned limit = limit_ptr ? *limit_ptr : MBEMA_SPIN_LIMIT;
     for (unsigned it = 0; it < limit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);

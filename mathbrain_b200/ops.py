@@ -428,6 +428,8 @@ class FlashEMAFunction(torch.autograd.Function):
         Qc, xx, Ek, Ev, W, rh, O, LSE = ctx.saved_tensors
         h = ctx.handle
         B, H, L, hd, N, K, V_total, flags, mode = ctx.meta
+        if _OPTIONS["_test_withhold_arrive"]:      # test hook of the tensor-core backward, read at call time
+            flags |= _lib.FLAG_TEST_WITHHOLD_ARRIVE
         D = H * hd
         dOc = _f32_or_bf16(dO).contiguous()
         dQ = torch.empty(B, H, L, hd, dtype=torch.float32, device=dO.device)

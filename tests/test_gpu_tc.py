@@ -179,3 +179,36 @@ def test_bounded_wait_gives_up_cleanly(mb):
     with mb.options(mode="fp32"):
         ref = run_flash(mb, inp, c_base, dtype=torch.bfloat16, with_grad=False)
     assert rel_err(out["O"], ref["O"]) < TOL_BF16
+
+
+def test_bounded_wait_gives_up_cleanly_in_the_backward(mb):
+    """The same for the tensor-core backward: the forward runs normally, the hook withholds one hand-off of the backward's
+    gate product; the launch ends by itself, the status names a wait of the backward, no gradient of the failed CTAs is
+    trusted (the status says so), and after clear_status() forward + backward are correct again."""
+    inp, c_base, _ = make_case(902, B=2, T=200, N=64, H=2, vocab=300, max_prefix=100, min_hl=4.0, max_hl=500.0, std=0.1)
+    assert mb.device_status() == 0
+    dev = "cuda"
+    unique = inp["unique"].to(dev)
+    with mb.options(mode="tc_bf16"):
+        h = mb.precompute_boundaries(inp["x"].to(dev), unique, inp["rhos"].to(dev), 64, c_init=c_base.to(dev))
+        leaves = [inp[k].to(dev).to(torch.bfloat16 if k != "W_pe" else torch.float32).requires_grad_(True)
+                  for k in ("Q", "E_k", "E_v", "W_pe")]
+        O = mb.FlashEMAFunction.apply(leaves[0], inp["x"].to(dev), leaves[1], leaves[2], leaves[3], inp["rhos"].to(dev),
+                                      inp["V"], unique, unique.shape[1], h, True)
+        torch.cuda.synchronize()
+        assert mb.device_status() == 0
+        mb.ops._OPTIONS["_test_withhold_arrive"] = True
+        try:
+            O.backward(inp["dO"].to(dev).float())
+        finally:
+            mb.ops._OPTIONS["_test_withhold_arrive"] = False
+    torch.cuda.synchronize()
+    st = mb.device_status()
+    assert st & 1, hex(st)
+    assert 1 <= (st >> 8) <= 8, hex(st)
+    with pytest.raises(mb._lib.MbemaError):
+        mb.ops.check_status()
+    mb.ops.clear_status()
+    out = run_tc(mb, inp, c_base)
+    ref = oracle_flash(inp, c_base)
+    compare_all(out, ref, TOL_BF16)
