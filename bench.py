@@ -687,6 +687,76 @@ def next_rows_bench(hp, dev, steps=5):
     return out
 
 
+def next_case(args):
+    """The memory-bound kernels of the rows around the path at the bench's sizes, a few calls each (for profiler
+    captures): gather + LayerNorm over distinct tokens forward / backward, slot-gradient scatter, chunk-start state
+    gather, row-wise cross-entropy over one 4096-row chunk.  Prints device time and algorithmic GB/s; no benchmark line."""
+    import mathbrain_b200 as mb
+    from mathbrain_b200 import _lib, synth
+    from mathbrain_b200.ops import _ptr, _stream
+    c = CFG
+    dev = torch.device("cuda", 0)
+    B, T, D, V, N = c["B"], c["T"], c["D"], c["V"], c["N"]
+    host = make_rank_batch(0, 1)
+    K = host["K_max"]
+    unique = host["unique_slots"].clone()
+    unique[~host["pad_mask"]] = -1
+    unique = unique.to(dev)
+    g = torch.Generator().manual_seed(3)
+    E = (torch.randn(V, D, generator=g) * 0.02).to(dev).requires_grad_(True)
+    ln = torch.nn.LayerNorm(D).to(dev)
+    tokens, _ = mb.shared_slot_rows(unique)
+    U = int(tokens.numel())
+    gy = torch.randn(U, D, generator=g).to(dev).to(torch.bfloat16)
+    dEk = torch.randn(B, K, D, generator=g).to(dev).to(torch.bfloat16)
+    dEv = torch.randn(B, K, D, generator=g).to(dev).to(torch.bfloat16)
+    table = torch.zeros(V, D, device=dev)
+    state = torch.rand(B, V, N, generator=g).to(dev)
+    last_t = torch.randint(0, 4096, (B, V), generator=g).to(torch.int32).to(dev)
+    t0 = torch.full((B,), 8192, dtype=torch.int32, device=dev)
+    rhos = host["rhos"].to(dev)
+    c_base = torch.empty(B, K, N, device=dev)
+    R, ld = 4096, (V + 7) // 8 * 8
+    logits = torch.randn(R, ld, generator=g).to(dev).to(torch.bfloat16)
+    targets = torch.randint(0, V, (R,), generator=g).to(dev)
+    loss_rows = torch.empty(R, device=dev)
+    lib = _lib.load()
+    n_slots = int(host["pad_mask"].sum())
+
+    def ev_time(fn, n=5):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    out = {"profile_case": "next", "hbm_peak_GBps": peaks()["hbm"], "distinct_rows": U, "listed_slots": n_slots}
+    y = None
+
+    def ln_fwd():
+        nonlocal y
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = mb.SlotLayerNormFunction.apply(E, tokens, ln.weight, ln.bias, ln.eps)
+
+    ms = ev_time(ln_fwd)
+    out["mbema_slot_ln_fwd"] = {"ms": ms, "GBps": U * D * (4 + 2) / ms / 1e6}
+    ms = ev_time(lambda: torch.autograd.grad(y, [E, ln.weight, ln.bias], gy, retain_graph=True))
+    out["mbema_slot_ln_bwd (+ 103 MB table memset)"] = {"ms": ms, "GBps": (U * D * (4 + 2 + 4) + V * D * 4) / ms / 1e6}
+    ms = ev_time(lambda: mb.slot_grad_scatter(dEk, dEv, unique, table))
+    out["mbema_slot_grad_scatter"] = {"ms": ms, "GBps": (2 * B * K * D * 2 + n_slots * D * 4) / ms / 1e6}
+    slots = unique.contiguous()
+    ms = ev_time(lambda: lib.mbema_slot_state_gather(_ptr(state), _ptr(last_t), _ptr(slots), _ptr(t0), _ptr(rhos), _ptr(c_base),
+                                                     B, K, V, N, _stream()))
+    out["mbema_slot_state_gather"] = {"ms": ms, "GBps": (n_slots * N * 4 + B * K * N * 4) / ms / 1e6}
+    ms = ev_time(lambda: lib.mbema_ce_rows(_ptr(logits), _lib.BF16, _ptr(targets), 1.0 / R, _ptr(loss_rows), R, V, ld, _stream()))
+    out["mbema_ce_rows"] = {"ms": ms, "GBps": 2 * R * ld * 2 / ms / 1e6}
+    print(json.dumps(out))
+
+
 def timed(fn, steps, warmup, barrier):
     for _ in range(warmup):
         fn()
@@ -782,7 +852,7 @@ def main():
     ap.add_argument("--no-documents", action="store_true",
                     help="skip the measurement on the 8-GPU configuration's document data (extra key `documents`)")
     ap.add_argument("--no-decode", action="store_true", help="skip the streaming-decode measurement (extra key `decode`)")
-    ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd", "long", "aux", "decode", "triton"],
+    ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd", "long", "aux", "decode", "triton", "next"],
                     help="run a small one-layer attention workload (for ncu captures) instead of the benchmark")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
@@ -804,6 +874,9 @@ def main():
         return
     if args.profile_case == "triton":
         triton_case(args)
+        return
+    if args.profile_case == "next":
+        next_case(args)
         return
     if args.profile_case:
         profile_case(args)
