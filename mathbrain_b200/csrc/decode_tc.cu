@@ -1,17 +1,19 @@
 // Streaming decode on the tensor cores (MBEMA_MODE_TC_BF16, N = 64, bf16 slot embeddings): attention of ONE query
-// per sequence over the slots seen so far, in ONE walk over the slots.  Rows of a tile are SLOTS here (a thread per
-// slot and 32-column half of a head), so the softmax runs across threads:
-//   per 128-slot tile   decayed state tile (fp16) -> tcgen05.mma against W -> gate -> score s[k] per head (the two
-//                       halves of a head meet in shared memory) -> tile maximum m -> p = exp(s - m) ->
-//                       the bf16 tile (p * gate * E_v)[k, d] is summed over its 128 slots by a second tcgen05.mma
-//                       against a ones operand (the column-sum trick of the training backward) into a fresh TMEM
-//                       region, which the CTA folds into its running (max, normaliser, output) one tile later;
-//   per CTA             partial (m, l, O[128]) of its tiles, written to the workspace;
-//   merge kernel        per (sequence, head): the partials of all CTAs plus the mass of the never-seen slots
-//                       (exp(0 - m) each) -> O.
-// The gate product, its tanh and every gather are done once per slot and head pair.  Embedding rows are cp.async
-// copies two tiles ahead into shared-memory rings; state rows are prefetched into registers a tile ahead (64 bytes a
-// thread), so the tile of slot tile i+1 is converted and its UMMA issued before the epilogue of tile i.
+// per sequence over the slots seen so far, in ONE walk over the slots, warp-specialised like the training kernels.
+// A CTA owns (sequence, head pair, share of the 128-slot tiles); rows of a tile are SLOTS.
+//   eight producer warps (two threads per slot): cp.async gathers of the tile's E_k / E_v rows into two-stage rings, the
+//       slot's state row from global memory -> decayed fp16 row of the A tile; one lane issues the gate product
+//       (tcgen05.mma against W, accumulators in TMEM, two stages), another the column-sum product below;
+//   eight epilogue warps (a warpgroup per head, a thread per slot and the head's 64 columns): gate = SiLU of the
+//       accumulators, score s[k] = sum_c q g E_k in the thread, tile maximum over the head's 128 threads (warp
+//       shuffles + one named barrier of 128 threads), p = exp(s - m), the bf16 tile (p * gate * E_v)[k, d] written
+//       over the E_v rows it was made from; its sum over the 128 slots is a second tcgen05.mma against a ones operand
+//       (the column-sum trick of the training backward) into one of two TMEM regions, which warpgroup 0 folds into the
+//       CTA's running (max, normaliser, output) one tile later (online softmax in registers);
+//   per CTA      partial (O[128], m[2], l[2]) of its tiles, written to the workspace;
+//   merge kernel per (sequence, head): the partials of all CTAs plus the mass of the never-seen slots -> O.
+// No block barrier inside the tile loop: the roles meet on mbarriers (every wait bounded), so the gathers, the state
+// conversion and the gate product of tile i+1 run while the epilogue works on tile i.
 #include "common.cuh"
 #include <cuda_fp16.h>
 #include "sm100_ptx.cuh"
@@ -22,16 +24,18 @@ namespace dtc {
 
 using namespace ptx;
 
-static constexpr int TM = 128, HD = 64, HPC = 2, N = 64, ACC_COLS = HPC * HD, THREADS = 512, MAXT = 16;
+static constexpr int TM = 128, HD = 64, HPC = 2, N = 64, ACC_COLS = HPC * HD, MAXT = 16;
+static constexpr int EPI_WARPS = 8, PROD_WARPS = 8, THREADS = (EPI_WARPS + PROD_WARPS) * 32;
 static constexpr int ATOM_BYTES = TM * 128;
 static constexpr int STAGE_BYTES = 2 * ATOM_BYTES;            // one embedding stage: 2 heads x 128 rows x 128 B
 static constexpr int PART_FLOATS = ACC_COLS + 4;              // per-CTA partial: O[128], m[2], l[2]
-static constexpr int OFF_B = 0, OFF_A = ATOM_BYTES, OFF_EK = 2 * ATOM_BYTES, OFF_EV = OFF_EK + 2 * STAGE_BYTES,
-                     OFF_V = OFF_EV + 2 * STAGE_BYTES, OFF_ONES = OFF_V + 2 * ATOM_BYTES, OFF_Q = OFF_ONES + 2048,
-                     OFF_L2R = OFF_Q + 512, OFF_IDS = OFF_L2R + 256, OFF_DTS = OFF_IDS + MAXT * TM * 4,
-                     OFF_SC = OFF_DTS + MAXT * TM * 4, OFF_WRED = OFF_SC + TM * 4 * 4, OFF_TILE = OFF_WRED + 2 * 16 * 4,
-                     OFF_BARS = OFF_TILE + MAXT * 4 * 4, SMEM_BYTES = OFF_BARS + 64 + 1024;
+static constexpr int OFF_B = 0, OFF_A = ATOM_BYTES, OFF_EK = OFF_A + 2 * ATOM_BYTES, OFF_EV = OFF_EK + 2 * STAGE_BYTES,
+                     OFF_ONES = OFF_EV + 2 * STAGE_BYTES, OFF_Q = OFF_ONES + 2048, OFF_L2R = OFF_Q + 512,
+                     OFF_IDS = OFF_L2R + 256, OFF_DTS = OFF_IDS + MAXT * TM * 4, OFF_WRED = OFF_DTS + MAXT * TM * 4,
+                     OFF_BARS = OFF_WRED + 4 * 2 * EPI_WARPS * 4, SMEM_BYTES = OFF_BARS + 128 + 1024;
 static constexpr int COL_R = 2 * ACC_COLS;                    // TMEM: two gate accumulators, then two 16-column sum regions
+// setmaxnreg: 8*32*184 (epilogue) + 8*32*72 (producers) equals the launch allocation 512*128
+static_assert(EPI_WARPS * 32 * 184 + PROD_WARPS * 32 * 72 == THREADS * 128, "register split");
 
 struct Args {
     const void* q; int q_dt;
@@ -66,33 +70,41 @@ __device__ __forceinline__ float tmem_ld_1(uint32_t taddr) {
     return __uint_as_float(r);
 }
 
-struct Bars { uint64_t acc_full[2]; uint64_t pv_done[2]; uint32_t tmem_base; int abort_flag; };
+struct Bars {
+    uint64_t a_full[2];          // every producer warp has written its part of the A tile                 (8 arrivals)
+    uint64_t acc_full[2];        // gate product done (1 commit) + every producer warp's E rows have landed (8 arrivals)
+    uint64_t acc_empty[2];       // every epilogue warp has read the stage's accumulators                 (8 arrivals)
+    uint64_t v_full[2];          // every epilogue warp has written its rows of the column-sum operand     (8 arrivals)
+    uint64_t pv_done[2];         // column-sum product done: the E stages of that tile are free            (1 commit)
+    uint64_t hbar[2];            // per head: its four epilogue warps have published their maxima          (4 arrivals)
+    uint64_t drain;              // the two issuing lanes' products have completed (teardown)              (2 arrivals)
+    uint32_t tmem_base;
+    int abort_flag;
+    int drain_flag;
+};
+static_assert(sizeof(Bars) <= 128, "barrier block");
 
 template <bool SILU>
 __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    unsigned char* A_sh = sm + OFF_A;
+    unsigned char* A_sh = sm + OFF_A;       // [2 stages][128 rows][64 channels] fp16, K-major, 128-byte swizzle
     unsigned char* B_sh = sm + OFF_B;
     unsigned char* Ek_st = sm + OFF_EK;     // [2 stages][head][128 rows][8 chunks of 8 bf16, chunk ^ (row & 7)]
-    unsigned char* Ev_st = sm + OFF_EV;
-    unsigned char* V_sh = sm + OFF_V;       // [head][128 k][64 d] bf16, MN-major operand of the column sum
+    unsigned char* Ev_st = sm + OFF_EV;     // same; rewritten in place as (p * gate * E_v)[k, d], the MN-major operand of the column sum
     unsigned char* ones_sh = sm + OFF_ONES;
     float* q_sh = reinterpret_cast<float*>(sm + OFF_Q);                 // q / sqrt(hd) of the two heads
     float* l2r_sh = reinterpret_cast<float*>(sm + OFF_L2R);
     int* ids_sh = reinterpret_cast<int*>(sm + OFF_IDS);                 // slot of every row of this CTA's tiles, -1 = none
     float* dts_sh = reinterpret_cast<float*>(sm + OFF_DTS);             // steps since that slot's last update
-    float* sc_sh = reinterpret_cast<float*>(sm + OFF_SC);               // [128 rows][4 column groups] partial scores
-    float* wmax_sh = reinterpret_cast<float*>(sm + OFF_WRED);           // [16 warps] maxima, then [16 warps] sums of p
-    float* wsum_sh = wmax_sh + 16;
-    float* tile_sh = reinterpret_cast<float*>(sm + OFF_TILE);           // [tile][head] maximum, [tile][2 + head] sum of p
+    float* wred = reinterpret_cast<float*>(sm + OFF_WRED);              // [tile & 3][max | sum of p][epilogue warp]
     Bars* bars = reinterpret_cast<Bars*>(sm + OFF_BARS);
     volatile int* abort_flag = &bars->abort_flag;
 
     const int split = blockIdx.x, hp = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int cg = tid >> 7, row = tid & 127;                   // column group: head cg >> 1 of the pair, 32-column half cg & 1
-    const int hh = cg >> 1, half = cg & 1;
+    const int row = (warp & 3) * 32 + lane;                     // slot within the tile (== TMEM lane of the epilogue warps)
+    const bool is_epi = warp < EPI_WARPS;
     const int D = a.H * HD;
     const int na = min(a.n_active[b], a.Kcap);
     const int ntile_b = (na + TM - 1) / TM;
@@ -100,256 +112,269 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
     const int nt = min((ntile_b - split + a.S - 1) / a.S, MAXT);
 
     if (tid == 0) {
-        mbar_init(&bars->acc_full[0], 1);
-        mbar_init(&bars->acc_full[1], 1);
-        mbar_init(&bars->pv_done[0], 1);
-        mbar_init(&bars->pv_done[1], 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bars->a_full[i], PROD_WARPS);
+            mbar_init(&bars->acc_full[i], 1 + PROD_WARPS);
+            mbar_init(&bars->acc_empty[i], EPI_WARPS);
+            mbar_init(&bars->v_full[i], EPI_WARPS);
+            mbar_init(&bars->pv_done[i], 1);
+        }
+        mbar_init(&bars->hbar[0], 4);
+        mbar_init(&bars->hbar[1], 4);
+        mbar_init(&bars->drain, 2);
+        bars->drain_flag = 0;
         bars->abort_flag = *reinterpret_cast<volatile int*>(status);
         fence_barrier_init();
     }
-    if (warp == 0) {
+    if (warp == EPI_WARPS) {
         tmem_alloc(&bars->tmem_base, 512);
         tmem_relinquish();
     }
-    // B operand values first (independent loads), then the slot ids and their ages (two dependent rounds of loads)
-    float4 wv[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const int g = tid + THREADS * j, n = g >> 5, dd4 = (g & 31) * 4;
-        wv[j] = __ldg(reinterpret_cast<const float4*>(a.W + (size_t)n * D + hp * ACC_COLS + dd4));
-    }
-    const int t_now = a.t_dev ? *a.t_dev : a.t_now;
-    int vv[MAXT * TM / THREADS];
-#pragma unroll
-    for (int j = 0; j < MAXT * TM / THREADS; ++j) {
-        const int idx = tid + THREADS * j;
-        const int k = (split + (idx >> 7) * a.S) * TM + (idx & 127);
-        vv[j] = (idx < nt * TM && k < na) ? a.active[(size_t)b * a.Kcap + k] : -1;
-    }
-#pragma unroll
-    for (int j = 0; j < MAXT * TM / THREADS; ++j) {
-        const int idx = tid + THREADS * j;
-        if (idx < nt * TM) {
-            ids_sh[idx] = vv[j];
-            dts_sh[idx] = vv[j] >= 0 ? (float)(t_now - a.last_t[(size_t)b * a.V + vv[j]]) : 0.f;
-        }
-    }
-    __syncthreads();
-
-    // state row of this thread's slot in tile i, channels [16 cg, 16 cg + 16), straight into registers
-    float4 sreg[4];
-    auto load_state = [&](int i) {
-        const int v = i < nt ? ids_sh[i * TM + row] : -1;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-            sreg[j] = v >= 0 ? __ldg(reinterpret_cast<const float4*>(a.state + ((size_t)b * a.V + v) * N + 16 * cg + 4 * j))
-                             : make_float4(0.f, 0.f, 0.f, 0.f);
-    };
-    auto issue_emb = [&](int i) {
-        if (i < nt) {
-#pragma unroll
-            for (int kv = 0; kv < 2; ++kv) {
-                const __nv_bfloat16* E = kv == 0 ? a.Ek : a.Ev;
-                unsigned char* dst = (kv == 0 ? Ek_st : Ev_st) + (i & 1) * STAGE_BYTES;
-#pragma unroll
-                for (int e = 0; e < HPC; ++e)
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const int idx = tid + THREADS * j, r = idx >> 3, c = idx & 7;
-                        const int v = ids_sh[i * TM + r];
-                        if (v >= 0) cp_async16(dst + e * ATOM_BYTES + r * 128 + ((c ^ (r & 7)) << 4), E + (size_t)v * D + (hp * HPC + e) * HD + c * 8);
-                    }
-            }
-        }
-        cp_commit();
-    };
-    load_state(0);
-    issue_emb(0);
-    issue_emb(1);
-    {
-        const float wscale = SILU ? 0.5f : 1.0f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int g = tid + THREADS * j, n = g >> 5, dd4 = (g & 31) * 4;
-            // fp16 operands for the gate product (11 significant bits): state / 64 in the A tile, W * 64 here
-            *reinterpret_cast<__half*>(B_sh + sw128_off(dd4 + 0, n)) = __float2half_rn(wv[j].x * wscale * STATE_F16_UNSCALE);
-            *reinterpret_cast<__half*>(B_sh + sw128_off(dd4 + 1, n)) = __float2half_rn(wv[j].y * wscale * STATE_F16_UNSCALE);
-            *reinterpret_cast<__half*>(B_sh + sw128_off(dd4 + 2, n)) = __float2half_rn(wv[j].z * wscale * STATE_F16_UNSCALE);
-            *reinterpret_cast<__half*>(B_sh + sw128_off(dd4 + 3, n)) = __float2half_rn(wv[j].w * wscale * STATE_F16_UNSCALE);
+    {   // operands every tile shares: W (fp16, times 64; times 1/2 for SiLU), ones, decay logs, q; then this CTA's slots and ages
+        const float wscale = (SILU ? 0.5f : 1.0f) * STATE_F16_UNSCALE;
+        for (int idx = tid; idx < N * ACC_COLS / 4; idx += THREADS) {
+            const int n = idx >> 5, dd4 = (idx & 31) * 4;
+            const float4 w = __ldg(reinterpret_cast<const float4*>(a.W + (size_t)n * D + hp * ACC_COLS + dd4));
+            *reinterpret_cast<__half*>(B_sh + sw128_off(dd4 + 0, n)) = __float2half_rn(w.x * wscale);
+            *reinterpret_cast<__half*>(B_sh + sw128_off(dd4 + 1, n)) = __float2half_rn(w.y * wscale);
+            *reinterpret_cast<__half*>(B_sh + sw128_off(dd4 + 2, n)) = __float2half_rn(w.z * wscale);
+            *reinterpret_cast<__half*>(B_sh + sw128_off(dd4 + 3, n)) = __float2half_rn(w.w * wscale);
         }
         for (int i = tid; i < 1024; i += THREADS) reinterpret_cast<__nv_bfloat16*>(ones_sh)[i] = __float2bfloat16(1.0f);
         if (tid < N) l2r_sh[tid] = log2f(a.rhos[tid]);
         if (tid < ACC_COLS) q_sh[tid] = ld_dyn_f32(a.q, a.q_dt, ((size_t)b * a.H + hp * HPC) * HD + tid) * 0.125f;
-    }
-    // prefetched state registers -> decayed fp16 A tile; this thread: row `row`, channels [16 cg, 16 cg + 16)
-    auto convert = [&](int i) {
-        const bool ok = ids_sh[i * TM + row] >= 0;
-        const float dt = dts_sh[i * TM + row];
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-            uint4 pk = make_uint4(0u, 0u, 0u, 0u);
-            if (ok) {
-                const float4 s0 = sreg[2 * cc], s1 = sreg[2 * cc + 1];
-                const float* lr = l2r_sh + 16 * cg + cc * 8;
-                // state / 64 (STATE_F16_SCALE) folded into the exponent: 2^(dt log2 rho - 6)
-                pk.x = pack_f16x2(s0.x * ex2_approx(fmaf(dt, lr[0], -6.0f)), s0.y * ex2_approx(fmaf(dt, lr[1], -6.0f)));
-                pk.y = pack_f16x2(s0.z * ex2_approx(fmaf(dt, lr[2], -6.0f)), s0.w * ex2_approx(fmaf(dt, lr[3], -6.0f)));
-                pk.z = pack_f16x2(s1.x * ex2_approx(fmaf(dt, lr[4], -6.0f)), s1.y * ex2_approx(fmaf(dt, lr[5], -6.0f)));
-                pk.w = pack_f16x2(s1.z * ex2_approx(fmaf(dt, lr[6], -6.0f)), s1.w * ex2_approx(fmaf(dt, lr[7], -6.0f)));
-            }
-            *reinterpret_cast<uint4*>(A_sh + row * 128 + (((2 * cg + cc) ^ (row & 7)) << 4)) = pk;
+        const int t_now = a.t_dev ? *a.t_dev : a.t_now;
+        for (int idx = tid; idx < nt * TM; idx += THREADS) {
+            const int k = (split + (idx >> 7) * a.S) * TM + (idx & 127);
+            const int v = k < na ? a.active[(size_t)b * a.Kcap + k] : -1;
+            ids_sh[idx] = v;
+            dts_sh[idx] = v >= 0 ? (float)(t_now - a.last_t[(size_t)b * a.V + v]) : 0.f;
         }
-    };
-    const uint32_t idesc = umma_idesc_16(TM, ACC_COLS, 0, 0, 0, 0);      // fp16 state tile, fp16 W
-    const uint64_t da = umma_desc_k_sw128(smem_u32(A_sh)), db = umma_desc_k_sw128(smem_u32(B_sh));
-    auto issue_gate = [&](uint32_t tmem_base, int i) {
-#pragma unroll
-        for (int k16 = 0; k16 < 4; ++k16)
-            umma_bf16_ss(tmem_base + (uint32_t)((i & 1) * ACC_COLS), da + (uint64_t)((k16 * 32) >> 4), db + (uint64_t)((k16 * 32) >> 4), idesc, k16 != 0 ? 1u : 0u);
-        umma_commit(&bars->acc_full[i & 1]);
-    };
-
-    __syncthreads();                                            // B tile, q, ones, barriers and the TMEM address
-    tc_fence_after_sync();
-    const uint32_t tmem_base = bars->tmem_base;
-    convert(0);
+    }
     fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    if (tid == 0 && !bars->abort_flag) issue_gate(tmem_base, 0);
-    load_state(1);
+    const uint32_t tmem_base = bars->tmem_base;
 
-    // running softmax state of output column `row` of the head pair (threads of column group 0), head row >> 6
-    float m_run = -INFINITY, l_run = 0.f, o_run = 0.f;
-    const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-    auto fold = [&](int j) {        // tile j's column sums (its PV product has completed) into the running state
-        const float mt = tile_sh[j * 4 + (row >> 6)], lt = tile_sh[j * 4 + 2 + (row >> 6)];
-        const float v = tmem_ld_1(t_lane + (uint32_t)(COL_R + (j & 1) * 16));
-        tmem_wait_ld();
-        const float m_new = fmaxf(m_run, mt);
-        const float c_old = __expf(m_run - m_new), c_new = __expf(mt - m_new);     // exp(-inf) = 0 on the first tile
-        o_run = o_run * c_old + v * c_new;
-        l_run = l_run * c_old + lt * c_new;
-        m_run = m_new;
-    };
-
-    for (int i = 0; i < nt; ++i) {
-        if (!bars->abort_flag) mbar_wait(&bars->acc_full[i & 1], (uint32_t)((i >> 1) & 1), abort_flag);   // A tile free, accumulators of tile i ready
-        tc_fence_after_sync();
-        if (i + 1 < nt) {
-            convert(i + 1);
-            fence_proxy_async_smem();
-            tc_fence_before_sync();
-        }
-        cp_wait<1>();                                           // embedding stages of tile i (this thread's copies)
-        __syncthreads();                                        // ... everyone's, and the whole A tile of tile i + 1
-        tc_fence_after_sync();
-        if (i + 1 < nt && tid == 0 && !bars->abort_flag) issue_gate(tmem_base, i + 1);
-        load_state(i + 2);
-
-        const bool ok = ids_sh[i * TM + row] >= 0;
-        const uint32_t t_acc = t_lane + (uint32_t)((i & 1) * ACC_COLS + hh * HD + half * 32);
-        const unsigned char* ekrow = Ek_st + (i & 1) * STAGE_BYTES + hh * ATOM_BYTES + row * 128;
-        const unsigned char* evrow = Ev_st + (i & 1) * STAGE_BYTES + hh * ATOM_BYTES + row * 128;
-        const float* qh = q_sh + hh * HD + half * 32;
-        // ---- gate of this thread's 32 columns (kept) and its part of the score
-        float g[32];
-        float sp[2] = {0.f, 0.f};
-        {
-            float pre[32];
-            tmem_ld_32x32b_x32(t_acc, pre);
-            tmem_wait_ld();
+    if (!is_epi) {
+        // ============================================================ producer warps: two threads per slot of the tile
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+        const int pw = warp - EPI_WARPS, ptid = tid - EPI_WARPS * 32;
+        const int prow = ptid & 127, phalf = ptid >> 7;            // this thread: slot prow of the tile, channels [32 phalf, 32 phalf + 32)
+        const uint32_t idesc = umma_idesc_16(TM, ACC_COLS, 0, 0, 0, 0);      // fp16 state tile, fp16 W
+        const uint32_t idesc2 = umma_idesc_bf16(ACC_COLS, 16, 1, 0);         // column sum: A = tile (MN-major), B = ones
+        const uint64_t db = umma_desc_k_sw128(smem_u32(B_sh)), d1 = umma_desc_k_sw128(smem_u32(ones_sh));
+        auto issue_pv = [&](int j) {        // column sums of tile j, once the epilogue has written the operand
+            if (!mbar_wait(&bars->v_full[j & 1], (uint32_t)((j >> 1) & 1), abort_flag, 5)) return;
+            tc_fence_after_sync();
+            const uint64_t dv = umma_desc_mn_sw128(smem_u32(Ev_st + (j & 1) * STAGE_BYTES), ATOM_BYTES, 1024);
 #pragma unroll
-            for (int j8 = 0; j8 < 4; ++j8) {
-                const uint4 e = *reinterpret_cast<const uint4*>(ekrow + (((half * 4 + j8) ^ (row & 7)) << 4));
-                const uint32_t ew[4] = {e.x, e.y, e.z, e.w};
+            for (int ks = 0; ks < TM / 16; ++ks)
+                umma_bf16_ss(tmem_base + (uint32_t)(COL_R + (j & 1) * 16), dv + (uint64_t)(ks * (2048 >> 4)), d1, idesc2, ks != 0 ? 1u : 0u);
+            umma_commit(&bars->pv_done[j & 1]);
+        };
+        // this thread's half of its slot's state row, all of it in flight at once (32 registers), one tile ahead of its use
+        float4 sr[8];
+        auto load_state = [&](int i) {
+            const int v = i < nt ? ids_sh[i * TM + prow] : -1;
+            const float4* src = reinterpret_cast<const float4*>(a.state + ((size_t)b * a.V + (v >= 0 ? v : 0)) * N + 32 * phalf);
 #pragma unroll
-                for (int pr = 0; pr < 4; ++pr) {
-                    const int j = j8 * 8 + pr * 2;
-                    const float h0 = pre[j], h1 = pre[j + 1];
-                    g[j] = SILU ? fmaf(h0, tanh_approx(h0), h0) : h0;
-                    g[j + 1] = SILU ? fmaf(h1, tanh_approx(h1), h1) : h1;
-                    sp[0] = fmaf(g[j] * qh[j], bf16_lo(ew[pr]), sp[0]);
-                    sp[1] = fmaf(g[j + 1] * qh[j + 1], bf16_hi(ew[pr]), sp[1]);
+            for (int j = 0; j < 8; ++j) sr[j] = v >= 0 ? __ldg(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        };
+        load_state(0);
+        for (int i = 0; i < nt; ++i) {
+            const int st = i & 1, u = i >> 1;
+            // the stages of tile i - 2 are free once its column sum has completed (which also means: its gate product has,
+            // and the epilogue is done with its E_k rows and accumulators)
+            if (i >= 2 && !__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[st], (uint32_t)((u - 1) & 1), abort_flag, 1))) break;
+            {   // E_k / E_v rows of the tile: 16 copies of 16 bytes a thread.  The slot ids are fetched first: a copy is a compiler
+                // barrier, so an id load between two copies would put a shared-memory latency in front of every one of them
+                int vj[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) vj[j] = ids_sh[i * TM + ((ptid + PROD_WARPS * 32 * j) >> 3)];
+                const int c = ptid & 7;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int r = (ptid + PROD_WARPS * 32 * j) >> 3;
+                    if (vj[j] >= 0) {
+                        const size_t src = (size_t)vj[j] * D + hp * ACC_COLS + c * 8;
+                        const int dst = st * STAGE_BYTES + r * 128 + ((c ^ (r & 7)) << 4);
+                        cp_async16(Ek_st + dst, a.Ek + src);
+                        cp_async16(Ek_st + dst + ATOM_BYTES, a.Ek + src + HD);
+                        cp_async16(Ev_st + dst, a.Ev + src);
+                        cp_async16(Ev_st + dst + ATOM_BYTES, a.Ev + src + HD);
+                    }
                 }
             }
-        }
-        sc_sh[row * 4 + cg] = sp[0] + sp[1];
-        tc_fence_before_sync();
-        __syncthreads();                                        // both halves of every score; accumulators of tile i read
-        const float s = ok ? sc_sh[row * 4 + 2 * hh] + sc_sh[row * 4 + 2 * hh + 1] : -INFINITY;
-        {
-            float mx = s;
+            cp_commit();
+            {   // this thread's slot: state row (fetched an iteration ago) -> decayed fp16 row of the A tile (state / 64 folded into the exponent)
+                const float dt = dts_sh[i * TM + prow];
+                unsigned char* arow = A_sh + st * ATOM_BYTES + prow * 128;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            if (lane == 0) wmax_sh[warp] = mx;
-        }
-        __syncthreads();
-        const float mt = fmaxf(fmaxf(wmax_sh[8 * hh], wmax_sh[8 * hh + 1]), fmaxf(wmax_sh[8 * hh + 2], wmax_sh[8 * hh + 3]));
-        const float prob = ok ? __expf(s - mt) : 0.f;            // every tile holds at least one slot, so mt is finite
-        if (half == 0) {
-            const float ps = warp_sum(prob);
-            if (lane == 0) wsum_sh[warp] = ps;
-        }
-        // ---- V tile: (p * gate * E_v)[k, d] in bf16; the column sum of tile i - 2 used the other TMEM region, the V tile
-        // itself was last read by the product of tile i - 1
-        if (i > 0 && !bars->abort_flag) mbar_wait(&bars->pv_done[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1), abort_flag);
-        tc_fence_after_sync();
-        {
-            unsigned char* vrow = V_sh + hh * ATOM_BYTES + row * 128;
+                for (int cc = 0; cc < 4; ++cc) {                    // chunks of 8 channels
+                    const int ch = phalf * 4 + cc;
+                    const float4 la = *reinterpret_cast<const float4*>(l2r_sh + ch * 8), lb = *reinterpret_cast<const float4*>(l2r_sh + ch * 8 + 4);
+                    const float4 s0 = sr[2 * cc], s1 = sr[2 * cc + 1];
+                    uint4 pk;
+                    pk.x = pack_f16x2(s0.x * ex2_approx(fmaf(dt, la.x, -6.0f)), s0.y * ex2_approx(fmaf(dt, la.y, -6.0f)));
+                    pk.y = pack_f16x2(s0.z * ex2_approx(fmaf(dt, la.z, -6.0f)), s0.w * ex2_approx(fmaf(dt, la.w, -6.0f)));
+                    pk.z = pack_f16x2(s1.x * ex2_approx(fmaf(dt, lb.x, -6.0f)), s1.y * ex2_approx(fmaf(dt, lb.y, -6.0f)));
+                    pk.w = pack_f16x2(s1.z * ex2_approx(fmaf(dt, lb.z, -6.0f)), s1.w * ex2_approx(fmaf(dt, lb.w, -6.0f)));
+                    *reinterpret_cast<uint4*>(arow + ((ch ^ (prow & 7)) << 4)) = pk;
+                }
+                load_state(i + 1);                                  // in flight over the rest of this iteration and the next wait
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->a_full[st]);
+            if (pw == 0 && lane == 0) {      // gate product of tile i
+                bool go = mbar_wait(&bars->a_full[st], (uint32_t)(u & 1), abort_flag, 3);
+                if (go && i >= 2) go = mbar_wait(&bars->acc_empty[st], (uint32_t)((u - 1) & 1), abort_flag, 4);
+                if (go) {
+                    tc_fence_after_sync();
+                    const uint64_t da = umma_desc_k_sw128(smem_u32(A_sh + st * ATOM_BYTES));
 #pragma unroll
-            for (int j8 = 0; j8 < 4; ++j8) {
-                const uint4 e = *reinterpret_cast<const uint4*>(evrow + (((half * 4 + j8) ^ (row & 7)) << 4));
+                    for (int k16 = 0; k16 < 4; ++k16)
+                        umma_bf16_ss(tmem_base + (uint32_t)(st * ACC_COLS), da + (uint64_t)((k16 * 32) >> 4), db + (uint64_t)((k16 * 32) >> 4), idesc, k16 != 0 ? 1u : 0u);
+                    umma_commit(&bars->acc_full[st]);
+                }
+            }
+            cp_wait<0>();                    // this thread's E rows of tile i have landed
+            __syncwarp();                    // ... and so have the other lanes'
+            if (lane == 0) mbar_arrive(&bars->acc_full[st]);
+            if (pw == 1 && lane == 0 && i >= 1) issue_pv(i - 1);
+            __syncwarp();
+        }
+        if (pw == 1 && lane == 0 && nt > 0 && !*abort_flag) issue_pv(nt - 1);
+        cp_wait<0>();
+        if (lane == 0 && pw < 2) umma_commit(&bars->drain);      // arrives once every product this lane issued has completed
+    } else {
+        // ============================================================ epilogue warps: a warpgroup per head, a thread per slot
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
+        const int wg = warp >> 2;                                   // head of the pair
+        const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        const float* qh = q_sh + wg * HD;
+        float m_run = -INFINITY, l_run = 0.f, o_run = 0.f;          // warpgroup 0: running softmax state of output column `row`
+        const int hc = row >> 6;                                    // ... which belongs to head hc of the pair
+        auto fold = [&](int j) {        // tile j's column sums (its product has completed) into the running state
+            const float* wm = wred + (j & 3) * 2 * EPI_WARPS + hc * 4;
+            const float* ws = wm + EPI_WARPS;
+            const float mt = fmaxf(fmaxf(wm[0], wm[1]), fmaxf(wm[2], wm[3]));
+            const float lt = (ws[0] + ws[1]) + (ws[2] + ws[3]);
+            const float v = tmem_ld_1(t_lane + (uint32_t)(COL_R + (j & 1) * 16));
+            tmem_wait_ld();
+            const float m_new = fmaxf(m_run, mt);
+            const float c_old = __expf(m_run - m_new), c_new = __expf(mt - m_new);     // exp(-inf) = 0 on the first tile
+            o_run = o_run * c_old + v * c_new;
+            l_run = l_run * c_old + lt * c_new;
+            m_run = m_new;
+        };
+        bool alive = true;
+        for (int i = 0; i < nt; ++i) {
+            const int st = i & 1, u = i >> 1;
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars->acc_full[st], (uint32_t)(u & 1), abort_flag, 6))) { alive = false; break; }
+            tc_fence_after_sync();
+            const bool ok = ids_sh[i * TM + row] >= 0;
+            const uint32_t t_acc = t_lane + (uint32_t)(st * ACC_COLS + wg * HD);
+            const unsigned char* ekrow = Ek_st + st * STAGE_BYTES + wg * ATOM_BYTES + row * 128;
+            unsigned char* evrow = Ev_st + st * STAGE_BYTES + wg * ATOM_BYTES + row * 128;
+            // ---- gate of the head's 64 columns (kept) and the score
+            float g[HD];
+            float sp0 = 0.f, sp1 = 0.f;
+            {
+                float pre[2][16];
+                tmem_ld_32x32b_x16(t_acc, pre[0]);
+#pragma unroll
+                for (int c = 0; c < HD / 16; ++c) {              // 16 accumulator columns per load, the next load in flight
+                    tmem_wait_ld();
+                    if (c + 1 < HD / 16) tmem_ld_32x32b_x16(t_acc + (c + 1) * 16, pre[(c + 1) & 1]);
+#pragma unroll
+                    for (int j8 = 0; j8 < 2; ++j8) {
+                        const int ch = c * 2 + j8;               // chunk of 8 columns
+                        const uint4 e = *reinterpret_cast<const uint4*>(ekrow + ((ch ^ (row & 7)) << 4));
+                        const uint32_t ew[4] = {e.x, e.y, e.z, e.w};
+                        const float4 qa = *reinterpret_cast<const float4*>(qh + ch * 8), qb = *reinterpret_cast<const float4*>(qh + ch * 8 + 4);
+                        const float qv[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};      // broadcast reads
+#pragma unroll
+                        for (int pr = 0; pr < 4; ++pr) {
+                            const int j = ch * 8 + pr * 2;
+                            const float h0 = pre[c & 1][j8 * 8 + pr * 2], h1 = pre[c & 1][j8 * 8 + pr * 2 + 1];
+                            g[j] = SILU ? fmaf(h0, tanh_approx(h0), h0) : h0;
+                            g[j + 1] = SILU ? fmaf(h1, tanh_approx(h1), h1) : h1;
+                            sp0 = fmaf(g[j] * qv[pr * 2], bf16_lo(ew[pr]), sp0);
+                            sp1 = fmaf(g[j + 1] * qv[pr * 2 + 1], bf16_hi(ew[pr]), sp1);
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->acc_empty[st]);       // accumulators read
+            // ---- tile maximum of the head: warp shuffles, then the four warps meet on an mbarrier (bounded, unlike bar.sync)
+            const float s = ok ? sp0 + sp1 : -INFINITY;
+            float* wm = wred + (i & 3) * 2 * EPI_WARPS;
+            {
+                float mx = s;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                if (lane == 0) {
+                    wm[warp] = mx;
+                    mbar_arrive(&bars->hbar[wg]);
+                }
+            }
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars->hbar[wg], (uint32_t)(i & 1), abort_flag, 8))) { alive = false; break; }
+            const float mt = fmaxf(fmaxf(wm[wg * 4], wm[wg * 4 + 1]), fmaxf(wm[wg * 4 + 2], wm[wg * 4 + 3]));
+            const float prob = ok ? __expf(s - mt) : 0.f;            // every tile holds at least one slot, so mt is finite
+            {
+                const float ps = warp_sum(prob);
+                if (lane == 0) wm[EPI_WARPS + warp] = ps;
+            }
+            // ---- (p * gate * E_v)[k, d] in bf16, over the E_v rows themselves
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+                unsigned char* cp = evrow + ((ch ^ (row & 7)) << 4);
+                const uint4 e = *reinterpret_cast<const uint4*>(cp);
                 const uint32_t ew[4] = {e.x, e.y, e.z, e.w};
                 uint32_t w[4];
 #pragma unroll
                 for (int pr = 0; pr < 4; ++pr) {
-                    const int j = j8 * 8 + pr * 2;
+                    const int j = ch * 8 + pr * 2;
                     w[pr] = ok ? mul_bf16x2(pack_bf16x2(prob * g[j], prob * g[j + 1]), ew[pr]) : 0u;
                 }
-                st_shared_v4(vrow + (((half * 4 + j8) ^ (row & 7)) << 4), w[0], w[1], w[2], w[3]);
+                st_shared_v4(cp, w[0], w[1], w[2], w[3]);
+            }
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->v_full[st]);          // operand rows (and this warp's maximum and sum) are in place
+            if (wg == 0 && i > 0) {     // fold tile i - 1 while the column sum of tile i is on its way
+                if (!__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1), abort_flag, 7))) { alive = false; break; }
+                tc_fence_after_sync();
+                fold(i - 1);
             }
         }
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        __syncthreads();                // V tile written, embedding stages read, per-warp sums of p stored, by every warp
-        tc_fence_after_sync();
-        if (tid == 0 && !bars->abort_flag) {
-            const uint32_t idesc2 = umma_idesc_bf16(ACC_COLS, 16, 1, 0);
-            const uint64_t dv = umma_desc_mn_sw128(smem_u32(V_sh), ATOM_BYTES, 1024), d1 = umma_desc_k_sw128(smem_u32(ones_sh));
-#pragma unroll
-            for (int ks = 0; ks < TM / 16; ++ks)
-                umma_bf16_ss(tmem_base + (uint32_t)(COL_R + (i & 1) * 16), dv + (uint64_t)(ks * (2048 >> 4)), d1, idesc2, ks != 0 ? 1u : 0u);
-            umma_commit(&bars->pv_done[i & 1]);
-        }
-        if (tid < 2) {                  // head `tid`: this tile's maximum and sum of p (column-group 2 tid holds half 0)
-            tile_sh[i * 4 + tid] = fmaxf(fmaxf(wmax_sh[8 * tid], wmax_sh[8 * tid + 1]), fmaxf(wmax_sh[8 * tid + 2], wmax_sh[8 * tid + 3]));
-            tile_sh[i * 4 + 2 + tid] = wsum_sh[8 * tid] + wsum_sh[8 * tid + 1] + wsum_sh[8 * tid + 2] + wsum_sh[8 * tid + 3];
-        }
-        if (i > 0 && cg == 0) fold(i - 1);      // its product completed (waited for above); tile_sh[i - 1] was written an iteration ago
-        issue_emb(i + 2);
-    }
-    cp_wait<0>();
-    if (!bars->abort_flag) mbar_wait(&bars->pv_done[(nt - 1) & 1], (uint32_t)(((nt - 1) >> 1) & 1), abort_flag);
-    tc_fence_after_sync();
-    __syncthreads();                                            // tile_sh of the last tile
-    if (cg == 0) {
-        fold(nt - 1);
-        float* part = a.part + (((size_t)b * (a.H / HPC) + hp) * a.S + split) * PART_FLOATS;
-        part[row] = o_run;
-        if ((row & 63) == 0) {
-            part[ACC_COLS + (row >> 6)] = m_run;
-            part[ACC_COLS + 2 + (row >> 6)] = l_run;
+        if (wg == 0 && alive && nt > 0 &&
+            __all_sync(0xffffffffu, mbar_wait(&bars->pv_done[(nt - 1) & 1], (uint32_t)(((nt - 1) >> 1) & 1), abort_flag, 7))) {
+            tc_fence_after_sync();
+            fold(nt - 1);
+            float* part = a.part + (((size_t)b * (a.H / HPC) + hp) * a.S + split) * PART_FLOATS;
+            part[row] = o_run;
+            if ((row & 63) == 0) {
+                part[ACC_COLS + hc] = m_run;
+                part[ACC_COLS + 2 + hc] = l_run;
+            }
         }
     }
+    // ---------------------------------------------------------------- teardown
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 0) {
+    if (warp == EPI_WARPS) {
+        mbar_wait<100>(&bars->drain, 0u, &bars->drain_flag, 9);    // bounded: no product of this CTA is in flight when TMEM is released
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, 512);
     }
-    if (tid == 0 && bars->abort_flag) atomicOr(status, bars->abort_flag);   // sticky: never cleared by the library
+    if (tid == 0 && (bars->abort_flag | bars->drain_flag)) atomicOr(status, bars->abort_flag | bars->drain_flag);   // sticky: never cleared by the library
 }
 
 // O[b, h, :] from the partials of the CTAs that walked sequence b: softmax over all V_total slots (the never-seen
