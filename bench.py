@@ -426,7 +426,7 @@ def decode_bench(dev, mode):
     return {"workload": "streaming decode: 64 sequences, resident [50257 x 64] fp32 state each, 6 x attend + update per step",
             "value": d["B"] / ms * 1000.0, "unit": "tokens/s", "steps": d["steps"], "warmup": d["warmup"],
             "ms_per_step": ms, "mode": s["mode"], "launch": "one CUDA graph replay per step",
-            "active_slots_per_sequence": [n0, n1], "gpu_launches_per_step": L + 2,
+            "active_slots_per_sequence": [n0, n1], "gpu_launches_per_step": 2 * L + 2,
             "roofline": {"bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": pk["hbm"], "unit": "GB/s",
                          "frac": nbytes / ms / 1e6 / pk["hbm"], "bytes_per_step": nbytes}}
 
