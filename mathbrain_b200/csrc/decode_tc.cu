@@ -254,7 +254,9 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
         const int wg = warp >> 2;                                   // head of the pair
         const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-        const float* qh = q_sh + wg * HD;
+        uint32_t q2[HD / 2];                                        // q / sqrt(hd) of this head as packed bf16 pairs
+#pragma unroll
+        for (int j = 0; j < HD / 2; ++j) q2[j] = pack_bf16x2(q_sh[wg * HD + 2 * j], q_sh[wg * HD + 2 * j + 1]);
         float m_run = -INFINITY, l_run = 0.f, o_run = 0.f;          // warpgroup 0: running softmax state of output column `row`
         const int hc = row >> 6;                                    // ... which belongs to head hc of the pair
         auto fold = [&](int j) {        // tile j's column sums (its product has completed) into the running state
@@ -280,7 +282,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
             const unsigned char* ekrow = Ek_st + st * STAGE_BYTES + wg * ATOM_BYTES + row * 128;
             unsigned char* evrow = Ev_st + st * STAGE_BYTES + wg * ATOM_BYTES + row * 128;
             // ---- gate of the head's 64 columns (kept) and the score
-            float g[HD];
+            uint32_t g2[HD / 2];                                    // packed bf16 pairs
             float sp0 = 0.f, sp1 = 0.f;
             {
                 float pre[2][16];
@@ -294,16 +296,15 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
                         const int ch = c * 2 + j8;               // chunk of 8 columns
                         const uint4 e = *reinterpret_cast<const uint4*>(ekrow + ((ch ^ (row & 7)) << 4));
                         const uint32_t ew[4] = {e.x, e.y, e.z, e.w};
-                        const float4 qa = *reinterpret_cast<const float4*>(qh + ch * 8), qb = *reinterpret_cast<const float4*>(qh + ch * 8 + 4);
-                        const float qv[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};      // broadcast reads
 #pragma unroll
                         for (int pr = 0; pr < 4; ++pr) {
-                            const int j = ch * 8 + pr * 2;
+                            const int w = ch * 4 + pr;               // pair of columns
                             const float h0 = pre[c & 1][j8 * 8 + pr * 2], h1 = pre[c & 1][j8 * 8 + pr * 2 + 1];
-                            g[j] = SILU ? fmaf(h0, tanh_approx(h0), h0) : h0;
-                            g[j + 1] = SILU ? fmaf(h1, tanh_approx(h1), h1) : h1;
-                            sp0 = fmaf(g[j] * qv[pr * 2], bf16_lo(ew[pr]), sp0);
-                            sp1 = fmaf(g[j + 1] * qv[pr * 2 + 1], bf16_hi(ew[pr]), sp1);
+                            const float g0 = SILU ? fmaf(h0, tanh_approx(h0), h0) : h0;
+                            const float g1 = SILU ? fmaf(h1, tanh_approx(h1), h1) : h1;
+                            g2[w] = pack_bf16x2(g0, g1);
+                            // bf16 x bf16 products are exact in fp32, where the score is summed
+                            fma_f32_bf16x2(sp0, sp1, g2[w], mul_bf16x2(q2[w], ew[pr]));
                         }
                     }
                 }
@@ -326,6 +327,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
             if (!__all_sync(0xffffffffu, mbar_wait(&bars->hbar[wg], (uint32_t)(i & 1), abort_flag, 8))) { alive = false; break; }
             const float mt = fmaxf(fmaxf(wm[wg * 4], wm[wg * 4 + 1]), fmaxf(wm[wg * 4 + 2], wm[wg * 4 + 3]));
             const float prob = ok ? __expf(s - mt) : 0.f;            // every tile holds at least one slot, so mt is finite
+            const uint32_t p2 = pack_bf16x2(prob, prob);
             {
                 const float ps = warp_sum(prob);
                 if (lane == 0) wm[EPI_WARPS + warp] = ps;
@@ -338,10 +340,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
                 const uint32_t ew[4] = {e.x, e.y, e.z, e.w};
                 uint32_t w[4];
 #pragma unroll
-                for (int pr = 0; pr < 4; ++pr) {
-                    const int j = ch * 8 + pr * 2;
-                    w[pr] = ok ? mul_bf16x2(pack_bf16x2(prob * g[j], prob * g[j + 1]), ew[pr]) : 0u;
-                }
+                for (int pr = 0; pr < 4; ++pr) w[pr] = ok ? mul_bf16x2(mul_bf16x2(g2[ch * 4 + pr], p2), ew[pr]) : 0u;   // rows without a slot hold stale bytes
                 st_shared_v4(cp, w[0], w[1], w[2], w[3]);
             }
             fence_proxy_async_smem();
