@@ -33,7 +33,7 @@ static constexpr int ATOM_BYTES = TM * 128;
 static constexpr int ACC_COLS = HPC * HD;
 // Per channel count N = 64 * NK (NK = 1, 2): stages and the TMEM map
 //   NK = 1: gate 2 x 128 | dW^T 64  | dE_k 16 | dE_v 16 | ... | dQ 128 at column 384
-//   NK = 2: gate 1 x 128 | dW^T 128 | dE_k 16 | dE_v 16 | ... | dQ 128 at column 384
+//   NK = 2: gate 1 x 128 | dW^T 128 | dE_k 16 | dE_v 16 | ... | decay powers 64 at column 320 | dQ 128 at column 384
 template <int NK> struct Cfg {
     static constexpr int N = 64 * NK;
     static constexpr int NA = 2;                       // A-tile / E-row stages in shared memory (32 KB each, see STAGE_BYTES)
@@ -42,6 +42,7 @@ template <int NK> struct Cfg {
     static constexpr int COL_DEK = COL_DW + N;         // dE_k column sums (16 columns, all equal)
     static constexpr int COL_DEV = COL_DEK + 16;
     static constexpr int COL_DQ = 384;                 // dQ accumulators [128 t x (2 heads x 64)] fp32, one row per thread
+    static constexpr int COL_RT = 320;                 // NK = 2 only: the row's decay powers as 64 packed fp16 pairs (columns 320..383 are free there)
 };
 static constexpr int TMEM_COLS = 512;
 // every producer warp prefetches into its own ring: the slot's fp16 snapshot row (N <= 128) and the 32 columns of E_k / E_v
@@ -108,7 +109,7 @@ __device__ __forceinline__ float tmem_ld_1(uint32_t taddr) {
 template <bool SILU, int NK, bool ROWS>
 __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* status) {
     constexpr int N = Cfg<NK>::N, NA = Cfg<NK>::NA, NACC = Cfg<NK>::NACC;
-    constexpr int COL_DW = Cfg<NK>::COL_DW, COL_DEK = Cfg<NK>::COL_DEK, COL_DEV = Cfg<NK>::COL_DEV, COL_DQ = Cfg<NK>::COL_DQ;
+    constexpr int COL_DW = Cfg<NK>::COL_DW, COL_DEK = Cfg<NK>::COL_DEK, COL_DEV = Cfg<NK>::COL_DEV, COL_DQ = Cfg<NK>::COL_DQ, COL_RT = Cfg<NK>::COL_RT;
     constexpr int STAGE_BYTES = 2 * ATOM_BYTES;
     extern __shared__ unsigned char smem_raw[];
     // 1024-byte alignment for the swizzled operand tiles; the offset is added to the __shared__ array itself so that the
@@ -330,13 +331,35 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
 #pragma unroll
             for (int j = 0; j < 32; ++j) R2[j] = *reinterpret_cast<const uint32_t*>(Rb_sh + row * N + 2 * j);
         }
+        // NK = 2: this row's 128 powers as packed fp16 pairs do not fit the registers, and rebuilding them from the two-level
+        // table for every slot (four 16-byte table loads, eight multiplies and four conversions per eight channels) made the
+        // producers the critical path.  They are built once and parked in 64 unused TMEM columns of the thread's own lane;
+        // a slot reads them back with four tcgen05.ld.  Same values as before: fp16 of the fp32 two-level product.
+        const uint32_t t_rt = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)COL_RT;
+        if (NK == 2) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float buf[16];
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4) {
+                    float rr[8];
+                    decay8(row, (q * 4 + c4) * 8, rr);
+                    buf[c4 * 4 + 0] = __uint_as_float(pack_f16x2(rr[0], rr[1]));
+                    buf[c4 * 4 + 1] = __uint_as_float(pack_f16x2(rr[2], rr[3]));
+                    buf[c4 * 4 + 2] = __uint_as_float(pack_f16x2(rr[4], rr[5]));
+                    buf[c4 * 4 + 3] = __uint_as_float(pack_f16x2(rr[6], rr[7]));
+                }
+                tmem_st_32x32b_x16(t_rt + q * 16, buf);
+            }
+            tmem_wait_st();
+        }
         for (int j = 0; j < PD; ++j) prefetch(j);
         for (int i = 0; i < n_slots; ++i) {
             const int sa = i % NA, sc = i % NACC;
             prefetch(i + PD);
             asm volatile("cp.async.wait_group %0;" ::"n"(PD) : "memory");   // this lane's copies for slot i have landed
             __syncwarp();                                                      // ... and so have the other lanes'
-            if (i >= NA && !mbar_wait(&a_free[sa], (uint32_t)((i / NA - 1) & 1), abort_flag, 2, &bars->spin_limit)) break;   // gave up: drain and leave
+            if (i >= NA && !__all_sync(0xffffffffu, mbar_wait(&a_free[sa], (uint32_t)((i / NA - 1) & 1), abort_flag, 2, &bars->spin_limit))) break;   // gave up (the whole warp leaves together): drain and leave
             const int keyf = key_sh[i];
             const int key = keyf & 0x7fffffff;
             const unsigned char* rg = ring_w + (i % RING) * RING_STAGE_BYTES;
@@ -364,6 +387,29 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                 }
             }
             unsigned char* Arow = A_sh + sa * STAGE_BYTES + row * 128;
+            if (NK == 2) {
+                // every lane builds the cold row (snapshot times parked powers; the TMEM loads are warp-wide), lanes whose
+                // token occurs in the tile overwrite it below
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float rv[16];
+                    tmem_ld_32x32b_x16(t_rt + q * 16, rv);
+                    uint4 sv[4];
+#pragma unroll
+                    for (int c4 = 0; c4 < 4; ++c4) sv[c4] = *reinterpret_cast<const uint4*>(rg + (q * 4 + c4) * 16);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int c4 = 0; c4 < 4; ++c4) {
+                        const int cc = q * 4 + c4;
+                        uint4 pk;
+                        pk.x = mul_f16x2(sv[c4].x, __float_as_uint(rv[c4 * 4 + 0]));
+                        pk.y = mul_f16x2(sv[c4].y, __float_as_uint(rv[c4 * 4 + 1]));
+                        pk.z = mul_f16x2(sv[c4].z, __float_as_uint(rv[c4 * 4 + 2]));
+                        pk.w = mul_f16x2(sv[c4].w, __float_as_uint(rv[c4 * 4 + 3]));
+                        *reinterpret_cast<uint4*>(Arow + (cc >> 3) * ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) = pk;
+                    }
+                }
+            }
             if (s >= 0) {   // restart from the token's own state at its last in-tile occurrence (+1)
                 const float* base = a.tok_state + ((size_t)b * a.T + t0 + s) * N;
 #pragma unroll 2
@@ -387,7 +433,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                     pk.x = mul_f16x2(pk.x, rv.x); pk.y = mul_f16x2(pk.y, rv.y); pk.z = mul_f16x2(pk.z, rv.z); pk.w = mul_f16x2(pk.w, rv.w);
                     *reinterpret_cast<uint4*>(Arow + (cc >> 3) * ATOM_BYTES + (((cc & 7) ^ (row & 7)) << 4)) = pk;
                 }
-            } else {
+            } else if (NK == 1) {
                 // snapshot times decay power.  All loads come first: the compiler cannot move a shared-memory load above an
                 // earlier shared-memory store (it cannot tell the buffers apart), so a load-multiply-store loop would run as
                 // N / 8 load latencies in a row.
