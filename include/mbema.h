@@ -275,10 +275,11 @@ int mbema_decode_attend(const void* q, int q_dtype, const void* E_k, const void*
                         const int32_t* n_active, float* O, int64_t B, int64_t H, int64_t hd, int64_t V, int64_t N,
                         int64_t Kcap, int64_t t_now, int64_t V_total, int flags, const int32_t* t_now_dev,
                         void* stream);
-/* Tensor-core variant of mbema_decode_attend (bf16 operands, fp32 accumulation; N = 64, hd = 64, H even, E_k/E_v
- * stored as bf16): two
- * tcgen05 passes over 128-slot tiles with a softmax over all V_total slots between them.  Same arguments plus a
- * workspace of mbema_decode_attend_tc_workspace_bytes(B, H, Kcap) bytes; O is zeroed and accumulated by the call.
+/* Tensor-core variant of mbema_decode_attend (16-bit operands, fp32 accumulation; N = 64, hd = 64, H even, E_k/E_v
+ * stored as bf16): one walk over the seen slots in 128-slot tiles (tcgen05 gate product, online softmax per CTA, the
+ * P.V column sums by a second tcgen05 product), per-CTA partials in the workspace, then a merge kernel that writes O
+ * with the softmax over all V_total slots.  Same arguments plus a workspace of
+ * mbema_decode_attend_tc_workspace_bytes(B, H, Kcap) bytes; O is written by the call.
  * The int32 at the start of the workspace is the status word described under Conventions. */
 size_t mbema_decode_attend_tc_workspace_bytes(int64_t B, int64_t H, int64_t Kcap);
 int mbema_decode_attend_tc(const void* q, int q_dtype, const void* E_k, const void* E_v, int e_dtype,
