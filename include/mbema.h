@@ -54,8 +54,9 @@ extern "C" {
                                    /* mathbrain/flash_ema_attention.py:76-79                               */
 #define MBEMA_FLAG_CBASE_EXTRA_DECAY 4 /* M_0 = rho * c_base (mathbrain/triton_flash_ema.py:48-50,185)     */
 #define MBEMA_FLAG_FP32_BACKWARD 8     /* MBEMA_MODE_TC_BF16 only: run the backward with the fp32 kernels      */
-/* Test hook of the tensor-core forward: one hand-off between its warps is withheld and the bounded waits give up after
- * a few polls, so the kernel must end through its give-up path (status word set, TMEM released, outputs undefined).
+/* Test hook of the tensor-core forward and backward: one hand-off between the kernel's warps is withheld and the bounded
+ * waits give up after a few polls, so the kernel must end through its give-up path (status word set, products in flight
+ * drained, TMEM released, outputs undefined).
  * It exists so that this path can be exercised without hanging or faulting a GPU; never set it otherwise. */
 #define MBEMA_FLAG_TEST_WITHHOLD_ARRIVE (1 << 30)
 
