@@ -595,6 +595,10 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                     }
                 }
             }
+            // the gate accumulators have been read: the next gate product may overwrite the stage while pass 2 runs
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->acc_empty[sc]);
             const float s = sp[0] + sp[1];
             const float p = row_ok ? __expf(s - lse) : 0.f;
             const float dsr = p * ((dpp[0] + dpp[1]) - drow);     // d loss / d score
@@ -651,10 +655,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             fence_proxy_async_smem();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&bars->z_full);
-                mbar_arrive(&bars->acc_empty[sc]);
-            }
+            if (lane == 0) mbar_arrive(&bars->z_full);
             if (ROWS) de_row_prev = de_row_cur;
         }
         if (n_slots > 0 && alive && mbar_wait(&bars->z_done, (uint32_t)((n_slots - 1) & 1), abort_flag, 7, &bars->spin_limit)) {
