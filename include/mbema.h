@@ -54,6 +54,11 @@ extern "C" {
                                    /* mathbrain/flash_ema_attention.py:76-79                               */
 #define MBEMA_FLAG_CBASE_EXTRA_DECAY 4 /* M_0 = rho * c_base (mathbrain/triton_flash_ema.py:48-50,185)     */
 #define MBEMA_FLAG_FP32_BACKWARD 8     /* MBEMA_MODE_TC_BF16 only: run the backward with the fp32 kernels      */
+#define MBEMA_FLAG_INDEX_READY 16      /* mbema_tile_states only: `workspace` still holds the token order that       */
+                                       /* mbema_query_scan (or an earlier mbema_tile_states) left there for the SAME  */
+                                       /* x, B and T: the sort is skipped, only the links to the listed keys are      */
+                                       /* rebuilt (the model calls the scan and the snapshots on the same chunk,      */
+                                       /* mathbrain/model.py:157 and :180)                                            */
 /* Test hook of the tensor-core forward and backward: one hand-off between the kernel's warps is withheld and the bounded
  * waits give up after a few polls, so the kernel must end through its give-up path (status word set, products in flight
  * drained, TMEM released, outputs undefined).

@@ -9,7 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libmbema.so")
 
 F32, BF16 = 0, 1
-FLAG_SILU, FLAG_LISTED_ONLY, FLAG_CBASE_EXTRA_DECAY, FLAG_FP32_BACKWARD = 1, 2, 4, 8
+FLAG_SILU, FLAG_LISTED_ONLY, FLAG_CBASE_EXTRA_DECAY, FLAG_FP32_BACKWARD, FLAG_INDEX_READY = 1, 2, 4, 8, 16
 FLAG_TEST_WITHHOLD_ARRIVE = 1 << 30
 MODE_FP32, MODE_TC_BF16 = 0, 1
 TILE_T = 128

@@ -142,6 +142,36 @@ k_sort_link(const int64_t* __restrict__ x, const int64_t* __restrict__ keys, Ind
 }
 
 // ----------------------------------------------------------------------------------------------
+// The workspace already holds the (token, t) order and the chain heads of the same x (left there by an earlier call):
+// only the links from listed keys to chain heads are rebuilt, for a new key list.  One CTA per sample.
+// ----------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_relink(const int64_t* __restrict__ keys, IndexWs w, int T, int K) {
+    __shared__ int cnt_sh;
+    const int b = blockIdx.x, tid = threadIdx.x;
+    int32_t* seed = w.seed + (size_t)b * T;
+    const int32_t* s_tok = w.s_tok + (size_t)b * T;
+    if (tid == 0) cnt_sh = 0;
+    for (int i = tid; i < T; i += blockDim.x) seed[i] = NO_SEED;
+    __syncthreads();
+    int nvalid = 0;
+    for (int i = tid; i < K; i += blockDim.x) {
+        const long long kv = keys[(size_t)b * K + i];
+        if (kv < 0) continue;
+        nvalid++;
+        const int key = (int)(kv & 0x7fffffff);
+        int l = 0, r = T;            // lower bound: the first entry of the key's chain, if the token occurs
+        while (l < r) {
+            const int m = (l + r) >> 1;
+            if (s_tok[m] < key) l = m + 1; else r = m;
+        }
+        if (l < T && s_tok[l] == key) atomicMin(&seed[l], i);      // first listed entry wins
+    }
+    atomicAdd(&cnt_sh, nvalid);
+    __syncthreads();
+    if (tid == 0) w.n_valid[b] = cnt_sh;
+}
+
+// ----------------------------------------------------------------------------------------------
 // one warp per chain; lanes hold channels lane, lane+32, lane+64, lane+96
 // ----------------------------------------------------------------------------------------------
 static constexpr int CHAIN_WARPS = 8;
@@ -478,7 +508,12 @@ extern "C" int mbema_tile_states(const int64_t* x, const int64_t* unique, const 
     cudaStream_t st = (cudaStream_t)stream;
     IndexWs w = carve_index_ws(workspace, B, T);
     const int extra = (flags & MBEMA_FLAG_CBASE_EXTRA_DECAY) ? 1 : 0;
-    rc = launch_sort_link(x, unique, w, B, T, K, st);
+    if (flags & MBEMA_FLAG_INDEX_READY) {     // the sort of this x is in the workspace already: new key links only
+        k_relink<<<(unsigned)B, 256, 0, st>>>(unique, w, (int)T, (int)K);
+        rc = check_launch();
+    } else {
+        rc = launch_sort_link(x, unique, w, B, T, K, st);
+    }
     if (rc) return rc;
     dim3 g1((unsigned)((T + CHAIN_WARPS - 1) / CHAIN_WARPS + COOP_BLOCKS), (unsigned)B);
     // a chain without a listed key keeps zero state in tok_state only if it is unlisted: such tokens own no slot,

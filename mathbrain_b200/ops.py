@@ -228,6 +228,17 @@ def clear_status(device=None):
             ws[:4].zero_()
 
 
+# The index workspace (token order, chain heads) of the last chunk that went through the scan or the snapshots, kept so
+# that the second of the two calls the model makes on a chunk does not sort it again.  The key names the tensor's storage,
+# its version counter (in-place writes bump it), its shape and the stream the workspace was filled on; the cache holds a
+# reference to the tensor, so no other tensor can sit at that address while the entry is alive.
+_index_cache = {"key": None, "ws": None, "x": None}     # "x" keeps the tensor alive: its address cannot be handed to another one
+
+
+def _index_key(x):
+    return (x.data_ptr(), x._version, tuple(x.shape), x.device.index, torch.cuda.current_stream(x.device).cuda_stream)
+
+
 # ---------------------------------------------------------------------------------------------
 # query-side scan
 # ---------------------------------------------------------------------------------------------
@@ -264,6 +275,8 @@ def compute_query_ema_history(x, rhos, vocab_size, c_init=None, c_init_keys=None
                               B, L, N, K, flags, _ptr(ws), ws.numel(), _stream())
     telemetry.end("mbema_query_scan", _ev)
     _lib.check(rc, "mbema_query_scan")
+    # the token order of this chunk stays in `ws`: precompute_boundaries on the same x (mathbrain/model.py:157, :180) reuses it
+    _index_cache["key"], _index_cache["ws"], _index_cache["x"] = _index_key(x), ws, x
     return C_seq
 
 
@@ -311,8 +324,13 @@ def precompute_boundaries(x, unique_tensor, rhos, Br, c_init=None, doc_ids=None,
     tile_state = tile_buf[: n_el * 4].view(torch.float32).view(B, nT, K, N)
     tok_state = torch.empty(B, L, N, dtype=torch.float32, device=x.device)
     kcount = torch.empty(2 * B, dtype=torch.int32, device=x.device)   # counts, then samples by decreasing count
-    ws = _workspace(lib.mbema_tile_states_workspace_bytes(B, L), x.device)
     flags = _lib.FLAG_CBASE_EXTRA_DECAY if _OPTIONS["cbase_extra_decay"] else 0
+    if _index_cache["key"] == _index_key(x) and _index_cache["ws"] is not None:
+        ws = _index_cache["ws"]               # the sort of this very x, left by compute_query_ema_history
+        flags |= _lib.FLAG_INDEX_READY
+    else:
+        ws = _workspace(lib.mbema_tile_states_workspace_bytes(B, L), x.device)
+        _index_cache["key"], _index_cache["ws"], _index_cache["x"] = _index_key(x), ws, x
     _ev = telemetry.begin("mbema_tile_states")
     rc = lib.mbema_tile_states(_ptr(x), _ptr(unique), _ptr(rhos), _ptr(c_init), _ptr(tile_state), _ptr(tok_state),
                                _ptr(kcount), B, L, N, K, flags, _ptr(ws), ws.numel(), _stream())

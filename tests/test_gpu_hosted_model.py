@@ -103,12 +103,17 @@ def test_reference_model_hosted_on_native_operators(vocab, T, B, n_pad, mode, to
 
 @needs_ref
 def test_default_mode_takes_the_tensor_core_kernels():
+    import subprocess
     import mathbrain_b200 as mb
-    assert mb.get_options()["mode"] == "auto"
-    assert mb.ops._flash_mode(8, 64, 500) == mb._lib.MODE_TC_BF16
-    assert mb.ops._flash_mode(2, 64, 12) in (mb._lib.MODE_TC_BF16, mb._lib.MODE_FP32)
-    assert mb.ops._flash_mode(3, 64, 500) == mb._lib.MODE_FP32          # odd head count: fp32 kernels, no error
-    assert mb.ops._flash_mode(8, 16, 500) == mb._lib.MODE_FP32
+    # the default of a fresh process (other test modules set the option for their own cases)
+    out = subprocess.run([sys.executable, "-c", "import mathbrain_b200 as m; print(m.get_options()['mode'])"],
+                         capture_output=True, text=True, cwd=os.path.dirname(os.path.dirname(REF)))
+    assert out.stdout.strip() == "auto", out.stderr[-300:]
+    with mb.options(mode="auto"):
+        assert mb.ops._flash_mode(8, 64, 500) == mb._lib.MODE_TC_BF16
+        assert mb.ops._flash_mode(2, 64, 12) in (mb._lib.MODE_TC_BF16, mb._lib.MODE_FP32)
+        assert mb.ops._flash_mode(3, 64, 500) == mb._lib.MODE_FP32          # odd head count: fp32 kernels, no error
+        assert mb.ops._flash_mode(8, 16, 500) == mb._lib.MODE_FP32
 
 
 @needs_ref

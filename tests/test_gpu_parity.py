@@ -404,3 +404,29 @@ def test_scan_long_chains(mb, N, with_docs):
     ref0 = orc.query_scan(x, rhos, V, doc_ids=doc, dtype=torch.float64)
     C0 = mb.compute_query_ema_history(cu(x), cu(rhos), V, doc_ids=cu(doc))
     assert rel_err(C0.cpu(), ref0) < TOL_STATE
+
+
+def test_snapshots_reuse_the_scan_index(mb):
+    """precompute_boundaries right after compute_query_ema_history on the same chunk reuses the token order the scan left
+    in its workspace (only the key links are rebuilt, for a different key list): same snapshots as a call of its own; a
+    chunk modified in place, or another chunk, is sorted afresh."""
+    from mathbrain_b200 import synth
+    b = synth.make_chunk_batch(77, B=3, T=300, N=16, vocab=200, max_prefix=200, min_fill=100, min_hl=2.0, max_hl=200.0)
+    x, rhos, c_base = cu(b["x"]), cu(b["rhos"]), cu(b["c_base"])
+    unique = b["unique_slots"].clone()
+    unique[~b["pad_mask"]] = -1
+    unique = cu(unique)
+    mb.ops._index_cache.update(key=None, ws=None, x=None)
+    fresh = mb.precompute_boundaries(x, unique, rhos, 64, c_init=c_base)              # sorts by itself
+    mb.compute_query_ema_history(x, rhos, b["vocab"], c_base, cu(b["unique_slots"]))   # 0-padded keys: another list
+    assert mb.ops._index_cache["key"] == mb.ops._index_key(x)
+    reused = mb.precompute_boundaries(x, unique, rhos, 64, c_init=c_base)             # key links only
+    assert torch.equal(fresh.tile_state, reused.tile_state) and torch.equal(fresh.tok_state, reused.tok_state)
+    assert torch.equal(fresh.kcount, reused.kcount)
+    x.add_(1).remainder_(b["vocab"])                                                  # in place: the cached order is stale
+    assert mb.ops._index_cache["key"] != mb.ops._index_key(x)
+    again = mb.precompute_boundaries(x, unique, rhos, 64, c_init=c_base)
+    ref = orc.tile_start_states(x.cpu(), unique.cpu(), b["rhos"], 128, c_base=b["c_base"], dtype=torch.float64)
+    nT = ref.shape[1]
+    got = again.tile_state.reshape(-1)[: 3 * nT * unique.shape[1] * 16].view(3, nT, unique.shape[1], 16)
+    assert rel_err(got.cpu(), ref) < TOL_STATE
