@@ -36,6 +36,10 @@ class DecodeState:
         return self.t_dev
 
     def advance(self):
+        with torch.cuda.device(self.state.device):
+            self._advance()
+
+    def _advance(self):
         _lib.check(_lib.load().mbema_decode_advance(_ptr(self.t_dev), _stream()), "mbema_decode_advance")
 
     def capture_step(self, qs, E_ks, E_vs, W_pes, tok, use_silu=True, mode=None):
@@ -69,6 +73,14 @@ class DecodeState:
         return graph, outs, C_q
 
     def attend(self, q, E_k, E_v, W_pe, t_now, V_total=None, use_silu=True, listed_only=False, mode=None):
+        """O [B, H, 64] float32; see _attend.  Runs with the state's device current and refuses operands elsewhere."""
+        for t in (q, E_k, E_v, W_pe):
+            if t.device != self.state.device:
+                raise _lib.MbemaError("decode: operand on %s, state on %s" % (t.device, self.state.device))
+        with torch.cuda.device(self.state.device):
+            return self._attend(q, E_k, E_v, W_pe, t_now, V_total, use_silu, listed_only, mode)
+
+    def _attend(self, q, E_k, E_v, W_pe, t_now, V_total=None, use_silu=True, listed_only=False, mode=None):
         """O [B, H, 64] float32.  q [B, H, 64]; E_k, E_v [V, H*64] projected slot embeddings; W_pe [N, H*64].
 
         mode "fp32" (exact kernel) or "tc_bf16" (tensor cores; N = 64, H even); default: the package option `mode`,
@@ -111,6 +123,13 @@ class DecodeState:
         return O
 
     def update(self, tok, t_now):
+        """C_q [B, N]; see _update.  Runs with the state's device current and refuses a token tensor elsewhere."""
+        if tok.device != self.state.device:
+            raise _lib.MbemaError("decode: tokens on %s, state on %s" % (tok.device, self.state.device))
+        with torch.cuda.device(self.state.device):
+            return self._update(tok, t_now)
+
+    def _update(self, tok, t_now):
         """Query-side state C_q [B, N] of the new tokens (before their update), then the slot update of step t_now."""
         _require_cuda(tok)
         lib = _lib.load()

@@ -60,6 +60,12 @@ class ChunkFeeder:
         """Wire format of the next chunk of every document: dict(unique_slots [B, K] int64 (0-padded, as the collate
         function pads), pad_mask [B, K] bool, c_base [B, K, N] float32, K_max).  x [B, T] int64, fill [B] valid lengths."""
         _require_cuda(x, fill)
+        if x.device != self.state.device:
+            raise _lib.MbemaError("ChunkFeeder: chunk on %s, state on %s" % (x.device, self.state.device))
+        with torch.cuda.device(self.state.device):
+            return self._next_batch(x, fill)
+
+    def _next_batch(self, x, fill):
         B, T = x.shape
         dev = x.device
         fill = fill.to(torch.long)
