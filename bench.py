@@ -757,6 +757,93 @@ def next_case(args):
     print(json.dumps(out))
 
 
+def model_case(args):
+    """The reference's own SlotTransformerLM (46M configuration, unmodified, from baseline/_ref) through one training step
+    (forward, masked cross-entropy, backward; bf16 autocast; B=56 chunks of T=512 of the bench's batch), once on the
+    reference's Triton operators and once hosted on this library's operators (install_as_mathbrain), same weights and
+    inputs.  Prints device time per step for both and the relative difference of the two losses; no benchmark line."""
+    import importlib
+    import mathbrain_b200 as mb
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isfile(os.path.join(ref_dir, "mathbrain", "model.py")):
+        print(json.dumps({"profile_case": "model", "unavailable": "baseline/_ref/mathbrain is absent"}))
+        return
+    c = CFG
+    dev = torch.device("cuda", 0)
+    host = make_rank_batch(0, 1)
+    B = int(os.environ.get("MBEMA_MODEL_B", c["B"]))
+    x = host["x"][:B].to(dev)
+    unique_slots, pad_mask, c_base = host["unique_slots"][:B].to(dev), host["pad_mask"][:B].to(dev), host["c_base"][:B].to(dev)
+    fill = host["fill"][:B].to(dev)
+    g = torch.Generator().manual_seed(9)
+    y = torch.randint(0, c["V"], (B, c["T"]), generator=g).to(dev)
+    y[torch.arange(c["T"], device=dev).unsqueeze(0) >= fill.unsqueeze(1)] = -1
+
+    def load(hosted):
+        for k in [k for k in sys.modules if k == "mathbrain" or k.startswith("mathbrain.")]:
+            del sys.modules[k]
+        if hosted:
+            mb.install_as_mathbrain()
+        sys.path.insert(0, ref_dir)
+        try:
+            return importlib.import_module("mathbrain.model")
+        finally:
+            sys.path.remove(ref_dir)
+
+    def step_time(model, n):
+        def step():
+            model.zero_grad(set_to_none=True)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                logits = model(x, unique_slots=unique_slots, c_base=c_base, pad_mask=pad_mask)
+                loss = torch.nn.functional.cross_entropy(logits.view(-1, logits.size(-1)), y.view(-1), ignore_index=-1)
+            loss.backward()
+            return loss.detach()
+        step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            loss = step()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n, float(loss)
+
+    out = {"profile_case": "model", "B": B, "T": c["T"], "config": "SlotTransformerLM(vocab 50257, d 512, 6 layers, 8 heads, N 64, half-lives 1024-4096)"}
+    cfg = dict(vocab_size=c["V"], d_model=c["D"], n_layers=c["L"], n_heads=c["H"], N=c["N"], dropout=0.0,
+               min_hl=c["min_hl"], max_hl=c["max_hl"])
+    state = None
+    for name, hosted in (("reference_triton", False), ("hosted_native", True)):
+        try:
+            mod = load(hosted)
+            torch.manual_seed(0)
+            model = mod.SlotTransformerLM(**cfg).to(dev)
+            if state is None:
+                # the model's default initialisation (embeddings N(0, 1)) gives pre-activations in the hundreds on states of
+                # an 8192-token prefix and NaN losses from the reference's own kernels: embeddings and gate weights are scaled
+                # to the magnitudes of the other benchmark cases, identically for both runs
+                state = {k: v.clone() for k, v in model.state_dict().items()}
+                for k in state:
+                    if k == "embed.weight" or k == "lm_head.weight":
+                        state[k] = state[k] * 0.02
+                    elif k.endswith("pe_proj.weight"):
+                        state[k] = state[k] * 0.16
+            model.load_state_dict(state)
+            if hosted:
+                # the reference's Triton kernels take the softmax over the listed slots and decay c_base once more:
+                # the same conventions here, so that the two losses are comparable
+                with mb.options(mode="auto", inactive_mass="listed_only", cbase_extra_decay=True):
+                    ms, loss = step_time(model, args.steps)
+            else:
+                ms, loss = step_time(model, max(1, min(args.steps, 2)))
+            out[name] = {"ms_per_step": ms, "tokens_per_s": B * c["T"] / ms * 1000.0, "loss": loss}
+            del model
+            torch.cuda.empty_cache()
+        except Exception as e:                                     # noqa: BLE001
+            out[name] = {"unavailable": repr(e)[:300]}
+    out["status"] = mb.device_status()
+    print(json.dumps(out))
+
+
 def timed(fn, steps, warmup, barrier):
     for _ in range(warmup):
         fn()
@@ -852,7 +939,7 @@ def main():
     ap.add_argument("--no-documents", action="store_true",
                     help="skip the measurement on the 8-GPU configuration's document data (extra key `documents`)")
     ap.add_argument("--no-decode", action="store_true", help="skip the streaming-decode measurement (extra key `decode`)")
-    ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd", "long", "aux", "decode", "triton", "next"],
+    ap.add_argument("--profile-case", default=None, choices=["fwd", "bwd", "long", "aux", "decode", "triton", "next", "model"],
                     help="run a small one-layer attention workload (for ncu captures) instead of the benchmark")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
@@ -877,6 +964,9 @@ def main():
         return
     if args.profile_case == "next":
         next_case(args)
+        return
+    if args.profile_case == "model":
+        model_case(args)
         return
     if args.profile_case:
         profile_case(args)
