@@ -790,12 +790,16 @@ def model_case(args):
         finally:
             sys.path.remove(ref_dir)
 
-    def step_time(model, n):
+    def step_time(model, n, rows=False):
         def step():
             model.zero_grad(set_to_none=True)
             with torch.autocast("cuda", dtype=torch.bfloat16):
-                logits = model(x, unique_slots=unique_slots, c_base=c_base, pad_mask=pad_mask)
-                loss = torch.nn.functional.cross_entropy(logits.view(-1, logits.size(-1)), y.view(-1), ignore_index=-1)
+                if rows:      # slot rows projected once per distinct token, lm_head + cross-entropy over the valid rows in chunks
+                    from mathbrain_b200.hosted import train_step_loss
+                    loss = train_step_loss(model, x, y, unique_slots, c_base, pad_mask, ignore_index=-1)
+                else:
+                    logits = model(x, unique_slots=unique_slots, c_base=c_base, pad_mask=pad_mask)
+                    loss = torch.nn.functional.cross_entropy(logits.view(-1, logits.size(-1)), y.view(-1), ignore_index=-1)
             loss.backward()
             return loss.detach()
         step()
@@ -833,6 +837,8 @@ def model_case(args):
                 # the same conventions here, so that the two losses are comparable
                 with mb.options(mode="auto", inactive_mass="listed_only", cbase_extra_decay=True):
                     ms, loss = step_time(model, args.steps)
+                    ms2, loss2 = step_time(model, args.steps, rows=True)
+                out["hosted_native_shared_rows_chunked_loss"] = {"ms_per_step": ms2, "tokens_per_s": B * c["T"] / ms2 * 1000.0, "loss": loss2}
             else:
                 ms, loss = step_time(model, max(1, min(args.steps, 2)))
             out[name] = {"ms_per_step": ms, "tokens_per_s": B * c["T"] / ms * 1000.0, "loss": loss}

@@ -164,3 +164,39 @@ def test_operators_against_the_reference_triton_kernels(mode, tol):
     scan = mb.compute_query_ema_history(x, rhos, V, c_base, unique)
     assert rel_err(scan.cpu(), ref_scan.cpu()) < 1e-5
     assert mb.device_status() == 0
+
+
+@needs_ref
+@pytest.mark.parametrize("mode,tol,autocast", [("fp32", 2e-4, False), ("auto", 2e-2, True)])
+def test_train_step_with_shared_rows_and_chunked_loss(mode, tol, autocast):
+    """hosted.train_step_loss (slot rows projected once per distinct token, lm_head + cross-entropy over valid rows in
+    chunks) against the reference model's own forward + F.cross_entropy on the same operators: same loss, same gradients."""
+    import mathbrain_b200 as mb
+    from mathbrain_b200.hosted import train_step_loss
+    vocab, T, B = 211, 96, 3
+    cfg = dict(vocab_size=vocab, d_model=128, n_layers=2, n_heads=2, N=64, dropout=0.0, min_hl=2.0, max_hl=64.0)
+    x, y, unique, mask = _batch(5, B, T, vocab, 2)
+    y[0, 60:] = -1                                            # padded positions
+    mod = _import_model(hosted=True)
+    torch.manual_seed(1)
+    model = mod.SlotTransformerLM(**cfg).cuda()
+    g = torch.Generator().manual_seed(2)
+    c_base = (torch.rand(B, unique.shape[1], 64, generator=g) * mask.unsqueeze(-1)).cuda()
+    xd, yd, ud, md = x.cuda(), y.cuda(), unique.cuda(), mask.cuda()
+    with mb.options(mode=mode, inactive_mass="full_V", cbase_extra_decay=False):
+        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=autocast):
+            logits = model(xd, unique_slots=ud, c_base=c_base, pad_mask=md)
+            ref = torch.nn.functional.cross_entropy(logits.float().view(-1, vocab), yd.view(-1), ignore_index=-1)
+        model.zero_grad(set_to_none=True)
+        ref.backward()
+        ref_grads = {n: p.grad.detach().float().clone() for n, p in model.named_parameters()}
+        model.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=autocast):
+            loss = train_step_loss(model, xd, yd, ud, c_base, md, ignore_index=-1)
+        loss.backward()
+    assert abs(float(loss.detach()) - float(ref.detach())) < tol * abs(float(ref.detach()))
+    for n, p in model.named_parameters():
+        if float(ref_grads[n].abs().max()) == 0.0:
+            continue
+        assert rel_err(p.grad.float().cpu(), ref_grads[n].cpu()) < tol, (n, rel_err(p.grad.float().cpu(), ref_grads[n].cpu()))
+    assert mb.device_status() == 0
