@@ -421,10 +421,11 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
             float sp0 = 0.f, sp1 = 0.f;
 #pragma unroll
             for (int c = 0; c < HD / 16; ++c) {      // 16 accumulator columns (8 pairs) per TMEM load, the next load in flight
-                tmem_wait_ld();
-                if (c + 1 < HD / 16) tmem_ld_32x32b_x16(t_acc + (c + 1) * 16, pre[(c + 1) & 1]);
+                // the E-row broadcasts are issued before the wait (a load after it could not be moved above it by the compiler)
                 const uint4 ekA = *reinterpret_cast<const uint4*>(ek2 + c * 8), ekB = *reinterpret_cast<const uint4*>(ek2 + c * 8 + 4);
                 const uint4 evA = *reinterpret_cast<const uint4*>(ev2 + c * 8), evB = *reinterpret_cast<const uint4*>(ev2 + c * 8 + 4);
+                tmem_wait_ld();
+                if (c + 1 < HD / 16) tmem_ld_32x32b_x16(t_acc + (c + 1) * 16, pre[(c + 1) & 1]);
                 const uint32_t ekw[8] = {ekA.x, ekA.y, ekA.z, ekA.w, ekB.x, ekB.y, ekB.z, ekB.w};
                 const uint32_t evw[8] = {evA.x, evA.y, evA.z, evA.w, evB.x, evB.y, evB.z, evB.w};
                 uint32_t sa0 = 0u, sa1 = 0u;

@@ -561,12 +561,15 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             for (int c = 0; c < 4; ++c) {
                 float pre[16];
                 tmem_ld_32x32b_x16(t_acc + c * 16, pre);
+                // the E-row broadcasts are issued before the wait (a load after it could not be moved above it by the compiler)
+                const uint4 ekq[2] = {*reinterpret_cast<const uint4*>(ek2a + c * 8), *reinterpret_cast<const uint4*>(ek2a + c * 8 + 4)};
+                const uint4 evq[2] = {*reinterpret_cast<const uint4*>(ev2a + c * 8), *reinterpret_cast<const uint4*>(ev2a + c * 8 + 4)};
                 tmem_wait_ld();
 #pragma unroll
                 for (int j8 = 0; j8 < 2; ++j8) {
                     const int w0 = c * 8 + j8 * 4;
-                    const uint4 ekp = *reinterpret_cast<const uint4*>(ek2a + w0);
-                    const uint4 evp = *reinterpret_cast<const uint4*>(ev2a + w0);
+                    const uint4 ekp = ekq[j8];
+                    const uint4 evp = evq[j8];
                     const uint32_t ekw[4] = {ekp.x, ekp.y, ekp.z, ekp.w}, evw[4] = {evp.x, evp.y, evp.z, evp.w};
 #pragma unroll
                     for (int pr = 0; pr < 4; ++pr) {
