@@ -15,8 +15,9 @@
 //     accumulator columns, reads them with tcgen05.ld and fuses SiLU, K = E_k*gate, V = E_v*gate, the score, the
 //     online softmax and the P.V update, all thread-local.  One tanh per gate element is what the SM's
 //     special-function pipe allows (16 per clock per SM, packed or not); the gate is formed in fp32 and packed to
-//     fp16 pairs, the products with E_k, E_v and q are packed fp16 operations, score terms are summed 16 at a time in
-//     fp16 and then in fp32, and the P.V terms go into the fp32 output row with the mixed-precision FMA.  The P.V
+//     fp16 pairs, the products with E_k, E_v and q are packed fp16 operations, and both the score terms and the P.V
+//     terms are summed in fp32 with the mixed-precision FMA (one scheduler cycle per warp instruction, where a packed
+//     16-bit FMA takes two: summing the score in packed fp16 first saved nothing and cost the unpacking).  The P.V
 //     update of slot i - 1 shares the pass over the columns with the gate of slot i, and the softmax bookkeeping of
 //     slot i - 1 runs under the TMEM load of slot i.
 // A tiles and TMEM accumulators are four deep (all 512 TMEM columns) for N = 64.  Registers are rebalanced with
@@ -388,7 +389,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
         //   (3) walks its 64 columns once, doing per pair of columns
         //         O += p(i-1) * (E_v(i-1) * gate(i-1))                                    P.V, one slot behind
         //         gate(i) = SiLU(pre) = h + h * tanh(h), h = pre (W_pe carries the 1/2)    overwrites gate(i-1)
-        //         score(i) += gate(i) * (q * E_k(i))                                       16 columns in fp16, then fp32
+        //         score(i) += gate(i) * (q * E_k(i))                                       summed in fp32 (mixed-precision FMA)
         // The reference maximum only moves when a score exceeds it by more than LAZY_MAX (the probabilities stay below
         // e^LAZY_MAX, well inside fp16), so rescaling the output row is rare.
         float s_prev = 0.f;                     // score(i-1)
@@ -428,22 +429,32 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_fwd_tc(FlashArgs a, int* s
                 if (c + 1 < HD / 16) tmem_ld_32x32b_x16(t_acc + (c + 1) * 16, pre[(c + 1) & 1]);
                 const uint32_t ekw[8] = {ekA.x, ekA.y, ekA.z, ekA.w, ekB.x, ekB.y, ekB.z, ekB.w};
                 const uint32_t evw[8] = {evA.x, evA.y, evA.z, evA.w, evB.x, evB.y, evB.z, evB.w};
-                uint32_t sa0 = 0u, sa1 = 0u;
+                // software pipeline over the pairs: the two tanh of pair j + 1 are issued between the FMA-pipe work of pair j
+                float tA, tB;
+                asm volatile("tanh.approx.f32 %0, %1;" : "=f"(tA) : "f"(pre[c & 1][0]));
+                asm volatile("tanh.approx.f32 %0, %1;" : "=f"(tB) : "f"(pre[c & 1][1]));
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const int w = c * 8 + j;
-                    fma_f32_f16x2(o[2 * w], o[2 * w + 1], mul_f16x2(g_old[w], evw[j]), p2);
                     const float h0 = pre[c & 1][2 * j], h1 = pre[c & 1][2 * j + 1];
-                    const float g0 = SILU ? fmaf(h0, tanh_approx(h0), h0) : h0;
-                    const float g1 = SILU ? fmaf(h1, tanh_approx(h1), h1) : h1;
+                    const float t0v = tA, t1v = tB;
+                    if (j + 1 < 8) asm volatile("tanh.approx.f32 %0, %1;" : "=f"(tA) : "f"(pre[c & 1][2 * j + 2]));
+                    {
+                        const uint32_t gv = mul_f16x2(g_old[w], evw[j]);
+                        asm volatile("{\n\t.reg .b16 xl, xh, yl, yh;\n\tmov.b32 {xl, xh}, %2;\n\tmov.b32 {yl, yh}, %3;\n\t"
+                                     "fma.rn.f32.f16 %0, xl, yl, %0;\n\tfma.rn.f32.f16 %1, xh, yh, %1;\n\t}"
+                                     : "+f"(o[2 * w]), "+f"(o[2 * w + 1]) : "r"(gv), "r"(p2));
+                    }
+                    if (j + 1 < 8) asm volatile("tanh.approx.f32 %0, %1;" : "=f"(tB) : "f"(pre[c & 1][2 * j + 3]));
+                    const float g0 = SILU ? fmaf(h0, t0v, h0) : h0;
+                    const float g1 = SILU ? fmaf(h1, t1v, h1) : h1;
                     const uint32_t gg = pack_f16x2(g0, g1);
                     g_old[w] = gg;
                     const uint32_t qe = mul_f16x2(q2[w], ekw[j]);
-                    if (j & 1) sa1 = fma_f16x2(gg, qe, sa1); else sa0 = fma_f16x2(gg, qe, sa0);
+                    asm volatile("{\n\t.reg .b16 xl, xh, yl, yh;\n\tmov.b32 {xl, xh}, %2;\n\tmov.b32 {yl, yh}, %3;\n\t"
+                                 "fma.rn.f32.f16 %0, xl, yl, %0;\n\tfma.rn.f32.f16 %1, xh, yh, %1;\n\t}"
+                                 : "+f"(sp0), "+f"(sp1) : "r"(gg), "r"(qe));
                 }
-                const float2 f0 = unpack_f16x2(sa0), f1 = unpack_f16x2(sa1);
-                sp0 += f0.x + f0.y;
-                sp1 += f1.x + f1.y;
             }
             // the stage's accumulators are consumed (its E rows live in their own, deeper ring)
             tc_fence_before_sync();
