@@ -289,12 +289,15 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
                 tmem_ld_32x32b_x16(t_acc, pre[0]);
 #pragma unroll
                 for (int c = 0; c < HD / 16; ++c) {              // 16 accumulator columns per load, the next load in flight
+                    // the E_k chunks are loaded before the wait (a load after it could not be moved above it by the compiler)
+                    const uint4 eq[2] = {*reinterpret_cast<const uint4*>(ekrow + (((c * 2) ^ (row & 7)) << 4)),
+                                         *reinterpret_cast<const uint4*>(ekrow + (((c * 2 + 1) ^ (row & 7)) << 4))};
                     tmem_wait_ld();
                     if (c + 1 < HD / 16) tmem_ld_32x32b_x16(t_acc + (c + 1) * 16, pre[(c + 1) & 1]);
 #pragma unroll
                     for (int j8 = 0; j8 < 2; ++j8) {
                         const int ch = c * 2 + j8;               // chunk of 8 columns
-                        const uint4 e = *reinterpret_cast<const uint4*>(ekrow + ((ch ^ (row & 7)) << 4));
+                        const uint4 e = eq[j8];
                         const uint32_t ew[4] = {e.x, e.y, e.z, e.w};
 #pragma unroll
                         for (int pr = 0; pr < 4; ++pr) {
@@ -333,15 +336,21 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
                 if (lane == 0) wm[EPI_WARPS + warp] = ps;
             }
             // ---- (p * gate * E_v)[k, d] in bf16, over the E_v rows themselves
+            //      (four chunks' loads first: a store is a compiler barrier for the loads behind it)
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
-                unsigned char* cp = evrow + ((ch ^ (row & 7)) << 4);
-                const uint4 e = *reinterpret_cast<const uint4*>(cp);
-                const uint32_t ew[4] = {e.x, e.y, e.z, e.w};
-                uint32_t w[4];
+            for (int g4 = 0; g4 < 2; ++g4) {
+                uint4 ev4[4];
 #pragma unroll
-                for (int pr = 0; pr < 4; ++pr) w[pr] = ok ? mul_bf16x2(mul_bf16x2(g2[ch * 4 + pr], p2), ew[pr]) : 0u;   // rows without a slot hold stale bytes
-                st_shared_v4(cp, w[0], w[1], w[2], w[3]);
+                for (int c4 = 0; c4 < 4; ++c4) ev4[c4] = *reinterpret_cast<const uint4*>(evrow + (((g4 * 4 + c4) ^ (row & 7)) << 4));
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4) {
+                    const int ch = g4 * 4 + c4;
+                    const uint32_t ew[4] = {ev4[c4].x, ev4[c4].y, ev4[c4].z, ev4[c4].w};
+                    uint32_t w[4];
+#pragma unroll
+                    for (int pr = 0; pr < 4; ++pr) w[pr] = ok ? mul_bf16x2(mul_bf16x2(g2[ch * 4 + pr], p2), ew[pr]) : 0u;   // rows without a slot hold stale bytes
+                    st_shared_v4(evrow + ((ch ^ (row & 7)) << 4), w[0], w[1], w[2], w[3]);
+                }
             }
             fence_proxy_async_smem();
             tc_fence_before_sync();
