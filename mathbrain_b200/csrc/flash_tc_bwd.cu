@@ -539,7 +539,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
             for (int c = 0; c < 4; ++c) tmem_st_32x32b_x16(t_dq + c * 16, z16);
             tmem_wait_st();
         }
-        unsigned char* zrow = Z_sh + wg * ATOM_BYTES + row * 128;     // + kind * HPC * ATOM_BYTES + swizzled chunk
+        const uint32_t zr = smem_u32(Z_sh + wg * ATOM_BYTES + row * 128) | (uint32_t)((row & 7) << 4);   // shared-window address of the Z row, swizzle term folded in; + kind * HPC * ATOM_BYTES
         float* dE_out = (wg == 0 ? a.dEk : a.dEv) + hp * ACC_COLS + row;   // + E row of the slot * D
         size_t de_row_prev = 0;                                          // E row of slot i - 1
         const uint32_t t_de = t_lane + (wg == 0 ? COL_DEK : COL_DEV);
@@ -643,10 +643,11 @@ __global__ void __launch_bounds__(THREADS, 1) k_flash_bwd_tc(FlashArgs a, int* s
                         }
                         ge[pr] = mul_bf16x2(gg, ekw[pr]);                                 // K = g * E_k, for dQ
                     }
-                    const int chunk = ((c * 2 + j8) ^ (row & 7)) << 4;
-                    st_shared_v4(zrow + 0 * HPC * ATOM_BYTES + chunk, zp[0], zp[1], zp[2], zp[3]);
-                    st_shared_v4(zrow + 1 * HPC * ATOM_BYTES + chunk, zk[0], zk[1], zk[2], zk[3]);
-                    st_shared_v4(zrow + 2 * HPC * ATOM_BYTES + chunk, zv[0], zv[1], zv[2], zv[3]);
+                    // swizzled chunk address: the row base has bits 4..6 clear, so base + ((k ^ r) << 4) == (base | r << 4) ^ (k << 4)
+                    const uint32_t za = zr ^ (uint32_t)((c * 2 + j8) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(za), "r"(zp[0]), "r"(zp[1]), "r"(zp[2]), "r"(zp[3]) : "memory");
+                    asm volatile("st.shared.v4.b32 [%0+%5], {%1, %2, %3, %4};" ::"r"(za), "r"(zk[0]), "r"(zk[1]), "r"(zk[2]), "r"(zk[3]), "n"(1 * HPC * ATOM_BYTES) : "memory");
+                    asm volatile("st.shared.v4.b32 [%0+%5], {%1, %2, %3, %4};" ::"r"(za), "r"(zv[0]), "r"(zv[1]), "r"(zv[2]), "r"(zv[3]), "n"(2 * HPC * ATOM_BYTES) : "memory");
                     if (j8 == 0) tmem_wait_ld();
 #pragma unroll
                     for (int pr = 0; pr < 4; ++pr)      // dq += (ds / 8) * K in fp32: bf16 x bf16 products are exact
