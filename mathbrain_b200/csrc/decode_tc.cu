@@ -2,14 +2,18 @@
 // per sequence over the slots seen so far, in ONE walk over the slots, warp-specialised like the training kernels.
 // A CTA owns (sequence, head pair, share of the 128-slot tiles); rows of a tile are SLOTS.
 //   eight producer warps (two threads per slot): cp.async gathers of the tile's E_k / E_v rows into two-stage rings, the
-//       slot's state row from global memory -> decayed fp16 row of the A tile; one lane issues the gate product
-//       (tcgen05.mma against W, accumulators in TMEM, two stages), another the column-sum product below;
-//   eight epilogue warps (a warpgroup per head, a thread per slot and the head's 64 columns): gate = SiLU of the
-//       accumulators, score s[k] = sum_c q g E_k in the thread, tile maximum over the head's 128 threads (warp
-//       shuffles + one named barrier of 128 threads), p = exp(s - m), the bf16 tile (p * gate * E_v)[k, d] written
-//       over the E_v rows it was made from; its sum over the 128 slots is a second tcgen05.mma against a ones operand
-//       (the column-sum trick of the training backward) into one of two TMEM regions, which warpgroup 0 folds into the
-//       CTA's running (max, normaliser, output) one tile later (online softmax in registers);
+//       slot's state row from global memory -> decayed fp16 row of the A tile.  A tile's stages are released piecewise:
+//       the E_k rows, the A tile and the accumulators once the epilogue has finished its first pass over tile i - 2,
+//       the E_v rows only when that tile's column sum has completed, so only the E_v copies wait for the later event;
+//   one issuing warp (one lane): every tcgen05.mma of the CTA, gate products (against W, accumulators in TMEM, two
+//       stages) and column sums, so that no producer thread ever waits for the epilogue's operand tile;
+//   sixteen epilogue warps (a thread per slot and HALF a head, 32 columns): gate = SiLU of the accumulators, partial
+//       score sum_c q g E_k in the thread; both halves post their partial sums in shared memory, the head's eight warps
+//       meet on an mbarrier, and every warp forms the rows' scores and the head's tile maximum from the 128 posted
+//       pairs; p = exp(s - m), the bf16 tile (p * gate * E_v)[k, d] written over the E_v rows it was made from; its
+//       sum over the 128 slots is a second tcgen05.mma against a ones operand (the column-sum trick of the training
+//       backward) into one of two TMEM regions, which warps 0..3 fold into the CTA's running (max, normaliser, output)
+//       one tile later (online softmax in registers);
 //   per CTA      partial (O[128], m[2], l[2]) of its tiles, written to the workspace;
 //   merge kernel per (sequence, head): the partials of all CTAs plus the mass of the never-seen slots -> O.
 // No block barrier inside the tile loop: the roles meet on mbarriers (every wait bounded), so the gathers, the state
@@ -25,17 +29,17 @@ namespace dtc {
 using namespace ptx;
 
 static constexpr int TM = 128, HD = 64, HPC = 2, N = 64, ACC_COLS = HPC * HD, MAXT = 16;
-static constexpr int EPI_WARPS = 8, PROD_WARPS = 8, THREADS = (EPI_WARPS + PROD_WARPS) * 32;
+static constexpr int EPI_WARPS = 16, PROD_WARPS = 8, MMA_WARP = EPI_WARPS + PROD_WARPS, THREADS = (MMA_WARP + 1) * 32;
+static constexpr int HALF = HD / 2;                           // columns of a head per epilogue thread
 static constexpr int ATOM_BYTES = TM * 128;
 static constexpr int STAGE_BYTES = 2 * ATOM_BYTES;            // one embedding stage: 2 heads x 128 rows x 128 B
 static constexpr int PART_FLOATS = ACC_COLS + 4;              // per-CTA partial: O[128], m[2], l[2]
 static constexpr int OFF_B = 0, OFF_A = ATOM_BYTES, OFF_EK = OFF_A + 2 * ATOM_BYTES, OFF_EV = OFF_EK + 2 * STAGE_BYTES,
                      OFF_ONES = OFF_EV + 2 * STAGE_BYTES, OFF_Q = OFF_ONES + 2048, OFF_L2R = OFF_Q + 512,
                      OFF_IDS = OFF_L2R + 256, OFF_DTS = OFF_IDS + MAXT * TM * 4, OFF_WRED = OFF_DTS + MAXT * TM * 4,
-                     OFF_BARS = OFF_WRED + 4 * 2 * EPI_WARPS * 4, SMEM_BYTES = OFF_BARS + 128 + 1024;
+                     OFF_XCH = OFF_WRED + 4 * 16 * 4, OFF_BARS = OFF_XCH + 2 * HPC * 2 * TM * 4, SMEM_BYTES = OFF_BARS + 192 + 1024;
 static constexpr int COL_R = 2 * ACC_COLS;                    // TMEM: two gate accumulators, then two 16-column sum regions
-// setmaxnreg: 8*32*184 (epilogue) + 8*32*72 (producers) equals the launch allocation 512*128
-static_assert(EPI_WARPS * 32 * 184 + PROD_WARPS * 32 * 72 == THREADS * 128, "register split");
+// no setmaxnreg here: 800 threads at 80 registers; neither role needs more
 
 struct Args {
     const void* q; int q_dt;
@@ -72,17 +76,18 @@ __device__ __forceinline__ float tmem_ld_1(uint32_t taddr) {
 
 struct Bars {
     uint64_t a_full[2];          // every producer warp has written its part of the A tile                 (8 arrivals)
-    uint64_t acc_full[2];        // gate product done (1 commit) + every producer warp's E rows have landed (8 arrivals)
+    uint64_t acc_full[2];        // gate product done (1 commit) + every producer warp's E_k rows have landed (8 arrivals)
+    uint64_t ev_full[2];         // every producer warp's E_v rows have landed                              (8 arrivals)
     uint64_t acc_empty[2];       // every epilogue warp has read the stage's accumulators                 (8 arrivals)
     uint64_t v_full[2];          // every epilogue warp has written its rows of the column-sum operand     (8 arrivals)
     uint64_t pv_done[2];         // column-sum product done: the E stages of that tile are free            (1 commit)
-    uint64_t hbar[2];            // per head: its four epilogue warps have published their maxima          (4 arrivals)
-    uint64_t drain;              // the two issuing lanes' products have completed (teardown)              (2 arrivals)
+    uint64_t hbar[2];            // per head: its eight epilogue warps have posted their rows' partial scores (8 arrivals)
+    uint64_t drain;              // the issuing lane's products have completed (teardown)                  (1 arrival)
     uint32_t tmem_base;
     int abort_flag;
     int drain_flag;
 };
-static_assert(sizeof(Bars) <= 128, "barrier block");
+static_assert(sizeof(Bars) <= 192, "barrier block");
 
 template <bool SILU>
 __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
@@ -97,7 +102,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
     float* l2r_sh = reinterpret_cast<float*>(sm + OFF_L2R);
     int* ids_sh = reinterpret_cast<int*>(sm + OFF_IDS);                 // slot of every row of this CTA's tiles, -1 = none
     float* dts_sh = reinterpret_cast<float*>(sm + OFF_DTS);             // steps since that slot's last update
-    float* wred = reinterpret_cast<float*>(sm + OFF_WRED);              // [tile & 3][max | sum of p][epilogue warp]
+    float* wred = reinterpret_cast<float*>(sm + OFF_WRED);              // [tile & 3][16]: tile maximum per head at 0..1, sums of p per (head, warp of its first half) at 4..11
+    float* xch = reinterpret_cast<float*>(sm + OFF_XCH);                // [tile & 1][head][half][128 rows]: partial scores
     Bars* bars = reinterpret_cast<Bars*>(sm + OFF_BARS);
     volatile int* abort_flag = &bars->abort_flag;
 
@@ -115,13 +121,14 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bars->a_full[i], PROD_WARPS);
             mbar_init(&bars->acc_full[i], 1 + PROD_WARPS);
+            mbar_init(&bars->ev_full[i], PROD_WARPS);
             mbar_init(&bars->acc_empty[i], EPI_WARPS);
             mbar_init(&bars->v_full[i], EPI_WARPS);
             mbar_init(&bars->pv_done[i], 1);
         }
-        mbar_init(&bars->hbar[0], 4);
-        mbar_init(&bars->hbar[1], 4);
-        mbar_init(&bars->drain, 2);
+        mbar_init(&bars->hbar[0], 8);
+        mbar_init(&bars->hbar[1], 8);
+        mbar_init(&bars->drain, 1);
         bars->drain_flag = 0;
         bars->abort_flag = *reinterpret_cast<volatile int*>(status);
         fence_barrier_init();
@@ -157,23 +164,46 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
     tc_fence_after_sync();
     const uint32_t tmem_base = bars->tmem_base;
 
-    if (!is_epi) {
-        // ============================================================ producer warps: two threads per slot of the tile
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
-        const int pw = warp - EPI_WARPS, ptid = tid - EPI_WARPS * 32;
-        const int prow = ptid & 127, phalf = ptid >> 7;            // this thread: slot prow of the tile, channels [32 phalf, 32 phalf + 32)
-        const uint32_t idesc = umma_idesc_16(TM, ACC_COLS, 0, 0, 0, 0);      // fp16 state tile, fp16 W
-        const uint32_t idesc2 = umma_idesc_bf16(ACC_COLS, 16, 1, 0);         // column sum: A = tile (MN-major), B = ones
-        const uint64_t db = umma_desc_k_sw128(smem_u32(B_sh)), d1 = umma_desc_k_sw128(smem_u32(ones_sh));
-        auto issue_pv = [&](int j) {        // column sums of tile j, once the epilogue has written the operand
-            if (!mbar_wait(&bars->v_full[j & 1], (uint32_t)((j >> 1) & 1), abort_flag, 5)) return;
-            tc_fence_after_sync();
-            const uint64_t dv = umma_desc_mn_sw128(smem_u32(Ev_st + (j & 1) * STAGE_BYTES), ATOM_BYTES, 1024);
+    if (warp == MMA_WARP) {
+        // ============================================================ issuing warp: one lane issues every tcgen05.mma of the CTA
+        // A warp of its own, so that no producer thread ever waits for the epilogue's operand tile: in order
+        // gate(0), gate(1), sum(0), gate(2), sum(1), ...
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_16(TM, ACC_COLS, 0, 0, 0, 0);      // fp16 state tile, fp16 W
+            const uint32_t idesc2 = umma_idesc_bf16(ACC_COLS, 16, 1, 0);         // column sum: A = tile (MN-major), B = ones
+            const uint64_t db = umma_desc_k_sw128(smem_u32(B_sh)), d1 = umma_desc_k_sw128(smem_u32(ones_sh));
+            auto issue_pv = [&](int j) -> bool {        // column sums of tile j, once the epilogue has written the operand
+                if (!mbar_wait(&bars->v_full[j & 1], (uint32_t)((j >> 1) & 1), abort_flag, 5)) return false;
+                tc_fence_after_sync();
+                const uint64_t dv = umma_desc_mn_sw128(smem_u32(Ev_st + (j & 1) * STAGE_BYTES), ATOM_BYTES, 1024);
 #pragma unroll
-            for (int ks = 0; ks < TM / 16; ++ks)
-                umma_bf16_ss(tmem_base + (uint32_t)(COL_R + (j & 1) * 16), dv + (uint64_t)(ks * (2048 >> 4)), d1, idesc2, ks != 0 ? 1u : 0u);
-            umma_commit(&bars->pv_done[j & 1]);
-        };
+                for (int ks = 0; ks < TM / 16; ++ks)
+                    umma_bf16_ss(tmem_base + (uint32_t)(COL_R + (j & 1) * 16), dv + (uint64_t)(ks * (2048 >> 4)), d1, idesc2, ks != 0 ? 1u : 0u);
+                umma_commit(&bars->pv_done[j & 1]);
+                return true;
+            };
+            bool go = true;
+            for (int i = 0; i < nt && go; ++i) {
+                const int st = i & 1, u = i >> 1;
+                go = mbar_wait(&bars->a_full[st], (uint32_t)(u & 1), abort_flag, 3);
+                if (go && i >= 2) go = mbar_wait(&bars->acc_empty[st], (uint32_t)((u - 1) & 1), abort_flag, 4);
+                if (go) {
+                    tc_fence_after_sync();
+                    const uint64_t da = umma_desc_k_sw128(smem_u32(A_sh + st * ATOM_BYTES));
+#pragma unroll
+                    for (int k16 = 0; k16 < 4; ++k16)
+                        umma_bf16_ss(tmem_base + (uint32_t)(st * ACC_COLS), da + (uint64_t)((k16 * 32) >> 4), db + (uint64_t)((k16 * 32) >> 4), idesc, k16 != 0 ? 1u : 0u);
+                    umma_commit(&bars->acc_full[st]);
+                    if (i >= 1) go = issue_pv(i - 1);
+                }
+            }
+            if (go && nt > 0) issue_pv(nt - 1);
+            umma_commit(&bars->drain);       // arrives once every product issued above has completed
+        }
+    } else if (!is_epi) {
+        // ============================================================ producer warps: two threads per slot of the tile
+        const int ptid = tid - EPI_WARPS * 32;
+        const int prow = ptid & 127, phalf = ptid >> 7;            // this thread: slot prow of the tile, channels [32 phalf, 32 phalf + 32)
         // this thread's half of its slot's state row, all of it in flight at once (32 registers), one tile ahead of its use
         float4 sr[8];
         auto load_state = [&](int i) {
@@ -183,31 +213,32 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
             for (int j = 0; j < 8; ++j) sr[j] = v >= 0 ? __ldg(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
         };
         load_state(0);
+        const int c = ptid & 7;
+        int done = 0;                    // tiles whose E_v copies this thread has issued
         for (int i = 0; i < nt; ++i) {
             const int st = i & 1, u = i >> 1;
-            // the stages of tile i - 2 are free once its column sum has completed (which also means: its gate product has,
-            // and the epilogue is done with its E_k rows and accumulators)
-            if (i >= 2 && !__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[st], (uint32_t)((u - 1) & 1), abort_flag, 1))) break;
-            {   // E_k / E_v rows of the tile: 16 copies of 16 bytes a thread.  The slot ids are fetched first: a copy is a compiler
-                // barrier, so an id load between two copies would put a shared-memory latency in front of every one of them
-                int vj[4];
+            // The tile's stages are released piecewise.  The E_k rows and the accumulators of tile i - 2 are free once the
+            // epilogue has finished its first pass over them (its A tile even earlier: the gate product has completed);
+            // the E_v rows only once that tile's column sum has completed, a whole second pass later.  So the E_k copies,
+            // the state rows and the gate product of tile i start on the first event and only the E_v copies wait for the
+            // second one.
+            if (i >= 2 && !__all_sync(0xffffffffu, mbar_wait(&bars->acc_empty[st], (uint32_t)((u - 1) & 1), abort_flag, 1))) break;
+            // the slot ids are fetched first: a copy is a compiler barrier, so an id load between two copies would put a
+            // shared-memory latency in front of every one of them
+            int vj[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) vj[j] = ids_sh[i * TM + ((ptid + PROD_WARPS * 32 * j) >> 3)];
-                const int c = ptid & 7;
+            for (int j = 0; j < 4; ++j) vj[j] = ids_sh[i * TM + ((ptid + PROD_WARPS * 32 * j) >> 3)];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int r = (ptid + PROD_WARPS * 32 * j) >> 3;
-                    if (vj[j] >= 0) {
-                        const size_t src = (size_t)vj[j] * D + hp * ACC_COLS + c * 8;
-                        const int dst = st * STAGE_BYTES + r * 128 + ((c ^ (r & 7)) << 4);
-                        cp_async16(Ek_st + dst, a.Ek + src);
-                        cp_async16(Ek_st + dst + ATOM_BYTES, a.Ek + src + HD);
-                        cp_async16(Ev_st + dst, a.Ev + src);
-                        cp_async16(Ev_st + dst + ATOM_BYTES, a.Ev + src + HD);
-                    }
+            for (int j = 0; j < 4; ++j) {
+                const int r = (ptid + PROD_WARPS * 32 * j) >> 3;
+                if (vj[j] >= 0) {
+                    const size_t src = (size_t)vj[j] * D + hp * ACC_COLS + c * 8;
+                    const int dst = st * STAGE_BYTES + r * 128 + ((c ^ (r & 7)) << 4);
+                    cp_async16(Ek_st + dst, a.Ek + src);
+                    cp_async16(Ek_st + dst + ATOM_BYTES, a.Ek + src + HD);
                 }
             }
-            cp_commit();
+            cp_commit();                 // group E_k(i)
             {   // this thread's slot: state row (fetched an iteration ago) -> decayed fp16 row of the A tile (state / 64 folded into the exponent)
                 const float dt = dts_sh[i * TM + prow];
                 unsigned char* arow = A_sh + st * ATOM_BYTES + prow * 128;
@@ -228,42 +259,48 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->a_full[st]);
-            if (pw == 0 && lane == 0) {      // gate product of tile i
-                bool go = mbar_wait(&bars->a_full[st], (uint32_t)(u & 1), abort_flag, 3);
-                if (go && i >= 2) go = mbar_wait(&bars->acc_empty[st], (uint32_t)((u - 1) & 1), abort_flag, 4);
-                if (go) {
-                    tc_fence_after_sync();
-                    const uint64_t da = umma_desc_k_sw128(smem_u32(A_sh + st * ATOM_BYTES));
+            if (i >= 1) {                    // the E_v rows of tile i - 1 (every group but E_k(i)) have landed
+                cp_wait<1>();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->ev_full[(i - 1) & 1]);
+            }
+            if (i >= 2 && !__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[st], (uint32_t)((u - 1) & 1), abort_flag, 2))) break;
 #pragma unroll
-                    for (int k16 = 0; k16 < 4; ++k16)
-                        umma_bf16_ss(tmem_base + (uint32_t)(st * ACC_COLS), da + (uint64_t)((k16 * 32) >> 4), db + (uint64_t)((k16 * 32) >> 4), idesc, k16 != 0 ? 1u : 0u);
-                    umma_commit(&bars->acc_full[st]);
+            for (int j = 0; j < 4; ++j) {
+                const int r = (ptid + PROD_WARPS * 32 * j) >> 3;
+                if (vj[j] >= 0) {
+                    const size_t src = (size_t)vj[j] * D + hp * ACC_COLS + c * 8;
+                    const int dst = st * STAGE_BYTES + r * 128 + ((c ^ (r & 7)) << 4);
+                    cp_async16(Ev_st + dst, a.Ev + src);
+                    cp_async16(Ev_st + dst + ATOM_BYTES, a.Ev + src + HD);
                 }
             }
-            cp_wait<0>();                    // this thread's E rows of tile i have landed
-            __syncwarp();                    // ... and so have the other lanes'
-            if (lane == 0) mbar_arrive(&bars->acc_full[st]);
-            if (pw == 1 && lane == 0 && i >= 1) issue_pv(i - 1);
+            cp_commit();                 // group E_v(i)
+            done = i + 1;
+            cp_wait<1>();                // E_k(i) has landed (E_v(i) may still be on its way)
             __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->acc_full[st]);
         }
-        if (pw == 1 && lane == 0 && nt > 0 && !*abort_flag) issue_pv(nt - 1);
         cp_wait<0>();
-        if (lane == 0 && pw < 2) umma_commit(&bars->drain);      // arrives once every product this lane issued has completed
+        __syncwarp();
+        if (done > 0 && done == nt && lane == 0) mbar_arrive(&bars->ev_full[(nt - 1) & 1]);   // the last tile's E_v rows
     } else {
-        // ============================================================ epilogue warps: a warpgroup per head, a thread per slot
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
-        const int wg = warp >> 2;                                   // head of the pair
+        // ============================================================ epilogue warps: a thread per slot and HALF a head (32 columns)
+        // warp = half * 8 + head * 4 + TMEM lane quarter: four epilogue warps per scheduler instead of two.  The kernel is
+        // latency-bound (short dependent chains between the tanh-bound gate pass, the maximum exchange and the operand
+        // stores), so the extra warps are what fills the issue slots.
+        const int head = (warp >> 2) & 1, half = warp >> 3;
         const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-        uint32_t q2[HD / 2];                                        // q / sqrt(hd) of this head as packed bf16 pairs
+        uint32_t q2[HALF / 2];                                      // q / sqrt(hd) of this half head as packed bf16 pairs
 #pragma unroll
-        for (int j = 0; j < HD / 2; ++j) q2[j] = pack_bf16x2(q_sh[wg * HD + 2 * j], q_sh[wg * HD + 2 * j + 1]);
-        float m_run = -INFINITY, l_run = 0.f, o_run = 0.f;          // warpgroup 0: running softmax state of output column `row`
+        for (int j = 0; j < HALF / 2; ++j) q2[j] = pack_bf16x2(q_sh[head * HD + half * HALF + 2 * j], q_sh[head * HD + half * HALF + 2 * j + 1]);
+        float m_run = -INFINITY, l_run = 0.f, o_run = 0.f;          // warps 0..3: running softmax state of output column `row`
         const int hc = row >> 6;                                    // ... which belongs to head hc of the pair
+        const bool folder = warp < 4;
         auto fold = [&](int j) {        // tile j's column sums (its product has completed) into the running state
-            const float* wm = wred + (j & 3) * 2 * EPI_WARPS + hc * 4;
-            const float* ws = wm + EPI_WARPS;
-            const float mt = fmaxf(fmaxf(wm[0], wm[1]), fmaxf(wm[2], wm[3]));
-            const float lt = (ws[0] + ws[1]) + (ws[2] + ws[3]);
+            const float* wr = wred + (j & 3) * 16;
+            const float mt = wr[hc];
+            const float lt = (wr[4 + hc * 4] + wr[4 + hc * 4 + 1]) + (wr[4 + hc * 4 + 2] + wr[4 + hc * 4 + 3]);
             const float v = tmem_ld_1(t_lane + (uint32_t)(COL_R + (j & 1) * 16));
             tmem_wait_ld();
             const float m_new = fmaxf(m_run, mt);
@@ -278,91 +315,87 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
             if (!__all_sync(0xffffffffu, mbar_wait(&bars->acc_full[st], (uint32_t)(u & 1), abort_flag, 6))) { alive = false; break; }
             tc_fence_after_sync();
             const bool ok = ids_sh[i * TM + row] >= 0;
-            const uint32_t t_acc = t_lane + (uint32_t)(st * ACC_COLS + wg * HD);
-            const unsigned char* ekrow = Ek_st + st * STAGE_BYTES + wg * ATOM_BYTES + row * 128;
-            unsigned char* evrow = Ev_st + st * STAGE_BYTES + wg * ATOM_BYTES + row * 128;
-            // ---- gate of the head's 64 columns (kept) and the score
-            uint32_t g2[HD / 2];                                    // packed bf16 pairs
+            const uint32_t t_acc = t_lane + (uint32_t)(st * ACC_COLS + head * HD + half * HALF);
+            const unsigned char* ekrow = Ek_st + st * STAGE_BYTES + head * ATOM_BYTES + row * 128;
+            unsigned char* evrow = Ev_st + st * STAGE_BYTES + head * ATOM_BYTES + row * 128;
+            // ---- gate of this thread's 32 columns (kept) and its part of the score
+            uint32_t g2[HALF / 2];                                  // packed bf16 pairs
             float sp0 = 0.f, sp1 = 0.f;
-            {
-                float pre[2][16];
-                tmem_ld_32x32b_x16(t_acc, pre[0]);
 #pragma unroll
-                for (int c = 0; c < HD / 16; ++c) {              // 16 accumulator columns per load, the next load in flight
-                    // the E_k chunks are loaded before the wait (a load after it could not be moved above it by the compiler)
-                    const uint4 eq[2] = {*reinterpret_cast<const uint4*>(ekrow + (((c * 2) ^ (row & 7)) << 4)),
-                                         *reinterpret_cast<const uint4*>(ekrow + (((c * 2 + 1) ^ (row & 7)) << 4))};
-                    tmem_wait_ld();
-                    if (c + 1 < HD / 16) tmem_ld_32x32b_x16(t_acc + (c + 1) * 16, pre[(c + 1) & 1]);
+            for (int c = 0; c < HALF / 16; ++c) {                // 16 accumulator columns per load
+                float pre[16];
+                tmem_ld_32x32b_x16(t_acc + c * 16, pre);
+                // the E_k chunks are loaded before the wait (a load after it could not be moved above it by the compiler)
+                const uint4 eq[2] = {*reinterpret_cast<const uint4*>(ekrow + (((half * 4 + c * 2) ^ (row & 7)) << 4)),
+                                     *reinterpret_cast<const uint4*>(ekrow + (((half * 4 + c * 2 + 1) ^ (row & 7)) << 4))};
+                tmem_wait_ld();
 #pragma unroll
-                    for (int j8 = 0; j8 < 2; ++j8) {
-                        const int ch = c * 2 + j8;               // chunk of 8 columns
-                        const uint4 e = eq[j8];
-                        const uint32_t ew[4] = {e.x, e.y, e.z, e.w};
+                for (int j8 = 0; j8 < 2; ++j8) {
+                    const uint32_t ew[4] = {eq[j8].x, eq[j8].y, eq[j8].z, eq[j8].w};
 #pragma unroll
-                        for (int pr = 0; pr < 4; ++pr) {
-                            const int w = ch * 4 + pr;               // pair of columns
-                            const float h0 = pre[c & 1][j8 * 8 + pr * 2], h1 = pre[c & 1][j8 * 8 + pr * 2 + 1];
-                            const float g0 = SILU ? fmaf(h0, tanh_approx(h0), h0) : h0;
-                            const float g1 = SILU ? fmaf(h1, tanh_approx(h1), h1) : h1;
-                            g2[w] = pack_bf16x2(g0, g1);
-                            // bf16 x bf16 products are exact in fp32, where the score is summed
-                            fma_f32_bf16x2(sp0, sp1, g2[w], mul_bf16x2(q2[w], ew[pr]));
-                        }
+                    for (int pr = 0; pr < 4; ++pr) {
+                        const int w = (c * 2 + j8) * 4 + pr;         // pair of columns within the half head
+                        const float h0 = pre[j8 * 8 + pr * 2], h1 = pre[j8 * 8 + pr * 2 + 1];
+                        const float g0 = SILU ? fmaf(h0, tanh_approx(h0), h0) : h0;
+                        const float g1 = SILU ? fmaf(h1, tanh_approx(h1), h1) : h1;
+                        g2[w] = pack_bf16x2(g0, g1);
+                        // bf16 x bf16 products are exact in fp32, where the score is summed
+                        fma_f32_bf16x2(sp0, sp1, g2[w], mul_bf16x2(q2[w], ew[pr]));
                     }
                 }
             }
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->acc_empty[st]);       // accumulators read
-            // ---- tile maximum of the head: warp shuffles, then the four warps meet on an mbarrier (bounded, unlike bar.sync)
-            const float s = ok ? sp0 + sp1 : -INFINITY;
-            float* wm = wred + (i & 3) * 2 * EPI_WARPS;
-            {
-                float mx = s;
+            // ---- the rows' scores: both halves post their partial sums, the head's eight warps meet on an mbarrier (bounded)
+            float* xb = xch + ((i & 1) * HPC + head) * 2 * TM;
+            xb[half * TM + row] = ok ? sp0 + sp1 : -INFINITY;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->hbar[head]);
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars->hbar[head], (uint32_t)(i & 1), abort_flag, 8))) { alive = false; break; }
+            const float s = xb[row] + xb[TM + row];
+            // tile maximum of the head: every warp forms it from the 128 posted pairs (no second barrier)
+            float mt = fmaxf(fmaxf(xb[lane] + xb[TM + lane], xb[32 + lane] + xb[TM + 32 + lane]),
+                             fmaxf(xb[64 + lane] + xb[TM + 64 + lane], xb[96 + lane] + xb[TM + 96 + lane]));
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-                if (lane == 0) {
-                    wm[warp] = mx;
-                    mbar_arrive(&bars->hbar[wg]);
-                }
-            }
-            if (!__all_sync(0xffffffffu, mbar_wait(&bars->hbar[wg], (uint32_t)(i & 1), abort_flag, 8))) { alive = false; break; }
-            const float mt = fmaxf(fmaxf(wm[wg * 4], wm[wg * 4 + 1]), fmaxf(wm[wg * 4 + 2], wm[wg * 4 + 3]));
+            for (int o = 16; o > 0; o >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, o));
             const float prob = ok ? __expf(s - mt) : 0.f;            // every tile holds at least one slot, so mt is finite
             const uint32_t p2 = pack_bf16x2(prob, prob);
-            {
+            if (half == 0) {                                         // sums of p and the maximum, for the fold
+                float* wr = wred + (i & 3) * 16;
                 const float ps = warp_sum(prob);
-                if (lane == 0) wm[EPI_WARPS + warp] = ps;
+                if (lane == 0) {
+                    wr[4 + head * 4 + (warp & 3)] = ps;
+                    if ((warp & 3) == 0) wr[head] = mt;
+                }
             }
-            // ---- (p * gate * E_v)[k, d] in bf16, over the E_v rows themselves
-            //      (four chunks' loads first: a store is a compiler barrier for the loads behind it)
-#pragma unroll
-            for (int g4 = 0; g4 < 2; ++g4) {
+            // ---- (p * gate * E_v)[k, d] in bf16, over the E_v rows themselves, once they have landed (the four chunks' loads
+            //      first: a store is a compiler barrier for the loads behind it)
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars->ev_full[st], (uint32_t)(u & 1), abort_flag, 10))) { alive = false; break; }
+            {
                 uint4 ev4[4];
 #pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4) ev4[c4] = *reinterpret_cast<const uint4*>(evrow + (((g4 * 4 + c4) ^ (row & 7)) << 4));
+                for (int c4 = 0; c4 < 4; ++c4) ev4[c4] = *reinterpret_cast<const uint4*>(evrow + (((half * 4 + c4) ^ (row & 7)) << 4));
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4) {
-                    const int ch = g4 * 4 + c4;
                     const uint32_t ew[4] = {ev4[c4].x, ev4[c4].y, ev4[c4].z, ev4[c4].w};
                     uint32_t w[4];
 #pragma unroll
-                    for (int pr = 0; pr < 4; ++pr) w[pr] = ok ? mul_bf16x2(mul_bf16x2(g2[ch * 4 + pr], p2), ew[pr]) : 0u;   // rows without a slot hold stale bytes
-                    st_shared_v4(evrow + ((ch ^ (row & 7)) << 4), w[0], w[1], w[2], w[3]);
+                    for (int pr = 0; pr < 4; ++pr) w[pr] = ok ? mul_bf16x2(mul_bf16x2(g2[c4 * 4 + pr], p2), ew[pr]) : 0u;   // rows without a slot hold stale bytes
+                    st_shared_v4(evrow + (((half * 4 + c4) ^ (row & 7)) << 4), w[0], w[1], w[2], w[3]);
                 }
             }
             fence_proxy_async_smem();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->v_full[st]);          // operand rows (and this warp's maximum and sum) are in place
-            if (wg == 0 && i > 0) {     // fold tile i - 1 while the column sum of tile i is on its way
+            if (lane == 0) mbar_arrive(&bars->v_full[st]);          // operand rows (and this warp's sum, the head's maximum) are in place
+            if (folder && i > 0) {      // fold tile i - 1 while the column sum of tile i is on its way
                 if (!__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1), abort_flag, 7))) { alive = false; break; }
                 tc_fence_after_sync();
                 fold(i - 1);
             }
         }
-        if (wg == 0 && alive && nt > 0 &&
+        if (folder && alive && nt > 0 &&
             __all_sync(0xffffffffu, mbar_wait(&bars->pv_done[(nt - 1) & 1], (uint32_t)(((nt - 1) >> 1) & 1), abort_flag, 7))) {
             tc_fence_after_sync();
             fold(nt - 1);
