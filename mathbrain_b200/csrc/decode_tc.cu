@@ -137,7 +137,61 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
         tmem_alloc(&bars->tmem_base, 512);
         tmem_relinquish();
     }
-    {   // operands every tile shares: W (fp16, times 64; times 1/2 for SiLU), ones, decay logs, q; then this CTA's slots and ages
+    // producer threads (two per slot of a tile): slot prow, channels [32 phalf, 32 phalf + 32); 16-byte chunk c of four rows' E rows
+    const bool is_prod = !is_epi && warp != MMA_WARP;
+    const int ptid = tid - EPI_WARPS * 32;
+    const int prow = ptid & 127, phalf = (ptid >> 7) & 1;
+    const int c = ptid & 7;
+    float4 sr[8];        // a producer thread's half of its slot's state row, all of it in flight at once, one tile ahead of its use
+    auto load_state = [&](int i) {
+        const int v = i < nt ? ids_sh[i * TM + prow] : -1;
+        const float4* src = reinterpret_cast<const float4*>(a.state + ((size_t)b * a.V + (v >= 0 ? v : 0)) * N + 32 * phalf);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sr[j] = v >= 0 ? __ldg(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    // this thread's 8 copies of 16 bytes of tile i's E_k (or E_v) rows, both heads, into the tile's stage
+    auto issue_rows = [&](unsigned char* stage0, const __nv_bfloat16* table, int i, const int (&vj)[4]) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int r = (ptid + PROD_WARPS * 32 * j) >> 3;
+            if (vj[j] >= 0) {
+                const size_t src = (size_t)vj[j] * D + hp * ACC_COLS + c * 8;
+                const int dst = (i & 1) * STAGE_BYTES + r * 128 + ((c ^ (r & 7)) << 4);
+                cp_async16(stage0 + dst, table + src);
+                cp_async16(stage0 + dst + ATOM_BYTES, table + src + HD);
+            }
+        }
+    };
+    {   // this CTA's slots and their ages, and the operands every tile shares: W (fp16, times 64; times 1/2 for SiLU), ones,
+        // decay logs, q.  The slot ids are fetched first and the ages (a dependent load) after the W block, so that the
+        // two round trips to memory run under the W loads instead of after them: a CTA walks only a few tiles and the time
+        // to its first one counts.
+        constexpr int IDS_PER_THREAD = (MAXT * TM + THREADS - 1) / THREADS;
+        int vs[IDS_PER_THREAD];
+#pragma unroll
+        for (int j = 0; j < IDS_PER_THREAD; ++j) {
+            const int idx = tid + j * THREADS;
+            const int k = (split + (idx >> 7) * a.S) * TM + (idx & 127);
+            vs[j] = (idx < nt * TM && k < na) ? __ldg(a.active + (size_t)b * a.Kcap + k) : -1;
+        }
+        const int t_now = a.t_dev ? *a.t_dev : a.t_now;
+#pragma unroll
+        for (int j = 0; j < IDS_PER_THREAD; ++j) {
+            const int idx = tid + j * THREADS;
+            if (idx < nt * TM) ids_sh[idx] = vs[j];
+        }
+        __syncthreads();
+        // the producers' fetches for the first tile start here, under the W loads and the second round trip (the ages)
+        if (is_prod) {
+            int vj[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) vj[j] = ids_sh[(ptid + PROD_WARPS * 32 * j) >> 3];
+            issue_rows(Ek_st, a.Ek, 0, vj);
+            cp_commit();                 // group E_k(0)
+            issue_rows(Ev_st, a.Ev, 0, vj);
+            cp_commit();                 // group E_v(0)
+            load_state(0);
+        }
         const float wscale = (SILU ? 0.5f : 1.0f) * STATE_F16_UNSCALE;
         for (int idx = tid; idx < N * ACC_COLS / 4; idx += THREADS) {
             const int n = idx >> 5, dd4 = (idx & 31) * 4;
@@ -147,15 +201,16 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
             *reinterpret_cast<__half*>(B_sh + sw128_off(dd4 + 2, n)) = __float2half_rn(w.z * wscale);
             *reinterpret_cast<__half*>(B_sh + sw128_off(dd4 + 3, n)) = __float2half_rn(w.w * wscale);
         }
+        int lt[IDS_PER_THREAD];
+#pragma unroll
+        for (int j = 0; j < IDS_PER_THREAD; ++j) lt[j] = vs[j] >= 0 ? a.last_t[(size_t)b * a.V + vs[j]] : 0;
         for (int i = tid; i < 1024; i += THREADS) reinterpret_cast<__nv_bfloat16*>(ones_sh)[i] = __float2bfloat16(1.0f);
         if (tid < N) l2r_sh[tid] = log2f(a.rhos[tid]);
         if (tid < ACC_COLS) q_sh[tid] = ld_dyn_f32(a.q, a.q_dt, ((size_t)b * a.H + hp * HPC) * HD + tid) * 0.125f;
-        const int t_now = a.t_dev ? *a.t_dev : a.t_now;
-        for (int idx = tid; idx < nt * TM; idx += THREADS) {
-            const int k = (split + (idx >> 7) * a.S) * TM + (idx & 127);
-            const int v = k < na ? a.active[(size_t)b * a.Kcap + k] : -1;
-            ids_sh[idx] = v;
-            dts_sh[idx] = v >= 0 ? (float)(t_now - a.last_t[(size_t)b * a.V + v]) : 0.f;
+#pragma unroll
+        for (int j = 0; j < IDS_PER_THREAD; ++j) {
+            const int idx = tid + j * THREADS;
+            if (idx < nt * TM) dts_sh[idx] = vs[j] >= 0 ? (float)(t_now - lt[j]) : 0.f;
         }
     }
     fence_proxy_async_smem();
@@ -202,18 +257,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
         }
     } else if (!is_epi) {
         // ============================================================ producer warps: two threads per slot of the tile
-        const int ptid = tid - EPI_WARPS * 32;
-        const int prow = ptid & 127, phalf = ptid >> 7;            // this thread: slot prow of the tile, channels [32 phalf, 32 phalf + 32)
-        // this thread's half of its slot's state row, all of it in flight at once (32 registers), one tile ahead of its use
-        float4 sr[8];
-        auto load_state = [&](int i) {
-            const int v = i < nt ? ids_sh[i * TM + prow] : -1;
-            const float4* src = reinterpret_cast<const float4*>(a.state + ((size_t)b * a.V + (v >= 0 ? v : 0)) * N + 32 * phalf);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) sr[j] = v >= 0 ? __ldg(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-        };
-        load_state(0);
-        const int c = ptid & 7;
+        // (the copies and the state row of tile 0 were issued in the prologue)
         int done = 0;                    // tiles whose E_v copies this thread has issued
         for (int i = 0; i < nt; ++i) {
             const int st = i & 1, u = i >> 1;
@@ -228,17 +272,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
             int vj[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) vj[j] = ids_sh[i * TM + ((ptid + PROD_WARPS * 32 * j) >> 3)];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int r = (ptid + PROD_WARPS * 32 * j) >> 3;
-                if (vj[j] >= 0) {
-                    const size_t src = (size_t)vj[j] * D + hp * ACC_COLS + c * 8;
-                    const int dst = st * STAGE_BYTES + r * 128 + ((c ^ (r & 7)) << 4);
-                    cp_async16(Ek_st + dst, a.Ek + src);
-                    cp_async16(Ek_st + dst + ATOM_BYTES, a.Ek + src + HD);
-                }
-            }
-            cp_commit();                 // group E_k(i)
+            if (i >= 1) issue_rows(Ek_st, a.Ek, i, vj);
+            if (i >= 1) cp_commit();     // group E_k(i)
             {   // this thread's slot: state row (fetched an iteration ago) -> decayed fp16 row of the A tile (state / 64 folded into the exponent)
                 const float dt = dts_sh[i * TM + prow];
                 unsigned char* arow = A_sh + st * ATOM_BYTES + prow * 128;
@@ -265,17 +300,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_decode_tc(Args a, int* status) {
                 if (lane == 0) mbar_arrive(&bars->ev_full[(i - 1) & 1]);
             }
             if (i >= 2 && !__all_sync(0xffffffffu, mbar_wait(&bars->pv_done[st], (uint32_t)((u - 1) & 1), abort_flag, 2))) break;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int r = (ptid + PROD_WARPS * 32 * j) >> 3;
-                if (vj[j] >= 0) {
-                    const size_t src = (size_t)vj[j] * D + hp * ACC_COLS + c * 8;
-                    const int dst = st * STAGE_BYTES + r * 128 + ((c ^ (r & 7)) << 4);
-                    cp_async16(Ev_st + dst, a.Ev + src);
-                    cp_async16(Ev_st + dst + ATOM_BYTES, a.Ev + src + HD);
-                }
-            }
-            cp_commit();                 // group E_v(i)
+            if (i >= 1) issue_rows(Ev_st, a.Ev, i, vj);
+            if (i >= 1) cp_commit();     // group E_v(i)
             done = i + 1;
             cp_wait<1>();                // E_k(i) has landed (E_v(i) may still be on its way)
             __syncwarp();
